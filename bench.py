@@ -1,0 +1,356 @@
+#!/usr/bin/env python
+"""Throughput of the Word2Vec SGNS minibatch path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one minibatch through the whole hot path: preprocessing
+(subsampling, window bounds, pair list, permutation, negative ids), the
+positive-pair update kernel and the negative-pair update kernel.  Workload
+(BASELINE.json configs[1]): vocab 1M, dim 300 fp32, minibatches of 1M tokens
+drawn i.i.d. from Zipf(1.07) over word ranks (seeded), window 5, 5 negatives,
+nreuse 5, both matrices U(-0.5,0.5)/dim; frequent-word subsampling is switched
+off (wsample=1 keeps every word), so every token yields pairs.
+
+With N > 1 every rank runs the same workload on its own minibatches (weak
+scaling) and both matrices are averaged with an all-reduce every
+``--sync-every`` (8) minibatches, inside the timed region.
+
+Prints ONE JSON line (rank 0).  `value` is measured with the minibatches
+already in device memory; `e2e` is the same loop through the host-buffer entry
+point (pinned host minibatch -> device copy -> update -> pair count back).
+`--impl reference` times the reference's own CPU kernels (compiled from its C
+source into oracle/_ref) with all host cores on a bounded sample per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "SGNS train words/sec at vocab 1M dim 300"
+UNIT = "words/s"
+
+WORKLOAD = dict(vocab=1_000_000, dim=300, ntokens=1_000_000, zipf_s=1.07, nskip=5, nneg=5, nreuse=5,
+                lrate=1e-3, texp=0.5, vexp=0.5, wsample=1.0, doc_len=1000)
+POOL = 4             # distinct minibatches per rank, cycled
+CPU_SAMPLE = 500_000  # tokens of one minibatch the CPU arms process per step
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the negative-update
+# kernel on this workload, from an ncu capture (see the summary under profiles/);
+# None until a capture exists.
+NEG_DRAM_TRAFFIC_BYTES = None
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for k, nm in enumerate(names):
+                if len(r) > 5 + k and r[5 + k].lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(max(mx)) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_pool(rank: int, n: int):
+    from bidmach_b200.corpus import zipf_cdf, zipf_corpus
+    w = WORKLOAD
+    cdf = zipf_cdf(w["vocab"], w["zipf_s"])
+    return [zipf_corpus(w["vocab"], w["ntokens"], w["zipf_s"], seed=1000 * rank + k,
+                        doc_len=w["doc_len"], cdf=cdf, first_doc=k * 1000) for k in range(n)]
+
+
+# ---------------------------------------------------------------------------
+# reference arm / CPU baseline: the reference's own C kernels on host cores
+# ---------------------------------------------------------------------------
+
+def cpu_arm_setup(tokens: np.ndarray, seed: int = 5):
+    """Preprocess a CPU_SAMPLE-token prefix the CPU way and build host matrices."""
+    from oracle import oracle as orc
+    w = WORKLOAD
+    rng = np.random.default_rng(seed)
+    S = CPU_SAMPLE
+    toks = np.ascontiguousarray(tokens[:S])
+    words, lb, ub = orc.wordmats_bounds(toks, w["vocab"], w["nskip"], orc.salpha_of(w["wsample"], w["vocab"]),
+                                        rng.random(S, dtype=np.float32), rng.random(S, dtype=np.float32))
+    npairs = orc.count_pairs(words, lb, ub)
+    WA, WB = orc.getnegs(words, lb, ub, w["nneg"], w["nreuse"], w["vocab"], orc.expt_of(0.75),
+                         rng.random(npairs), rng.random(npairs // w["nreuse"] * w["nneg"] + 8, dtype=np.float32))
+    mats = []
+    for _ in range(2):
+        m = np.empty((w["vocab"], w["dim"]), np.float32)
+        rng.random(out=m, dtype=np.float32)
+        m -= np.float32(0.5)
+        m /= np.float32(w["dim"])
+        mats.append(m)
+    A, B = mats
+    return orc, (words, lb, ub, WA, WB, A, B)
+
+
+def cpu_arm_step(orc, state, kind: str, cores: int) -> float:
+    """One bounded step of the CPU path: positive + negative update.  Seconds."""
+    w = WORKLOAD
+    words, lb, ub, WA, WB, A, B = state
+    lr = np.float32(w["lrate"])
+    t0 = time.perf_counter()
+    orc.word2vecPos(w["dim"], len(words), w["nskip"], words, lb, ub, A, B, lr, w["vexp"], cores, kind)
+    orc.word2vecNeg(w["dim"], WA.shape[0], w["nneg"], w["nreuse"], WA, WB, A, B, lr / w["nneg"],
+                    w["vexp"], cores, kind)
+    return time.perf_counter() - t0
+
+
+def cpu_kind():
+    from oracle import oracle as orc
+    return "reference" if orc.have_reference() else "port"
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    kind = cpu_kind()
+    pool = make_pool(0, 1)
+    orc, state = cpu_arm_setup(pool[0])
+    for _ in range(args.warmup):
+        cpu_arm_step(orc, state, kind, cores)
+    t = [cpu_arm_step(orc, state, kind, cores) for _ in range(args.steps)]
+    total = float(np.sum(t))
+    value = CPU_SAMPLE * args.steps / total
+    sample = (f"first {CPU_SAMPLE} tokens of one 1M-token minibatch per step; positive + negative "
+              f"update kernels of BIDMach_CPUMACH.c, {cores} OpenMP threads; preprocessing untimed")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": config_dict(args, extra={"cpu_sample_tokens": CPU_SAMPLE}),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(args, extra=None):
+    w = WORKLOAD
+    c = {"workload": "configs[1]: single-minibatch SGNS update, vocab 1M, dim 300, 1M-token "
+                     "Zipf(1.07) minibatches, window 5, nneg 5, nreuse 5, no subsampling",
+         "vocab": w["vocab"], "dim": w["dim"], "tokens_per_minibatch": w["ntokens"], "nskip": w["nskip"],
+         "nneg": w["nneg"], "nreuse": w["nreuse"], "wsample": w["wsample"], "lrate": w["lrate"],
+         "vexp": w["vexp"], "minibatch_pool": POOL,
+         "parallelism": f"dp{args.gpus}: replicas, own minibatches, all-reduce(avg) of both matrices "
+                        f"every {args.sync_every} minibatches" if args.gpus > 1 else "single GPU",
+         "l2_policy": "inputs larger than L2: 2.4 GB of embedding rows gathered per Zipf draw; no flush"}
+    if extra:
+        c.update(extra)
+    return c
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from bidmach_b200 import _lib, Word2Vec
+    from bidmach_b200.word2vec import Opts
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for this path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = _lib.load()
+    w = WORKLOAD
+    N = w["ntokens"]
+
+    o = Opts(dim=w["dim"], vocabSize=w["vocab"], nskip=w["nskip"], nneg=w["nneg"], nreuse=w["nreuse"],
+             lrate=w["lrate"], texp=w["texp"], vexp=w["vexp"], wsample=w["wsample"], seed=17 + rank)
+    model = Word2Vec(o, device=torch.device("cuda", local)).init(N)
+    # configs[1]: both matrices random
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    model.modelmats[1].copy_((torch.rand(w["vocab"], w["dim"], device="cuda", generator=g) - 0.5) / w["dim"])
+    if world > 1:
+        for m in model.modelmats:
+            dist.broadcast(m, src=0)
+
+    pool = make_pool(rank, POOL)
+    host = [torch.from_numpy(p).pin_memory() for p in pool]
+    devt = [h.cuda() for h in host]
+    stream = torch.cuda.current_stream()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def run_steps(nsteps, host_path, first_pos):
+        pos = first_pos
+        for s in range(nsteps):
+            pos += N
+            if host_path:
+                model.dobatchg([host[s % POOL].numpy()], 0, pos)
+            else:
+                model.dobatch([devt[s % POOL]], 0, pos)
+            if world > 1 and (s + 1) % args.sync_every == 0:
+                model.mergeModelFn()
+        return pos
+
+    def timed(host_path, pos):
+        pos = run_steps(args.warmup, host_path, pos)
+        sync_all()
+        lib.w2v_set_timing(model._ctx, 0 if host_path else 1)
+        launches0 = lib.w2v_launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler = ClockSampler(local)
+        sampler.start()
+        e0.record(stream)
+        pos = run_steps(args.steps, host_path, pos)
+        e1.record(stream)
+        sync_all()
+        clocks = sampler.stop()
+        ms = e0.elapsed_time(e1)
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), lib.w2v_launch_count() - launches0, clocks, pos
+
+    pos = 0
+    ms_dev, launches, clocks, pos = timed(False, pos)
+    tm = _lib.W2VTiming()
+    lib.w2v_get_timing(model._ctx, tm)
+    ms_e2e, _, clocks_e2e, pos = timed(True, pos)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    K = args.steps
+    value = world * N * K / (ms_dev * 1e-3)
+    e2e_value = world * N * K / (ms_e2e * 1e-3)
+    peak, peak_kind = measured_peak_gbs()
+    row = 4 * w["dim"]
+    nb = max(1, tm.train_batches)
+    groups, pairs = tm.groups / nb, tm.pairs / nb
+    neg_bytes = 2.0 * groups * (w["nneg"] + w["nreuse"]) * row
+    neg_s = tm.neg_ms / nb * 1e-3
+    pos_s = tm.pos_ms / nb * 1e-3
+    achieved = neg_bytes / neg_s / 1e9 if neg_s > 0 else None
+    # positive kernel, same accounting: (centres-with-pairs + pairs) rows read and written;
+    # every token is kept in this workload, so centres ~ tokens
+    pos_bytes = 2.0 * (N + pairs) * row
+    roofline = {"bound": "hbm", "kernel": "neg_update_kernel<5,5,3>", "achieved": achieved, "peak": peak,
+                "peak_kind": peak_kind, "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
+                "traffic": NEG_DRAM_TRAFFIC_BYTES, "algorithmic_bytes_per_launch": neg_bytes,
+                "avg_launch_ms": neg_s * 1e3}
+    phases = {"prep_ms": tm.prep_ms / nb, "permute_ms": tm.permute_ms / nb, "pos_ms": tm.pos_ms / nb,
+              "neg_ms": tm.neg_ms / nb, "pairs_per_step": pairs, "groups_per_step": groups,
+              "pos_algorithmic_gbs": pos_bytes / pos_s / 1e9 if pos_s > 0 else None,
+              "update_kernels_frac_of_peak": ((neg_bytes + pos_bytes) / (neg_s + pos_s) / 1e9 / peak)
+              if neg_s + pos_s > 0 else None}
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        cores = os.cpu_count() or 1
+        kind = cpu_kind()
+        orc, state = cpu_arm_setup(pool[0])
+        cpu_arm_step(orc, state, kind, cores)
+        reps = 3
+        t = min(cpu_arm_step(orc, state, kind, cores) for _ in range(reps))
+        cpu = {"value": CPU_SAMPLE / t, "unit": UNIT, "cores": cores, "kind": kind,
+               "sample": f"first {CPU_SAMPLE} tokens of one minibatch, positive + negative update kernels "
+                         f"of the reference's BIDMach_CPUMACH.c with {cores} OpenMP threads, best of {reps}; "
+                         "preprocessing untimed"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": args.warmup,
+        "ms_per_step": ms_dev / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": config_dict(args),
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 8 * N, "d2h_bytes_per_step": 8,
+                "ms_per_step": ms_e2e / K},
+        "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu, "phases": phases,
+        "clocks": clocks, "clocks_e2e": clocks_e2e,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sync-every", type=int, default=8)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,11 @@
+"""B200 (sm_100a) implementation of BIDMach's Word2Vec skip-gram
+negative-sampling minibatch path behind the reference's CUMACH interface.
+
+``CUMACH``     the five native methods of edu.berkeley.bid.CUMACH for this path
+``Word2Vec``   host-side mirror of BIDMach.networks.Word2Vec (options, dobatch,
+               evalbatch) above the C-ABI library
+``Learner`` / ``ParLearner``  the minibatch schedule that drives it
+"""
+from .cumach import CUMACH, cuda_error_string  # noqa: F401
+from .word2vec import Word2Vec  # noqa: F401
+from .learner import Learner, ParLearner, MatSource  # noqa: F401

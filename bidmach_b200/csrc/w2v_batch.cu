@@ -1,0 +1,530 @@
+// Whole-minibatch path: the device version of Word2Vec.wordMats / dobatch /
+// evalbatch (networks/Word2Vec.scala:167-278) on top of the four kernels.
+//
+// Pipeline for one minibatch of `ncols` tokens (all on one stream):
+//   1. words_bounds_kernel   subsampling mask + window bounds      (:216-237)
+//   2. count_pairs_kernel    good contexts per centre              (:283-302)
+//   3. exclusive scan        start of each centre's contexts
+//   4. fill_pairs_kernel     ordered context list + permutation keys (:309-330, :254-255)
+//   5. radix sort            permutation = stable descending key order (:256-259)
+//   6. negative_ids_kernel   min(V-1, int(V * u^expt))             (:264-265, :356)
+//   7. Pos / Neg update kernels, or the two eval kernels
+//
+// Every step is a deterministic map of the token matrix and of four arrays of
+// uniform draws, so with caller-supplied draws the outputs can be compared bit
+// for bit with the CPU path.  Without them the draws come from Philox4x32-10
+// (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11) keyed
+// by (seed, batch id), generated inside the kernels that consume them.
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <cub/device/device_radix_sort.cuh>
+#include <cub/device/device_scan.cuh>
+
+#include "../../include/bidmach_b200.h"
+#include "w2v_internal.h"
+
+namespace w2v {
+
+// ---------------------------------------------------------------------------
+// Philox4x32-10
+// ---------------------------------------------------------------------------
+struct PhiloxOut {
+  uint32_t v[4];
+};
+
+__host__ __device__ inline PhiloxOut philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2,
+                                                   uint32_t c3, uint32_t k0, uint32_t k1) {
+  const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+  for (int r = 0; r < 10; r++) {
+    uint64_t p0 = (uint64_t)M0 * c0, p1 = (uint64_t)M1 * c2;
+    uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ k0;
+    uint32_t n1 = (uint32_t)p1;
+    uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ k1;
+    uint32_t n3 = (uint32_t)p0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += W0; k1 += W1;
+  }
+  PhiloxOut o;
+  o.v[0] = c0; o.v[1] = c1; o.v[2] = c2; o.v[3] = c3;
+  return o;
+}
+
+// 24 random bits -> fp32 in [0, 1)
+__host__ __device__ inline float u01(uint32_t x) { return (float)(x >> 8) * (1.0f / 16777216.0f); }
+
+enum : uint32_t { kStreamSampleWindow = 1, kStreamPermute = 2, kStreamNegs = 3, kStreamInit = 4 };
+
+struct Rng {
+  uint32_t k0, k1, batch;
+};
+
+// ---------------------------------------------------------------------------
+// Preprocessing kernels
+// ---------------------------------------------------------------------------
+
+// words[i] = id if (id < vocab and u1 < sqrt(x) + x, x = float(id+1) * salpha) else -1;
+// ub = min(nskip, int(u2 * nskip) + 1) clipped to the sentence; lb likewise.
+// Sentence clipping only ever matters within nskip positions, so each thread
+// looks at most nskip tokens back and forth instead of running a segmented scan.
+__global__ void words_bounds_kernel(int ncols, const int *__restrict__ tokens, int wrow, int vocab,
+                                    int nskip, float salpha, const float *__restrict__ usample,
+                                    const float *__restrict__ uwindow, Rng rng,
+                                    int *__restrict__ words, int *__restrict__ lb,
+                                    int *__restrict__ ub) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= ncols) return;
+  const int srow = 1 - wrow;
+  const int id = tokens[2 * i + wrow];
+  const int sid = tokens[2 * i + srow];
+  float u1, u2;
+  if (usample == nullptr || uwindow == nullptr) {
+    PhiloxOut r = philox4x32_10((uint32_t)i, 0u, kStreamSampleWindow, rng.batch, rng.k0, rng.k1);
+    u1 = u01(r.v[0]);
+    u2 = u01(r.v[1]);
+  }
+  if (usample) u1 = usample[i];
+  if (uwindow) u2 = uwindow[i];
+
+  const float x = __fmul_rn((float)(id + 1), salpha);
+  const float thr = __fadd_rn(__fsqrt_rn(x), x);
+  const bool good = (id < vocab) && (u1 < thr);
+  words[i] = good ? id : -1;
+
+  int ubr = (int)__fmul_rn(u2, (float)nskip) + 1;
+  ubr = min(ubr, nskip);
+  int back = 0;
+  while (back < nskip && i - back - 1 >= 0 && tokens[2 * (i - back - 1) + srow] == sid) back++;
+  int fwd = 0;
+  while (fwd < nskip && i + fwd + 1 < ncols && tokens[2 * (i + fwd + 1) + srow] == sid) fwd++;
+  lb[i] = max(-ubr, -back);
+  ub[i] = min(ubr, fwd);
+}
+
+__global__ void count_pairs_kernel(int ncols, const int *__restrict__ words,
+                                   const int *__restrict__ lb, const int *__restrict__ ub,
+                                   int *__restrict__ cnt) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= ncols) return;
+  int n = 0;
+  if (words[i] >= 0) {
+    const int hi = ub[i];
+    for (int j = lb[i]; j <= hi; j++)
+      if (j != 0 && words[i + j] >= 0) n++;
+  }
+  cnt[i] = n;
+}
+
+// counts[0] = number of pairs, counts[1] = pairs / nreuse
+__global__ void totals_kernel(int ncols, const int *__restrict__ cnt, const int *__restrict__ off,
+                              int nreuse, int *__restrict__ counts) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    int total = (ncols > 0) ? off[ncols - 1] + cnt[ncols - 1] : 0;
+    counts[0] = total;
+    counts[1] = total / nreuse;
+  }
+}
+
+// Context words in (centre ascending, offset ascending) order, each with its
+// permutation key.  The reference turns a uniform u into the key (u + 1) - 1
+// in fp32 (Word2Vec.scala:255), i.e. u rounded to a multiple of 2^-23; the key
+// is stored as that multiple, an integer in [0, 2^23], which sorts identically.
+__global__ void fill_pairs_kernel(int ncols, int nskip, const int *__restrict__ words,
+                                  const int *__restrict__ lb, const int *__restrict__ ub,
+                                  const int *__restrict__ off, const float *__restrict__ upermute,
+                                  Rng rng, int *__restrict__ ctx, uint32_t *__restrict__ keys) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= ncols) return;
+  if (words[i] < 0) return;
+  int at = off[i];
+  const int hi = ub[i];
+  PhiloxOut r;
+  int have = -1;
+  for (int j = lb[i]; j <= hi; j++) {
+    if (j == 0) continue;
+    const int w = words[i + j];
+    if (w < 0) continue;
+    const int row = (j < 0) ? j + nskip : j + nskip - 1;
+    float u;
+    if (upermute) {
+      u = upermute[(int64_t)i * (2 * nskip) + row];
+    } else {
+      if ((row >> 2) != have) {
+        have = row >> 2;
+        r = philox4x32_10((uint32_t)i, (uint32_t)have, kStreamPermute, rng.batch, rng.k0, rng.k1);
+      }
+      u = u01(r.v[row & 3]);
+    }
+    const float key = __fadd_rn(__fadd_rn(u, 1.0f), -1.0f);
+    ctx[at] = w;
+    keys[at] = (uint32_t)__fmul_rn(key, 8388608.0f);
+    at++;
+  }
+}
+
+__global__ void negative_ids_kernel(int64_t n, const float *__restrict__ unegs, Rng rng, int vocab,
+                                    float expt, int *__restrict__ out) {
+  const int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (q >= n) return;
+  float u;
+  if (unegs) {
+    u = unegs[q];
+  } else {
+    const uint64_t blk = (uint64_t)q >> 2;
+    PhiloxOut r = philox4x32_10((uint32_t)blk, (uint32_t)(blk >> 32), kStreamNegs, rng.batch,
+                                rng.k0, rng.k1);
+    u = u01(r.v[q & 3]);
+  }
+  const double v = (double)vocab * pow((double)u, (double)expt);
+  const int id = (v >= 2147483647.0) ? 2147483647 : (int)v;
+  out[q] = min(id, vocab - 1);
+}
+
+__global__ void init_model_kernel(int64_t n, int dim, Rng rng, float *__restrict__ B) {
+  const int64_t blk = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t e = blk * 4;
+  if (e >= n) return;
+  PhiloxOut r = philox4x32_10((uint32_t)blk, (uint32_t)((uint64_t)blk >> 32), kStreamInit, 0u,
+                              rng.k0, rng.k1);
+  const float fd = (float)dim;
+#pragma unroll
+  for (int k = 0; k < 4; k++)
+    if (e + k < n) B[e + k] = __fdiv_rn(__fadd_rn(u01(r.v[k]), -0.5f), fd);
+}
+
+}  // namespace w2v
+
+// ---------------------------------------------------------------------------
+// Context
+// ---------------------------------------------------------------------------
+struct w2v_ctx {
+  w2v_opts o;
+  int ncols;
+  int device;
+  int64_t max_pairs;
+  float expt, salpha;
+  int64_t first_pos;
+  // device
+  int *tokens, *words, *lb, *ub, *cnt, *off, *counts;
+  int *ctx_in, *ctx_out, *wa;
+  uint32_t *key_in, *key_out;
+  float *retvals;  // [0] positive, [1] negative
+  void *cub_tmp;
+  size_t cub_tmp_bytes;
+  // pinned host
+  int *counts_host;
+  float *retvals_host;
+  // results of the latest wordmats
+  int64_t npairs;
+  int ngroups;
+  // phase timers (off by default): events at the phase boundaries of the batch
+  // in flight, harvested once the stream is known to have passed them
+  int timing_on;
+  cudaEvent_t ev[5];
+  int ev_pending;       // 0 none, 1 train batch, 2 eval batch
+  cudaStream_t ev_stream;
+  w2v_timing acc;
+};
+
+#define W2V_CHECK(call)                    \
+  do {                                     \
+    cudaError_t e_ = (call);               \
+    if (e_ != cudaSuccess) return (int)e_; \
+  } while (0)
+
+static w2v::Rng make_rng(const w2v_opts &o, uint64_t batch_id) {
+  w2v::Rng r;
+  r.k0 = (uint32_t)o.seed;
+  r.k1 = (uint32_t)(o.seed >> 32);
+  r.batch = (uint32_t)batch_id;
+  return r;
+}
+
+static void mark(w2v_ctx *c, int k, cudaStream_t stream) {
+  if (c->timing_on) cudaEventRecord(c->ev[k], stream);
+}
+
+// Adds the phase durations of the batch whose events are pending.  Only called
+// when the stream has already been synchronised past ev[4].
+static void harvest(w2v_ctx *c) {
+  if (!c->ev_pending) return;
+  float ms[4] = {0, 0, 0, 0};
+  bool ok = true;
+  for (int k = 0; k < 4; k++) ok = ok && cudaEventElapsedTime(&ms[k], c->ev[k], c->ev[k + 1]) == cudaSuccess;
+  if (ok) {
+    c->acc.prep_ms += ms[0];
+    c->acc.permute_ms += ms[1];
+    if (c->ev_pending == 1) {
+      c->acc.pos_ms += ms[2];
+      c->acc.neg_ms += ms[3];
+      c->acc.train_batches += 1;
+    } else {
+      c->acc.evalpos_ms += ms[2];
+      c->acc.evalneg_ms += ms[3];
+      c->acc.eval_batches += 1;
+    }
+  } else {
+    cudaGetLastError();
+  }
+  c->ev_pending = 0;
+}
+
+extern "C" {
+
+int w2v_set_timing(w2v_ctx *c, int on) {
+  if (!c) return 1;
+  if (on && !c->ev[0]) {
+    for (int k = 0; k < 5; k++) W2V_CHECK(cudaEventCreate(&c->ev[k]));
+  }
+  c->timing_on = on ? 1 : 0;
+  c->ev_pending = 0;
+  memset(&c->acc, 0, sizeof(c->acc));
+  return 0;
+}
+
+int w2v_get_timing(w2v_ctx *c, w2v_timing *out) {
+  if (!c || !out) return 1;
+  if (c->ev_pending) {
+    W2V_CHECK(cudaStreamSynchronize(c->ev_stream));
+    harvest(c);
+  }
+  *out = c->acc;
+  return 0;
+}
+
+void w2v_default_opts(w2v_opts *o) {
+  memset(o, 0, sizeof(*o));
+  o->dim = 256;
+  o->nskip = 5;
+  o->nneg = 5;
+  o->nreuse = 5;
+  o->vocabSize = 100000;
+  o->wexpt = 0.75f;
+  o->wsample = 1e-4f;
+  o->lrate = 1.0f;
+  o->texp = 0.5f;
+  o->vexp = 0.5f;
+  o->iflip = 0;
+  o->eqPosNeg = 0;
+  o->seed = 0;
+}
+
+void w2v_destroy(w2v_ctx *c) {
+  if (!c) return;
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(c->device);
+  cudaFree(c->tokens); cudaFree(c->words); cudaFree(c->lb); cudaFree(c->ub); cudaFree(c->cnt);
+  cudaFree(c->off); cudaFree(c->counts); cudaFree(c->ctx_in); cudaFree(c->ctx_out);
+  cudaFree(c->wa); cudaFree(c->key_in); cudaFree(c->key_out); cudaFree(c->retvals);
+  cudaFree(c->cub_tmp);
+  cudaFreeHost(c->counts_host); cudaFreeHost(c->retvals_host);
+  for (int k = 0; k < 5; k++) if (c->ev[k]) cudaEventDestroy(c->ev[k]);
+  cudaSetDevice(prev);
+  delete c;
+}
+
+int w2v_create(const w2v_opts *opts, int ncols, w2v_ctx **out) {
+  if (!opts || !out || ncols <= 0) return 1;
+  const w2v_opts &o = *opts;
+  if (o.dim <= 0 || o.nskip < 1 || o.nskip > 15 || o.vocabSize <= 0 || o.nreuse < 1) return 1;
+  if (!w2v::neg_shape_supported(o.nneg, o.nreuse)) {
+    printf("word2vec unsupport size combination %d %d\n", o.nneg, o.nreuse);
+    return 1;
+  }
+  w2v_ctx *c = new w2v_ctx();
+  memset(c, 0, sizeof(*c));
+  c->o = o;
+  c->ncols = ncols;
+  c->first_pos = -1;
+  c->max_pairs = (int64_t)2 * o.nskip * ncols;
+  if (c->max_pairs > 0x7fffffffLL) { delete c; return 1; }
+  // expt and salpha exactly as Word2Vec.init forms them (Word2Vec.scala:139,150)
+  c->expt = 1.0f / (1.0f - o.wexpt);
+  c->salpha = o.wsample * (float)log((double)o.vocabSize);
+  cudaError_t e = cudaGetDevice(&c->device);
+  const size_t n4 = sizeof(int) * (size_t)ncols, p4 = sizeof(int) * (size_t)c->max_pairs;
+  const int64_t max_groups = c->max_pairs / o.nreuse;
+  size_t scan_bytes = 0, sort_bytes = 0;
+  if (e == cudaSuccess) e = cudaMalloc(&c->tokens, 2 * n4);
+  if (e == cudaSuccess) e = cudaMalloc(&c->words, n4);
+  if (e == cudaSuccess) e = cudaMalloc(&c->lb, n4);
+  if (e == cudaSuccess) e = cudaMalloc(&c->ub, n4);
+  if (e == cudaSuccess) e = cudaMalloc(&c->cnt, n4);
+  if (e == cudaSuccess) e = cudaMalloc(&c->off, n4);
+  if (e == cudaSuccess) e = cudaMalloc(&c->counts, 256);
+  if (e == cudaSuccess) e = cudaMalloc(&c->ctx_in, p4);
+  if (e == cudaSuccess) e = cudaMalloc(&c->ctx_out, p4);
+  if (e == cudaSuccess) e = cudaMalloc(&c->key_in, p4);
+  if (e == cudaSuccess) e = cudaMalloc(&c->key_out, p4);
+  if (e == cudaSuccess) e = cudaMalloc(&c->wa, sizeof(int) * (size_t)(max_groups + 1) * o.nneg);
+  if (e == cudaSuccess) e = cudaMalloc(&c->retvals, 256);
+  if (e == cudaSuccess) e = cudaMallocHost(&c->counts_host, 256);
+  if (e == cudaSuccess) e = cudaMallocHost(&c->retvals_host, 256);
+  if (e == cudaSuccess)
+    e = cub::DeviceScan::ExclusiveSum(nullptr, scan_bytes, c->cnt, c->off, ncols);
+  if (e == cudaSuccess)
+    e = cub::DeviceRadixSort::SortPairsDescending(nullptr, sort_bytes, c->key_in, c->key_out,
+                                                  c->ctx_in, c->ctx_out, (int)c->max_pairs, 0, 24);
+  c->cub_tmp_bytes = (scan_bytes > sort_bytes ? scan_bytes : sort_bytes) + 256;
+  if (e == cudaSuccess) e = cudaMalloc(&c->cub_tmp, c->cub_tmp_bytes);
+  if (e != cudaSuccess) {
+    w2v_destroy(c);
+    return (int)e;
+  }
+  *out = c;
+  return 0;
+}
+
+int w2v_init_model(const w2v_opts *o, float *A, float *B, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const int64_t n = (int64_t)o->dim * o->vocabSize;
+  W2V_CHECK(cudaMemsetAsync(A, 0, sizeof(float) * (size_t)n, stream));
+  const int64_t blocks4 = (n + 3) / 4;
+  const int threads = 256;
+  w2v::init_model_kernel<<<(unsigned)((blocks4 + threads - 1) / threads), threads, 0, stream>>>(
+      n, o->dim, make_rng(*o, 0), B);
+  w2v::count_launch(1);
+  return (int)cudaGetLastError();
+}
+
+int w2v_wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64_t batch_id,
+                 void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const w2v_opts &o = c->o;
+  const int n = c->ncols;
+  const int threads = 256, blocks = (n + threads - 1) / threads;
+  const w2v::Rng rng = make_rng(o, batch_id);
+  const float *us = u ? u->sample : nullptr, *uw = u ? u->window : nullptr;
+  const float *up = u ? u->permute : nullptr, *un = u ? u->negs : nullptr;
+
+  // the events of the previous batch are about to be re-recorded: read them
+  // first (waits for that batch to finish; only in timing mode)
+  if (c->timing_on && c->ev_pending) {
+    if (cudaEventSynchronize(c->ev[4]) == cudaSuccess) harvest(c);
+    c->ev_pending = 0;
+  }
+  mark(c, 0, stream);
+  w2v::words_bounds_kernel<<<blocks, threads, 0, stream>>>(
+      n, tokens, o.iflip ? 1 : 0, o.vocabSize, o.nskip, c->salpha, us, uw, rng, c->words, c->lb, c->ub);
+  w2v::count_pairs_kernel<<<blocks, threads, 0, stream>>>(n, c->words, c->lb, c->ub, c->cnt);
+  size_t tmp = c->cub_tmp_bytes;
+  W2V_CHECK(cub::DeviceScan::ExclusiveSum(c->cub_tmp, tmp, c->cnt, c->off, n, stream));
+  w2v::totals_kernel<<<1, 32, 0, stream>>>(n, c->cnt, c->off, o.nreuse, c->counts);
+  W2V_CHECK(cudaMemcpyAsync(c->counts_host, c->counts, 2 * sizeof(int), cudaMemcpyDeviceToHost, stream));
+  w2v::fill_pairs_kernel<<<blocks, threads, 0, stream>>>(n, o.nskip, c->words, c->lb, c->ub, c->off,
+                                                        up, rng, c->ctx_in, c->key_in);
+  w2v::count_launch(4);
+  W2V_CHECK(cudaGetLastError());
+  mark(c, 1, stream);
+  W2V_CHECK(cudaStreamSynchronize(stream));
+  c->npairs = c->counts_host[0];
+  c->ngroups = c->counts_host[1];
+  if (c->npairs > 0) {
+    tmp = c->cub_tmp_bytes;
+    W2V_CHECK(cub::DeviceRadixSort::SortPairsDescending(c->cub_tmp, tmp, c->key_in, c->key_out,
+                                                        c->ctx_in, c->ctx_out, (int)c->npairs, 0,
+                                                        24, stream));
+  }
+  const int64_t nn = (int64_t)c->ngroups * o.nneg;
+  if (nn > 0) {
+    w2v::negative_ids_kernel<<<(unsigned)((nn + threads - 1) / threads), threads, 0, stream>>>(
+        nn, un, rng, o.vocabSize, c->expt, c->wa);
+    w2v::count_launch(1);
+  }
+  mark(c, 2, stream);
+  return (int)cudaGetLastError();
+}
+
+int w2v_buffers(w2v_ctx *c, w2v_buffers_t *out) {
+  if (!c || !out) return 1;
+  out->words = c->words; out->lb = c->lb; out->ub = c->ub;
+  out->contexts = c->ctx_in;
+  out->WB = c->ctx_out;
+  out->WA = c->wa;
+  out->npairs = c->npairs;
+  out->ngroups = c->ngroups;
+  return 0;
+}
+
+int w2v_dobatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, float *A, float *B,
+                int64_t pos, uint64_t batch_id, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const w2v_opts &o = c->o;
+  // learning-rate schedule of Word2Vec.dobatch (Word2Vec.scala:170-177)
+  if (c->first_pos < 0) c->first_pos = pos;
+  const float nsteps = (float)pos / (float)c->first_pos;
+  const float lrpos = o.lrate * (float)pow((double)nsteps, -(double)o.texp);
+  const float lrneg = o.eqPosNeg ? lrpos : lrpos / (float)o.nneg;
+  int err = w2v_wordmats(c, tokens, u, batch_id, stream);
+  if (err) return err;
+  err = w2v::pos_update_async(o.dim, c->ncols, nullptr, o.nskip, c->words, c->lb, c->ub, A, B,
+                              lrpos, o.vexp, stream);
+  if (err) return err;
+  mark(c, 3, stream);
+  err = w2v::neg_update_async(o.dim, c->ngroups, nullptr, 0x7fffffff, o.nneg, o.nreuse, c->wa,
+                              c->ctx_out, A, B, lrneg, o.vexp, stream);
+  mark(c, 4, stream);
+  if (c->timing_on) {
+    c->ev_pending = 1;
+    c->ev_stream = stream;
+    c->acc.pairs += c->npairs;
+    c->acc.groups += c->ngroups;
+  }
+  return err;
+}
+
+int w2v_evalbatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, const float *A,
+                  const float *B, uint64_t batch_id, double *score_host, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const w2v_opts &o = c->o;
+  int err = w2v_wordmats(c, tokens, u, batch_id, stream);
+  if (err) return err;
+  W2V_CHECK(cudaMemsetAsync(c->retvals, 0, 2 * sizeof(float), stream));
+  err = w2v::pos_eval_async(o.dim, c->ncols, nullptr, o.nskip, c->words, c->lb, c->ub, A, B,
+                            c->retvals, stream);
+  if (err) return err;
+  mark(c, 3, stream);
+  err = w2v::neg_eval_async(o.dim, c->ngroups, nullptr, o.nneg, o.nreuse, c->wa, c->ctx_out, A, B,
+                            c->retvals + 1, stream);
+  if (err) return err;
+  mark(c, 4, stream);
+  if (c->timing_on) {
+    c->ev_pending = 2;
+    c->ev_stream = stream;
+    c->acc.eval_pairs += c->npairs;
+    c->acc.eval_groups += c->ngroups;
+  }
+  W2V_CHECK(cudaMemcpyAsync(c->retvals_host, c->retvals, 2 * sizeof(float), cudaMemcpyDeviceToHost, stream));
+  W2V_CHECK(cudaStreamSynchronize(stream));
+  const double epos = c->retvals_host[0], eneg = c->retvals_host[1];
+  const double denom = (double)c->ngroups * o.nreuse;
+  // (epos + eneg / nneg) / goodwords.length  (Word2Vec.scala:209)
+  *score_host = denom > 0 ? (epos + eneg / (o.eqPosNeg ? 1 : o.nneg)) / denom : 0.0;
+  return 0;
+}
+
+int w2v_dobatch_host(w2v_ctx *c, const int *tokens_host, float *A, float *B, int64_t pos,
+                     uint64_t batch_id, int64_t *npairs_host, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  W2V_CHECK(cudaMemcpyAsync(c->tokens, tokens_host, 2 * sizeof(int) * (size_t)c->ncols,
+                            cudaMemcpyHostToDevice, stream));
+  int err = w2v_dobatch(c, c->tokens, nullptr, A, B, pos, batch_id, stream);
+  if (err) return err;
+  W2V_CHECK(cudaStreamSynchronize(stream));
+  if (npairs_host) *npairs_host = c->npairs;
+  return (int)cudaGetLastError();
+}
+
+int w2v_evalbatch_host(w2v_ctx *c, const int *tokens_host, const float *A, const float *B,
+                       uint64_t batch_id, double *score_host, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  W2V_CHECK(cudaMemcpyAsync(c->tokens, tokens_host, 2 * sizeof(int) * (size_t)c->ncols,
+                            cudaMemcpyHostToDevice, stream));
+  return w2v_evalbatch(c, c->tokens, nullptr, A, B, batch_id, score_host, stream);
+}
+
+}  // extern "C"

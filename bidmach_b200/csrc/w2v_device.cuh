@@ -1,0 +1,169 @@
+// Device-side building blocks shared by the Word2Vec SGNS kernels (sm_100a).
+//
+// A model matrix is column-major dim x vocab fp32, so word `w` is the
+// contiguous row `[w*dim, (w+1)*dim)`.  A warp owns a row at a time: lane `l`
+// holds the 16-byte vectors `l, l+32, l+64, ...` of the row, which makes every
+// row load and every row update a fully coalesced 128-bit access.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace w2v {
+
+constexpr unsigned kFullMask = 0xffffffffu;
+
+// Logistic function with the reference's guards: above 16 it is exactly 1,
+// below -16 exactly 0 (jni/src/DNN127.cu:128-135, BIDMach_CPUMACH.c:48-55).
+// expf and the division are the IEEE-accurate versions (no fast-math), so the
+// result tracks the CPU path to a few ulp.
+__device__ __forceinline__ float sigmoid_guard(float x) {
+  if (x > 16.0f) return 1.0f;
+  if (x < -16.0f) return 0.0f;
+  float e = expf(x);
+  return e / (1.0f + e);
+}
+
+// (1 + id)^vexp, the per-word learning-rate scale (BIDMach_CPUMACH.c:33,42;
+// jni/src/DNN127.cu:145,149 forms the same value from the row offset).
+__device__ __forceinline__ float freq_scale(int id, float vexp) {
+  if (vexp == 0.0f) return 1.0f;
+  return powf((float)(1 + id), vexp);
+}
+
+// 128-bit fire-and-forget atomic add into global memory (one L2 reduction per
+// 16 bytes instead of four scalar atomics).
+__device__ __forceinline__ void red_add_v4(float *addr, float4 v) {
+  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr),
+               "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(kFullMask, v, off);
+  return v;
+}
+
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(kFullMask, v, off);
+  return v;
+}
+
+// Row held in registers: NR vectors of 4 floats per lane.
+template <int NR>
+struct Row {
+  float4 v[NR];
+};
+
+template <int NR>
+__device__ __forceinline__ void row_zero(Row<NR> &r) {
+#pragma unroll
+  for (int q = 0; q < NR; q++) r.v[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+// Load row `w` (w >= 0) of a dim x vocab matrix.  nvec = dim / 4.
+template <int NR>
+__device__ __forceinline__ void row_load(Row<NR> &r, const float *M, int64_t w, int dim, int nvec,
+                                         int lane) {
+  const float4 *p = reinterpret_cast<const float4 *>(M + w * (int64_t)dim);
+#pragma unroll
+  for (int q = 0; q < NR; q++) {
+    int idx = lane + 32 * q;
+    r.v[q] = (idx < nvec) ? p[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+template <int NR>
+__device__ __forceinline__ float row_dot_partial(const Row<NR> &a, const Row<NR> &b) {
+  float s = 0.f;
+#pragma unroll
+  for (int q = 0; q < NR; q++) {
+    s = fmaf(a.v[q].x, b.v[q].x, s);
+    s = fmaf(a.v[q].y, b.v[q].y, s);
+    s = fmaf(a.v[q].z, b.v[q].z, s);
+    s = fmaf(a.v[q].w, b.v[q].w, s);
+  }
+  return s;
+}
+
+// acc += c * x
+template <int NR>
+__device__ __forceinline__ void row_axpy(Row<NR> &acc, float c, const Row<NR> &x) {
+#pragma unroll
+  for (int q = 0; q < NR; q++) {
+    acc.v[q].x = fmaf(c, x.v[q].x, acc.v[q].x);
+    acc.v[q].y = fmaf(c, x.v[q].y, acc.v[q].y);
+    acc.v[q].z = fmaf(c, x.v[q].z, acc.v[q].z);
+    acc.v[q].w = fmaf(c, x.v[q].w, acc.v[q].w);
+  }
+}
+
+// M[w] += r   (atomic, 128 bits at a time)
+template <int NR>
+__device__ __forceinline__ void row_red(float *M, int64_t w, int dim, int nvec, int lane,
+                                        const Row<NR> &r) {
+  float *p = M + w * (int64_t)dim;
+#pragma unroll
+  for (int q = 0; q < NR; q++) {
+    int idx = lane + 32 * q;
+    if (idx < nvec) red_add_v4(p + 4 * idx, r.v[q]);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Many-value warp reduction.  Each lane brings M partial sums; five exchange
+// steps later the M totals are spread over the lanes (FIN per lane) instead of
+// every lane holding every total, which takes about M shuffles rather than
+// 5*M, and lets the sigmoid of each total be evaluated by one lane only.
+// Total `idx` ends up in slot slot_of(idx) of lane lane_of(idx).
+// ---------------------------------------------------------------------------
+template <int M>
+struct Spread {
+  static constexpr int h1 = (M + 1) / 2, h2 = (h1 + 1) / 2, h3 = (h2 + 1) / 2, h4 = (h3 + 1) / 2,
+                       h5 = (h4 + 1) / 2;
+  static constexpr int FIN = h5;
+
+  static __host__ __device__ constexpr int lane_of(int idx) {
+    int lane = 0;
+    const int hs[5] = {h1, h2, h3, h4, h5};
+    for (int s = 0; s < 5; s++) {
+      if (idx >= hs[s]) {
+        lane |= (16 >> s);
+        idx -= hs[s];
+      }
+    }
+    return lane;
+  }
+  static __host__ __device__ constexpr int slot_of(int idx) {
+    const int hs[5] = {h1, h2, h3, h4, h5};
+    for (int s = 0; s < 5; s++)
+      if (idx >= hs[s]) idx -= hs[s];
+    return idx;
+  }
+
+  template <int CUR, int OFF>
+  static __device__ __forceinline__ void step(float (&v)[M], int lane) {
+    constexpr int H = (CUR + 1) / 2;
+    const bool up = (lane & OFF) != 0;
+#pragma unroll
+    for (int i = 0; i < H; i++) {
+      float lo = v[i];
+      float hi = (i + H < CUR) ? v[i + H] : 0.f;
+      float send = up ? lo : hi;
+      float keep = up ? hi : lo;
+      v[i] = keep + __shfl_xor_sync(kFullMask, send, OFF);
+    }
+  }
+
+  static __device__ __forceinline__ void reduce(float (&v)[M], int lane) {
+    step<M, 16>(v, lane);
+    step<h1, 8>(v, lane);
+    step<h2, 4>(v, lane);
+    step<h3, 2>(v, lane);
+    step<h4, 1>(v, lane);
+  }
+};
+
+}  // namespace w2v

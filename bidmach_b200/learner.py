@@ -1,0 +1,156 @@
+"""Minibatch schedule that drives the Word2Vec model: the part of
+``BIDMach.Learner`` / ``ParLearner`` (src/main/scala/BIDMach/Learner.scala)
+this path depends on.  Not a general training framework: only the loop, the
+evaluation cadence and the multi-GPU exchange are mirrored.
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+
+import numpy as np
+
+from .word2vec import Word2Vec
+
+
+class MatSource:
+    """In-memory data source: an int32 ``[ntokens, 2]`` array (word id, sentence
+    id) handed out in minibatches of ``batchSize`` tokens, the last one short
+    (datasources/MatSource.scala:78-91).  ``stride``/``offset`` give every rank
+    of a data-parallel job its own minibatches, dealt round-robin as ParLearner
+    deals them to its per-GPU threads (Learner.scala:638-651)."""
+
+    def __init__(self, tokens: np.ndarray, batchSize: int, offset: int = 0, stride: int = 1):
+        self.tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        self.batchSize = int(batchSize)
+        self.offset, self.stride = offset, stride
+        self.reset()
+
+    def reset(self):
+        self.k = self.offset
+
+    @property
+    def nbatches(self) -> int:
+        return max(0, math.ceil((self._usable() - self.offset) / self.stride))
+
+    def _usable(self) -> int:
+        total = math.ceil(self.tokens.shape[0] / self.batchSize)
+        # with several ranks every rank must see the same number of minibatches,
+        # so the ragged tail of the deal is dropped
+        return total if self.stride == 1 else (total // self.stride) * self.stride
+
+    def hasNext(self) -> bool:
+        return self.k < self._usable()
+
+    def next(self):
+        lo = self.k * self.batchSize
+        self.k += self.stride
+        return [self.tokens[lo: lo + self.batchSize]]
+
+    def progress(self) -> float:
+        return min(1.0, self.k * self.batchSize / max(1, self.tokens.shape[0]))
+
+
+@dataclasses.dataclass
+class LearnerOpts:
+    """The fields of Learner.Opts / ParLearner.Opts this path reads
+    (Learner.scala:1062-1081, 1152-1158), with the reference's defaults."""
+    npasses: int = 2
+    evalStep: int = 11
+    updateAll: bool = False
+    syncStep: int = 2
+
+
+def _scala_mod(a: int, b: int) -> int:
+    return int(math.fmod(a, b))
+
+
+class Learner:
+    """Single-GPU loop, ``Learner.nextPass`` (Learner.scala:173-252): minibatch
+    ``istep`` only scores when ``(istep - 1) % evalStep == 0`` or it is the last
+    one of the pass (and not the first); every other minibatch trains.  ``here``
+    advances by batchSize per minibatch and drives the learning-rate decay."""
+
+    def __init__(self, datasource: MatSource, model: Word2Vec, opts: LearnerOpts | None = None):
+        self.datasource, self.model = datasource, model
+        self.opts = opts or LearnerOpts()
+        self.reslist: list[float] = []
+        self.samplist: list[int] = []
+        self.here = 0
+        self.ipass = 0
+        self.nsamps = 0
+
+    def init(self):
+        self.model.init(self.datasource.batchSize)
+
+    def _after_train_step(self, istep_global: int):
+        pass
+
+    def train(self, do_init: bool = True):
+        if do_init:
+            self.init()
+        self.here, self.ipass, self.nsamps = 0, 0, 0
+        self.reslist, self.samplist = [], []
+        while self.ipass < self.opts.npasses:
+            self.nextPass()
+        return self
+
+    def nextPass(self):
+        ds, o = self.datasource, self.opts
+        ds.reset()
+        istep = 0
+        while ds.hasNext():
+            mats = ds.next()
+            self.nsamps += mats[0].shape[0]
+            self.here += ds.batchSize
+            if _scala_mod(istep - 1, o.evalStep) == 0 or (istep > 0 and not ds.hasNext()):
+                if o.updateAll:
+                    self.model.dobatchg(mats, self.ipass, self.here)
+                    self._after_train_step(istep)
+                self.reslist.append(self.model.evalbatchg(mats, self.ipass, self.here))
+                self.samplist.append(self.here)
+            else:
+                self.model.dobatchg(mats, self.ipass, self.here)
+                self._after_train_step(istep)
+            istep += 1
+        self.ipass += 1
+
+    def predict(self, datasource: MatSource) -> list[float]:
+        """Learner.predict (Learner.scala:322-391): score every full minibatch."""
+        datasource.reset()
+        out = []
+        while datasource.hasNext():
+            mats = datasource.next()
+            if mats[0].shape[0] == self.model.ncols:
+                out.append(self.model.evalbatchg(mats, 0, 0))
+        return out
+
+
+class ParLearner(Learner):
+    """Data-parallel loop: one process per GPU, each with a full replica of both
+    matrices and its own minibatches; every ``syncStep`` training minibatches the
+    replicas are averaged (ParLearner.syncmodels, Learner.scala:655, here one
+    all-reduce per matrix, see Word2Vec.mergeModelFn).  Requires an initialised
+    ``torch.distributed`` process group; rank 0's initial model is broadcast so
+    that all replicas start equal (the reference's first full sync,
+    Learner.scala:525)."""
+
+    def __init__(self, datasource: MatSource, model: Word2Vec, opts: LearnerOpts | None = None,
+                 group=None):
+        super().__init__(datasource, model, opts)
+        self.group = group
+        self._since_sync = 0
+
+    def init(self):
+        import torch.distributed as dist
+        super().init()
+        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            for m in self.model.modelmats:
+                dist.broadcast(m, src=dist.get_global_rank(self.group, 0) if self.group else 0,
+                               group=self.group)
+
+    def _after_train_step(self, istep_global: int):
+        self._since_sync += 1
+        if self._since_sync >= self.opts.syncStep:
+            self.model.mergeModelFn(self.group)
+            self._since_sync = 0

@@ -1,0 +1,278 @@
+"""Host-side mirror of ``BIDMach.networks.Word2Vec`` for the skip-gram
+negative-sampling path (src/main/scala/BIDMach/networks/Word2Vec.scala).
+
+The reference's host code is Scala; no JVM toolchain exists where this was
+built, so the same interface -- option names and defaults, ``init`` /
+``dobatch`` / ``evalbatch`` / ``wordMats`` / ``procPositives`` /
+``procNegatives`` / ``evalPositives`` / ``evalNegatives`` / ``mergeModelFn`` --
+is provided in Python above the C-ABI library.  PyTorch only supplies device
+memory, streams and the process group; every computation happens in the CUDA
+library, and nothing here works without it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import dataclasses
+
+import numpy as np
+import torch
+
+from . import _lib
+from .cumach import CUMACH, cuda_error_string
+
+
+@dataclasses.dataclass
+class Opts:
+    """``Word2Vec.Opts`` (Word2Vec.scala:574-591) with the inherited fields this
+    path reads: ``dim`` (models/Model.scala:537), ``lrate``/``texp``
+    (updaters/Grad.scala:242-243), ``vexp`` (updaters/ADAGrad.scala:158).
+    Defaults are the reference's."""
+    nskip: int = 5
+    nneg: int = 5
+    nreuse: int = 5
+    vocabSize: int = 100000
+    wexpt: float = 0.75
+    wsample: float = 1e-4
+    headlen: int = 10000
+    iflip: bool = False
+    eqPosNeg: bool = False
+    maxArraySize: int = 2047 * 1024 * 1024
+    nHeadTerms: int = 0
+    nSlices: int = 1
+    iSlice: int = 0
+    dualMode: bool = False
+    doHead: int = 1
+    dim: int = 256
+    lrate: float = 1.0
+    texp: float = 0.5
+    vexp: float = 0.5
+    useGPU: bool = True
+    seed: int = 0
+
+    def to_c(self) -> _lib.W2VOpts:
+        return _lib.W2VOpts(self.dim, self.nskip, self.nneg, self.nreuse, self.vocabSize,
+                            self.wexpt, self.wsample, self.lrate, self.texp, self.vexp,
+                            int(self.iflip), int(self.eqPosNeg), self.seed)
+
+
+class _DevView:
+    """A device buffer owned by the library, exposed through the CUDA array interface."""
+
+    def __init__(self, ptr: int, n: int, typestr: str = "<i4"):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False),
+                                         "version": 2}
+
+
+def _view_i32(ptr: int, n: int, device) -> torch.Tensor:
+    if n <= 0 or not ptr:
+        return torch.empty(0, dtype=torch.int32, device=device)
+    return torch.as_tensor(_DevView(ptr, n), device=device)
+
+
+def _check(err: int, what: str):
+    if err != 0:
+        raise RuntimeError(f"{what} error " + cuda_error_string(err))
+
+
+class Word2Vec:
+    """SGNS model.  ``modelmats[0]`` is the context/embedding matrix (random
+    init) and ``modelmats[1]`` the centre/negative matrix (zeros), both stored
+    as ``[vocabSize, dim]`` fp32 CUDA tensors, i.e. the reference's column-major
+    ``dim x vocabSize`` (Word2Vec.scala:113-117)."""
+
+    Opts = Opts
+
+    def __init__(self, opts: Opts | None = None, device=None):
+        self.opts = opts or Opts()
+        if not self.opts.useGPU:
+            raise RuntimeError("this build has no CPU path: useGPU must stay true")
+        if self.opts.nSlices != 1 or self.opts.dualMode or self.opts.nHeadTerms != 0:
+            raise NotImplementedError("model slicing (nSlices/dualMode/nHeadTerms) is a CPU-only "
+                                      "feature of the reference and is not part of this path")
+        self.device = torch.device(device if device is not None else "cuda")
+        self.modelmats: list[torch.Tensor] = []
+        self.ncols = 0
+        self._ctx = None
+        self._copts = None
+        self._batches = 0
+
+    # -- life cycle ---------------------------------------------------------
+    def init(self, ncols: int, refresh: bool = True):
+        """Word2Vec.init (Word2Vec.scala:100-165): allocate both matrices and the
+        per-minibatch work buffers for minibatches of ``ncols`` tokens."""
+        o = self.opts
+        lib = _lib.load()
+        self.ncols = int(ncols)
+        self._copts = o.to_c()
+        with torch.cuda.device(self.device):
+            if refresh or not self.modelmats:
+                mm0 = torch.empty(o.vocabSize, o.dim, dtype=torch.float32, device=self.device)
+                mm1 = torch.empty_like(mm0)
+                _check(lib.w2v_init_model(C.byref(self._copts), mm1.data_ptr(), mm0.data_ptr(),
+                                          self._stream()), "w2v_init_model")
+                self.modelmats = [mm0, mm1]
+            ctx = C.c_void_p()
+            err = lib.w2v_create(C.byref(self._copts), self.ncols, C.byref(ctx))
+            if err:
+                raise RuntimeError(f"w2v_create failed ({err}): unsupported options or out of memory")
+            self._free_ctx()
+            self._ctx = ctx
+        return self
+
+    def _free_ctx(self):
+        if self._ctx is not None:
+            _lib.load().w2v_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self._free_ctx()
+        except Exception:
+            pass
+
+    def _stream(self) -> int:
+        return int(torch.cuda.current_stream(self.device).cuda_stream)
+
+    @staticmethod
+    def _uniforms(u):
+        if u is None:
+            return None
+        s = _lib.W2VUniforms(*(int(u[k].data_ptr()) if u.get(k) is not None else 0
+                               for k in ("sample", "window", "permute", "negs")))
+        return C.byref(s)
+
+    # -- minibatch entry points --------------------------------------------
+    def dobatch(self, gmats, ipass: int, pos: int, uniforms=None):
+        """Word2Vec.dobatch (Word2Vec.scala:167-190).  ``gmats[0]`` is the device
+        minibatch, int32 ``[ncols, 2]`` (word id, sentence id).  A minibatch of
+        another length is skipped, as in the reference (:169)."""
+        toks = gmats[0]
+        if toks.shape[0] != self.ncols:
+            return
+        self._batches += 1
+        with torch.cuda.device(self.device):
+            _check(_lib.load().w2v_dobatch(self._ctx, toks.data_ptr(), self._uniforms(uniforms),
+                                           self.modelmats[1].data_ptr(), self.modelmats[0].data_ptr(),
+                                           int(pos), self._batches, self._stream()), "w2v_dobatch")
+
+    def evalbatch(self, gmats, ipass: int, pos: int, uniforms=None) -> float:
+        """Word2Vec.evalbatch (Word2Vec.scala:192-212): mean log-likelihood score."""
+        toks = gmats[0]
+        if toks.shape[0] != self.ncols:
+            return 0.0
+        self._batches += 1
+        score = C.c_double(0.0)
+        with torch.cuda.device(self.device):
+            _check(_lib.load().w2v_evalbatch(self._ctx, toks.data_ptr(), self._uniforms(uniforms),
+                                             self.modelmats[1].data_ptr(), self.modelmats[0].data_ptr(),
+                                             self._batches, C.byref(score), self._stream()),
+                   "w2v_evalbatch")
+        return score.value
+
+    def dobatchg(self, mats, ipass: int, pos: int) -> int:
+        """Model.dobatchg (models/Model.scala:350-354): the minibatch is still in
+        host memory (numpy int32 ``[ncols, 2]`` or a CPU tensor); it is copied to
+        the device inside the call.  Returns the number of positive pairs."""
+        host = _host_i32(mats[0])
+        if host.shape[0] != self.ncols:
+            return 0
+        self._batches += 1
+        npairs = C.c_int64(0)
+        with torch.cuda.device(self.device):
+            _check(_lib.load().w2v_dobatch_host(self._ctx, host.ctypes.data,
+                                                self.modelmats[1].data_ptr(), self.modelmats[0].data_ptr(),
+                                                int(pos), self._batches, C.byref(npairs),
+                                                self._stream()), "w2v_dobatch_host")
+        return npairs.value
+
+    def evalbatchg(self, mats, ipass: int, pos: int) -> float:
+        """Model.evalbatchg (models/Model.scala:356-365) for a host minibatch."""
+        host = _host_i32(mats[0])
+        if host.shape[0] != self.ncols:
+            return 0.0
+        self._batches += 1
+        score = C.c_double(0.0)
+        with torch.cuda.device(self.device):
+            _check(_lib.load().w2v_evalbatch_host(self._ctx, host.ctypes.data,
+                                                  self.modelmats[1].data_ptr(), self.modelmats[0].data_ptr(),
+                                                  self._batches, C.byref(score), self._stream()),
+                   "w2v_evalbatch_host")
+        return score.value
+
+    # -- the pieces, one reference method each ------------------------------
+    def wordMats(self, gmats, ipass: int = 0, pos: int = 0, uniforms=None, batch_id: int = 0):
+        """Word2Vec.wordMats (Word2Vec.scala:214-278).  Returns
+        ``(words, lb, ub, trandwords, contextwords)`` as device tensors that alias
+        the library's work buffers (valid until the next minibatch call):
+        trandwords is ``[ngroups, nneg]`` and contextwords ``[ngroups, nreuse]``."""
+        toks = gmats[0]
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            _check(lib.w2v_wordmats(self._ctx, toks.data_ptr(), self._uniforms(uniforms), batch_id,
+                                    self._stream()), "w2v_wordmats")
+        b = _lib.W2VBuffers()
+        lib.w2v_buffers(self._ctx, C.byref(b))
+        o, d = self.opts, self.device
+        words = _view_i32(b.words, self.ncols, d)
+        lb = _view_i32(b.lb, self.ncols, d)
+        ub = _view_i32(b.ub, self.ncols, d)
+        wa = _view_i32(b.WA, b.ngroups * o.nneg, d).view(-1, o.nneg)
+        wb = _view_i32(b.WB, b.ngroups * o.nreuse, d).view(-1, o.nreuse)
+        self.last_contexts = _view_i32(b.contexts, b.npairs, d)
+        return words, lb, ub, wa, wb
+
+    def procPositives(self, nskip, words, lbound, ubound, model1, model2, lrate, vexp):
+        """Word2Vec.procPositives (Word2Vec.scala:366-383), GPU branch."""
+        err = CUMACH.word2vecPos(model1.shape[1], words.numel(), nskip, words, lbound, ubound,
+                                 model1, model2, lrate, vexp)
+        _check(err, "CUMACH.word2vecPos")
+
+    def procNegatives(self, nwa, nwb, wordsa, wordsb, modela, modelb, lrate, vexp):
+        """Word2Vec.procNegatives (Word2Vec.scala:385-402), GPU branch."""
+        err = CUMACH.word2vecNeg(modela.shape[1], wordsa.shape[0], nwa, nwb, wordsa, wordsb, modela,
+                                 modelb, lrate, vexp)
+        _check(err, "CUMACH.word2vecNeg")
+
+    def evalPositives(self, nskip, words, lbound, ubound, model1, model2) -> float:
+        """Word2Vec.evalPositives (Word2Vec.scala:469-489), GPU branch."""
+        ret = torch.zeros(1, dtype=torch.float32, device=model1.device)
+        err = CUMACH.word2vecEvalPos(model1.shape[1], words.numel(), nskip, words, lbound, ubound,
+                                     model1, model2, ret)
+        _check(err, "CUMACH.word2vecEvalPos")
+        return float(ret.item())
+
+    def evalNegatives(self, nwa, nwb, wordsa, wordsb, modela, modelb) -> float:
+        """Word2Vec.evalNegatives (Word2Vec.scala:503-523), GPU branch."""
+        ret = torch.zeros(1, dtype=torch.float32, device=modela.device)
+        err = CUMACH.word2vecEvalNeg(modela.shape[1], wordsa.shape[0], nwa, nwb, wordsa, wordsb,
+                                     modela, modelb, ret)
+        _check(err, "CUMACH.word2vecEvalNeg")
+        return float(ret.item())
+
+    # -- multi-GPU ------------------------------------------------------------
+    def mergeModelFn(self, group=None):
+        """Replaces Word2Vec.mergeModelFn (Word2Vec.scala:547-568), which averages a
+        frequency-ranked prefix of each matrix through host-driven peer copies:
+        here both full matrices are averaged over the process group with one
+        all-reduce each (NCCL over NVLink when the group's backend is nccl)."""
+        import torch.distributed as dist
+        if not dist.is_initialized() or dist.get_world_size(group) == 1:
+            return
+        avg = dist.ReduceOp.AVG if dist.get_backend(group) == "nccl" else None
+        for m in self.modelmats:
+            if avg is not None:
+                dist.all_reduce(m, op=avg, group=group)
+            else:
+                dist.all_reduce(m, op=dist.ReduceOp.SUM, group=group)
+                m.mul_(1.0 / dist.get_world_size(group))
+
+
+def _host_i32(x) -> np.ndarray:
+    if isinstance(x, torch.Tensor):
+        if x.is_cuda:
+            raise ValueError("dobatchg/evalbatchg take the minibatch in host memory")
+        x = x.numpy()
+    x = np.ascontiguousarray(x, dtype=np.int32)
+    if x.ndim != 2 or x.shape[1] != 2:
+        raise ValueError("minibatch must be int32 [ncols, 2] (word id, sentence id)")
+    return x

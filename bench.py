@@ -66,11 +66,18 @@ class ClockSampler:
 
     def __init__(self, gpu_index: int):
         self.rows, self.proc, self.gpu = [], None, gpu_index
+        self.t0 = self.t1 = None
+
+    def window_open(self):
+        self.t0 = time.monotonic()
+
+    def window_close(self):
+        self.t1 = time.monotonic()
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -79,7 +86,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append((time.monotonic(), [x.strip() for x in line.split(",")]))
 
     def stop(self):
         if self.proc is None:
@@ -91,7 +98,10 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        inside = [r for (t, r) in self.rows if self.t0 is None or (self.t0 <= t <= (self.t1 or t))]
+        if not inside:  # region shorter than the sampling period: take the nearest sample
+            inside = [r for (_, r) in self.rows[-1:]]
+        for r in inside:
             try:
                 sm.append(float(r[1]))
                 mx.append(float(r[2]))
@@ -257,17 +267,19 @@ def run_ours(args):
         return pos
 
     def timed(host_path, pos):
+        sampler = ClockSampler(local)
+        sampler.start()
         pos = run_steps(args.warmup, host_path, pos)
         sync_all()
         lib.w2v_set_timing(model._ctx, 0 if host_path else 1)
         launches0 = lib.w2v_launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        sampler = ClockSampler(local)
-        sampler.start()
+        sampler.window_open()
         e0.record(stream)
         pos = run_steps(args.steps, host_path, pos)
         e1.record(stream)
         sync_all()
+        sampler.window_close()
         clocks = sampler.stop()
         ms = e0.elapsed_time(e1)
         t = torch.tensor([ms], device="cuda", dtype=torch.float64)
@@ -340,12 +352,18 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=16)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=48)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sync-every", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--vocab", type=int, default=None, help="override the workload's vocabulary (profiling)")
+    ap.add_argument("--tokens", type=int, default=None, help="override tokens per minibatch (profiling)")
     args = ap.parse_args()
+    if args.vocab:
+        WORKLOAD["vocab"] = args.vocab
+    if args.tokens:
+        WORKLOAD["ntokens"] = args.tokens
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -1,0 +1,180 @@
+"""Host logic: minibatch schedule, data source dealing, corpora, Philox, and the
+multi-rank averaging over a gloo group (CPU, world size 2)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def test_eval_schedule_matches_learner_nextpass(oracle):
+    from bidmach_b200.learner import _scala_mod
+    # (istep - 1) % evalStep == 0 with Scala's truncated remainder: 1, 12, 23, ...
+    steps = [i for i in range(40) if _scala_mod(i - 1, 11) == 0]
+    assert steps == [1, 12, 23, 34]
+    assert not oracle.is_eval_step(0, 11, True) and oracle.is_eval_step(1, 11, True)
+    assert oracle.is_eval_step(5, 11, False) and not oracle.is_eval_step(0, 11, False)
+
+
+def test_learning_rate_schedule(oracle):
+    assert oracle.lrate_at(1e-3, 0.5, 100000, 100000) == np.float32(1e-3)
+    assert abs(float(oracle.lrate_at(1e-3, 0.5, 400000, 100000)) - 0.5e-3) < 1e-9
+    assert oracle.eval_score(-10.0, -20.0, 5, 7) == pytest.approx((-10.0 - 4.0) / 7)
+
+
+def test_matsource_deals_minibatches_round_robin():
+    from bidmach_b200.learner import MatSource
+    toks = np.arange(2 * 1050, dtype=np.int32).reshape(1050, 2)
+    s = MatSource(toks, 100)
+    sizes = []
+    while s.hasNext():
+        sizes.append(s.next()[0].shape[0])
+    assert sizes == [100] * 10 + [50]
+    a, b = MatSource(toks, 100, 0, 2), MatSource(toks, 100, 1, 2)
+    ga, gb = [], []
+    while a.hasNext():
+        ga.append(int(a.next()[0][0, 0]) // 200)
+    while b.hasNext():
+        gb.append(int(b.next()[0][0, 0]) // 200)
+    assert ga == [0, 2, 4, 6, 8] and gb == [1, 3, 5, 7, 9]   # ragged 11th batch dropped for both
+    assert a.nbatches == b.nbatches == 5
+
+
+class _FakeModel:
+    def __init__(self):
+        self.calls, self.ncols = [], 100
+
+    def init(self, ncols):
+        self.ncols = ncols
+
+    def dobatchg(self, mats, ipass, pos):
+        self.calls.append(("train", pos, mats[0].shape[0]))
+        return 0
+
+    def evalbatchg(self, mats, ipass, pos):
+        self.calls.append(("eval", pos, mats[0].shape[0]))
+        return -1.0
+
+
+def test_learner_replays_the_reference_schedule():
+    from bidmach_b200.learner import Learner, LearnerOpts, MatSource
+    toks = np.zeros((1450, 2), np.int32)
+    m = _FakeModel()
+    Learner(MatSource(toks, 100), m, LearnerOpts(npasses=2, evalStep=11)).train()
+    kinds = [c[0] for c in m.calls]
+    one_pass = ["train", "eval"] + ["train"] * 10 + ["eval"] + ["train"] + ["eval"]
+    assert kinds == one_pass * 2
+    assert [c[1] for c in m.calls][:3] == [100, 200, 300]          # `here` advances by batchSize
+    assert m.calls[14][2] == 50                                      # the short last batch still arrives
+    assert [c[1] for c in m.calls][15] == 1600                       # and `here` keeps counting in pass 2
+
+
+def test_corpora_are_seeded_and_ranked():
+    from bidmach_b200.corpus import TopicCorpus, zipf_corpus
+    a = zipf_corpus(5000, 20000, 1.0, seed=3, doc_len=100)
+    b = zipf_corpus(5000, 20000, 1.0, seed=3, doc_len=100)
+    assert a.dtype == np.int32 and a.shape == (20000, 2) and np.array_equal(a, b)
+    assert not np.array_equal(a, zipf_corpus(5000, 20000, 1.0, seed=4, doc_len=100))
+    counts = np.bincount(a[:, 0], minlength=5000)
+    assert counts[0] > counts[10] > counts[200] and a[:, 0].max() < 5000
+    assert np.array_equal(a[:, 1], np.arange(20000) // 100)
+    tc = TopicCorpus(2000, 20, seed=1, doc_len=50, rank_sample_docs=400)
+    x, y = tc.tokens(5, 40), tc.tokens(5, 40)
+    assert np.array_equal(x, y) and x.shape == (2000, 2) and x[:, 0].max() < 2000
+    assert np.array_equal(np.unique(x[:, 1]), np.arange(5, 45))
+    c = np.bincount(tc.tokens(100, 400)[:, 0], minlength=2000)
+    assert c[:100].sum() > c[1000:1100].sum()                        # low ids are the frequent ones
+    # topical structure: a document concentrates on few words compared with the corpus
+    doc = tc.tokens(0, 1)[:, 0]
+    assert len(np.unique(doc)) < 50
+
+
+def test_philox_known_answers(oracle):
+    """Known-answer vectors of Philox4x32-10 from the generator's publication."""
+    z = np.zeros(1, np.uint32)
+    out = oracle.philox4x32_10(z, z, z, z, 0, 0)
+    assert [int(x[0]) for x in out] == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
+    f = np.full(1, 0xFFFFFFFF, np.uint32)
+    out = oracle.philox4x32_10(f, f, f, f, 0xFFFFFFFF, 0xFFFFFFFF)
+    assert [int(x[0]) for x in out] == [0x408F276D, 0x41C83B0E, 0xA20BC7C6, 0x6D5451FD]
+    out = oracle.philox4x32_10(np.array([0x243F6A88], np.uint32), np.array([0x85A308D3], np.uint32),
+                               np.array([0x13198A2E], np.uint32), np.array([0x03707344], np.uint32),
+                               0xA4093822, 0x299F31D0)
+    assert [int(x[0]) for x in out] == [0xD16CFE09, 0x94FDCCEB, 0x5001E420, 0x24126EA1]
+    u = oracle.u01(np.array([0, 0xFFFFFFFF, 0x80000000], np.uint32))
+    assert u[0] == 0.0 and u[1] < 1.0 and u[2] == 0.5
+
+
+def _avg_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from bidmach_b200.word2vec import Word2Vec
+    m = Word2Vec.__new__(Word2Vec)          # no device needed for the exchange itself
+    m.modelmats = [torch.full((6, 4), float(rank + 1)), torch.arange(24.0).view(6, 4) * (rank + 1)]
+    m.mergeModelFn()
+    q.put((rank, m.modelmats[0].clone(), m.modelmats[1].clone()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_merge_model_averages_both_matrices_over_a_gloo_group():
+    world, port = 2, 29511 + os.getpid() % 500
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_avg_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for _, m0, m1 in got:
+        assert torch.allclose(m0, torch.full((6, 4), 1.5))
+        assert torch.allclose(m1, torch.arange(24.0).view(6, 4) * 1.5)
+
+
+def _par_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from bidmach_b200.learner import LearnerOpts, MatSource, ParLearner
+
+    class M(_FakeModel):
+        def __init__(self):
+            super().__init__()
+            self.modelmats = [torch.full((3, 2), float(rank)), torch.zeros(3, 2)]
+            self.merges = 0
+
+        def dobatchg(self, mats, ipass, pos):
+            self.modelmats[0] += 1.0 + rank
+            return super().dobatchg(mats, ipass, pos)
+
+        def mergeModelFn(self, group=None):
+            self.merges += 1
+            for t in self.modelmats:
+                dist.all_reduce(t)
+                t /= world
+
+    toks = np.zeros((2100, 2), np.int32)
+    m = M()
+    ParLearner(MatSource(toks, 100, rank, world), m, LearnerOpts(npasses=1, evalStep=11, syncStep=2)).train()
+    q.put((rank, m.merges, len(m.calls), m.modelmats[0].clone()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_parlearner_syncs_every_syncstep_and_replicas_agree():
+    world, port = 2, 29011 + os.getpid() % 500
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_par_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted((q.get(timeout=120) for _ in range(world)), key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    # 21 batches -> 20 usable, 10 per rank; istep 1 and the last are eval-only: 8 train steps, 4 syncs
+    assert got[0][1] == got[1][1] == 4 and got[0][2] == got[1][2] == 10
+    assert torch.equal(got[0][3], got[1][3])

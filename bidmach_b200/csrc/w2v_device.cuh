@@ -166,4 +166,39 @@ struct Spread {
   }
 };
 
+// Which lanes hold a real total in slot q after Spread<M>::reduce.
+template <int M>
+__host__ __device__ constexpr unsigned spread_valid_mask(int q) {
+  unsigned m = 0;
+  for (int idx = 0; idx < M; idx++)
+    if (Spread<M>::slot_of(idx) == q) m |= 1u << Spread<M>::lane_of(idx);
+  return m;
+}
+
+// Lane l < NWA carries A-word l of the column, lanes NWA..NWA+NWB-1 the
+// B-words.  Ids at or above `nwords` are masked to -1 (word2vecNegFilt,
+// jni/src/DNN127.cu:690-712): a masked word acts as a zero row and is not
+// updated.
+template <int NWA, int NWB>
+__device__ __forceinline__ int column_word(const int *__restrict__ WA, const int *__restrict__ WB,
+                                           int64_t col, int nwords, int lane) {
+  int w = -1;
+  if (lane < NWA)
+    w = WA[col * NWA + lane];
+  else if (lane < NWA + NWB)
+    w = WB[col * NWB + (lane - NWA)];
+  if (w >= nwords) w = -1;
+  return w;
+}
+
+template <int NWA, int NWB, int NR>
+__device__ __forceinline__ void column_dots(const Row<NR> (&a)[NWA], const Row<NR> (&b)[NWB],
+                                            float (&p)[NWA * NWB], int lane) {
+#pragma unroll
+  for (int j = 0; j < NWA; j++)
+#pragma unroll
+    for (int k = 0; k < NWB; k++) p[j * NWB + k] = row_dot_partial(a[j], b[k]);
+  Spread<NWA * NWB>::reduce(p, lane);
+}
+
 }  // namespace w2v

@@ -49,6 +49,7 @@ SIGNATURES = {
     "word2vecNegFilt": (_I, [_I, _I, _I, _I, _I, _P, _P, _P, _P, _F, _F]),
     "word2vecEvalPos": (_I, [_I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "word2vecEvalNeg": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "word2vecEvalNegNoAlloc": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "JNI_OnLoad": (_I, [_P, _P]),
     "Java_edu_berkeley_bid_CUMACH_word2vecPos": (_I, [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _F, _F]),
     "Java_edu_berkeley_bid_CUMACH_word2vecNeg": (_I, [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _F, _F]),

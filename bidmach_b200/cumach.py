@@ -55,6 +55,16 @@ class CUMACH:
                                            _addr(B), _addr(retVal))
 
 
+def word2vecEvalNegNoAlloc(nrows, ncols, nwa, nwb, WA, WB, A, B, retVal) -> int:
+    """``CUMACH.word2vecEvalNeg`` for callers that cannot allocate device memory
+    while running (the Java class has no such method).  Same arguments and
+    result; its scratch memory is an array inside the library, so it accepts at
+    most 2,097,152 columns per call, returns 1 beyond that, and must not run
+    concurrently with another call of itself on the same GPU."""
+    return _lib.load().word2vecEvalNegNoAlloc(nrows, ncols, nwa, nwb, _addr(WA), _addr(WB),
+                                              _addr(A), _addr(B), _addr(retVal))
+
+
 def cuda_error_string(err: int) -> str:
     """Text for a code returned by the methods above (cudaGetErrorString)."""
     if err == 0:

@@ -68,6 +68,19 @@ int word2vecEvalPos(int nrows, int ncols, int shift, int *W, int *LB, int *UB, f
 int word2vecEvalNeg(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A, float *B,
                     float *Retval);
 
+/* No counterpart in the reference.  Same contract as word2vecEvalNeg, for
+ * hosts that must not allocate device memory while they run (a JVM whose matrix
+ * cache already owns the card, a process that froze its memory map, work being
+ * recorded into a stream capture): the partial sums live in an array built into
+ * the library's device image (about 64 KiB on every GPU that loads the library)
+ * instead of a buffer obtained with cudaMalloc.  At most 2,097,152 columns per
+ * call; a larger ncols prints a message and returns 1.  The first call on a
+ * device looks up the array's device address and should therefore be made
+ * outside any stream capture.  Calls on the same GPU share the array: do not
+ * let two of them run at the same time. */
+int word2vecEvalNegNoAlloc(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A,
+                           float *B, float *Retval);
+
 /* ------------------------------------------------------------------------
  * Part 2 -- JNI entry points, bound by name from edu.berkeley.bid.CUMACH
  * (src/main/java/edu/berkeley/bid/CUMACH.java:90-98).  They replace the

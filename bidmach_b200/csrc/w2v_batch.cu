@@ -212,6 +212,8 @@ struct w2v_ctx {
   int *ctx_in, *ctx_out, *wa;
   uint32_t *key_in, *key_out;
   float *retvals;  // [0] positive, [1] negative
+  float *hot_buf;  // replica rows of the hot ids
+  w2v::HotRows hot;
   void *cub_tmp;
   size_t cub_tmp_bytes;
   // pinned host
@@ -320,7 +322,7 @@ void w2v_destroy(w2v_ctx *c) {
   cudaFree(c->tokens); cudaFree(c->words); cudaFree(c->lb); cudaFree(c->ub); cudaFree(c->cnt);
   cudaFree(c->off); cudaFree(c->counts); cudaFree(c->ctx_in); cudaFree(c->ctx_out);
   cudaFree(c->wa); cudaFree(c->key_in); cudaFree(c->key_out); cudaFree(c->retvals);
-  cudaFree(c->cub_tmp);
+  cudaFree(c->cub_tmp); cudaFree(c->hot_buf);
   cudaFreeHost(c->counts_host); cudaFreeHost(c->retvals_host);
   for (int k = 0; k < 5; k++) if (c->ev[k]) cudaEventDestroy(c->ev[k]);
   cudaSetDevice(prev);
@@ -362,6 +364,11 @@ int w2v_create(const w2v_opts *opts, int ncols, w2v_ctx **out) {
   if (e == cudaSuccess) e = cudaMalloc(&c->key_out, p4);
   if (e == cudaSuccess) e = cudaMalloc(&c->wa, sizeof(int) * (size_t)(max_groups + 1) * o.nneg);
   if (e == cudaSuccess) e = cudaMalloc(&c->retvals, 256);
+  if (e == cudaSuccess && w2v::hot_levels_default() > 0) {
+    e = cudaMalloc(&c->hot_buf, w2v::hot_rows_bytes());
+    if (e == cudaSuccess) e = cudaMemset(c->hot_buf, 0, w2v::hot_rows_bytes());
+  }
+  c->hot = w2v::hot_rows_at(c->hot_buf, w2v::hot_levels_default());
   if (e == cudaSuccess) e = cudaMallocHost(&c->counts_host, 256);
   if (e == cudaSuccess) e = cudaMallocHost(&c->retvals_host, 256);
   if (e == cudaSuccess)
@@ -462,11 +469,11 @@ int w2v_dobatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, float *A, 
   int err = w2v_wordmats(c, tokens, u, batch_id, stream);
   if (err) return err;
   err = w2v::pos_update_async(o.dim, c->ncols, nullptr, o.nskip, c->words, c->lb, c->ub, A, B,
-                              lrpos, o.vexp, stream);
+                              lrpos, o.vexp, c->hot, stream);
   if (err) return err;
   mark(c, 3, stream);
   err = w2v::neg_update_async(o.dim, c->ngroups, nullptr, 0x7fffffff, o.nneg, o.nreuse, c->wa,
-                              c->ctx_out, A, B, lrneg, o.vexp, stream);
+                              c->ctx_out, A, B, lrneg, o.vexp, c->hot, stream);
   mark(c, 4, stream);
   if (c->timing_on) {
     c->ev_pending = 1;

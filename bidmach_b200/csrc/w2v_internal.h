@@ -14,6 +14,18 @@ struct EvalScratch {
   unsigned pad;
 };
 
+// Side buffer of replica rows for the most frequent word ids (see
+// w2v_kernels.cu).  limit = 2^levels: ids with id + 1 < limit are hot; 0 = off.
+struct HotRows {
+  float *shadowA;
+  float *shadowB;
+  int limit;
+};
+size_t hot_rows_bytes();
+int hot_levels_default();
+HotRows hot_rows_at(float *zeroed_buffer, int levels);
+int thread_hot_rows(HotRows *out);
+
 int eval_scratch(EvalScratch **out);
 int device_sm_count();
 long long launch_count();
@@ -26,13 +38,13 @@ bool neg_shape_supported(int nwa, int nwb);
 // upper bound used to size the grid.
 int pos_update_async(int dim, int ncols, const int *ncols_dev, int skip, const int *W,
                      const int *LB, const int *UB, float *A, float *B, float lrate, float vexp,
-                     cudaStream_t stream);
+                     const HotRows &hot, cudaStream_t stream);
 int pos_eval_async(int dim, int ncols, const int *ncols_dev, int skip, const int *W, const int *LB,
                    const int *UB, const float *A, const float *B, float *retval,
                    cudaStream_t stream);
 int neg_update_async(int dim, int ncols, const int *ncols_dev, int nwords, int nwa, int nwb,
                      const int *WA, const int *WB, float *A, float *B, float lrate, float vexp,
-                     cudaStream_t stream);
+                     const HotRows &hot, cudaStream_t stream);
 int neg_eval_async(int dim, int ncols, const int *ncols_dev, int nwa, int nwb, const int *WA,
                    const int *WB, const float *A, const float *B, float *retval,
                    cudaStream_t stream);

@@ -28,14 +28,30 @@
 // inputs where no row is shared between units the result equals the sequential
 // CPU result up to fp32 summation order.
 //
-// Work decomposition: one warp per centre (Pos) or per column (Neg); the rows
-// of the unit live in registers as 128-bit vectors; dot products are reduced
-// with warp shuffles; grids are sized to fill every SM and stride over the
-// minibatch.
+// Work decomposition: one warp per token position (Pos) or per column (Neg);
+// the rows of the unit live in registers as 128-bit vectors; dot products are
+// reduced with warp shuffles; grids are sized to fill every SM.
+//
+// Pos walks the minibatch in order: every warp owns a contiguous stretch of
+// positions and visits its centres one after the other.  The delta of a
+// context row is not sent to memory per pair; it is accumulated in a ring of
+// 2*skip+1 row-sized slots in shared memory (one per position of the sliding
+// window, private to the warp) and added to B once, when the window has moved
+// past that position.  Each position therefore costs two atomic row updates
+// (its A row as a centre, its B row as a context) instead of one per pair, and
+// a pair is still evaluated by exactly one warp from one reading of its rows.
+//
+// Hot rows: under a Zipf-like draw a handful of word ids receive a large share
+// of all updates, and atomic adds to one address serialise in L2.  Updates to
+// the most frequent ids (id + 1 < 2^levels; ids are frequency ranks) are
+// therefore spread over up to 64 replica rows in a small side buffer and
+// folded into the model by a tiny kernel that follows the update kernel.
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
+#include <algorithm>
 #include <atomic>
 
 #include "w2v_device.cuh"
@@ -43,7 +59,7 @@
 
 namespace w2v {
 
-constexpr int kPosThreads = 256;
+constexpr int kPosThreads = 128;
 constexpr int kNegThreads = 128;
 constexpr int kGenericThreads = 128;
 
@@ -62,49 +78,199 @@ __device__ __forceinline__ int window_word(const int *__restrict__ W, int i, int
   return W[t];
 }
 
+// Destination of an update to row w of matrix M: the row itself, or for a hot
+// id one of its replica rows in the side buffer (picked by the warp's number).
+__device__ __forceinline__ float *update_target(float *M, float *shadow, int hot_limit, int w,
+                                                int dim, unsigned pick) {
+  if (w + 1 < hot_limit) {
+    const int level = 31 - __clz(w + 1);
+    const int reps = 64 >> level;
+    const int row = 64 * level + (w + 1 - (1 << level)) * reps + (int)(pick & (unsigned)(reps - 1));
+    return shadow + (int64_t)row * dim;
+  }
+  return M + (int64_t)w * dim;
+}
+
 template <int NR>
-__global__ void __launch_bounds__(kPosThreads)
+__device__ __forceinline__ void row_red_to(float *p, int nvec, int lane, const Row<NR> &r) {
+#pragma unroll
+  for (int q = 0; q < NR; q++) {
+    int idx = lane + 32 * q;
+    if (idx < nvec) red_add_v4(p + 4 * idx, r.v[q]);
+  }
+}
+
+// Folds the replica rows of the hot ids back into the model and clears them.
+// grid = (hot ids, 2 matrices).
+__global__ void hot_fold_kernel(int dim, HotRows hot, float *A, float *B) {
+  const int h = blockIdx.x;
+  float *M = blockIdx.y ? B : A;
+  float *S = blockIdx.y ? hot.shadowB : hot.shadowA;
+  const int level = 31 - __clz(h + 1);
+  const int reps = 64 >> level;
+  float *base = S + (int64_t)(64 * level + (h + 1 - (1 << level)) * reps) * dim;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+    float sum = 0.f;
+    for (int r = 0; r < reps; r++) {
+      sum += base[(int64_t)r * dim + c];
+      base[(int64_t)r * dim + c] = 0.f;
+    }
+    if (sum != 0.f) M[(int64_t)h * dim + c] += sum;  // ids that were never touched are not read
+  }
+}
+
+// Neighbour rows loaded and reduced together: as many as the register file
+// allows for rows of NR vectors per lane.
+template <int NR>
+struct ChunkOf {
+  static constexpr int value = NR <= 4 ? 5 : (NR <= 6 ? 3 : 2);
+};
+// Resident blocks per SM the positive update is compiled for (its ring of
+// row-sized slots in shared memory allows no more for wide rows anyway).
+template <int NR>
+struct PosBlocksOf {
+  static constexpr int value = NR <= 3 ? 4 : (NR <= 5 ? 2 : 1);
+};
+
+// Takes up to kChunk set bits out of `todo` (lane numbers of neighbours), loads
+// their rows from M and returns the per-lane share of the kChunk dot products
+// with `own` after the spreading reduction: lane Spread::lane_of(c) holds dot c.
+template <int NR, int kChunk>
+__device__ __forceinline__ float chunk_dots(unsigned &todo, int (&src)[kChunk],
+                                            Row<NR> (&rows)[kChunk], const Row<NR> &own,
+                                            const float *M, int wnb, int dim, int nvec, int lane) {
+#pragma unroll
+  for (int c = 0; c < kChunk; c++) {
+    if (todo) {
+      src[c] = __ffs(todo) - 1;
+      todo &= todo - 1;
+      row_load(rows[c], M, __shfl_sync(kFullMask, wnb, src[c]), dim, nvec, lane);
+    } else {
+      src[c] = -1;
+      row_zero(rows[c]);
+    }
+  }
+  float p[kChunk];
+#pragma unroll
+  for (int c = 0; c < kChunk; c++) p[c] = row_dot_partial(own, rows[c]);
+  Spread<kChunk>::reduce(p, lane);
+  return p[0];
+}
+
+// What lane `lane` sees at offset lane - skip from position t: the word there
+// and whether t, as a centre, pairs with it.
+struct Neighbour {
+  int word;
+  bool t_is_centre;
+};
+
+__device__ __forceinline__ Neighbour look_at_neighbour(const int *__restrict__ W, int t, int lbt,
+                                                       int ubt, int skip, int ncols, int lane) {
+  Neighbour nb = {-1, false};
+  const int j = lane - skip, u = t + j;
+  if (lane <= 2 * skip && j != 0 && j >= lbt && j <= ubt && u >= 0 && u < ncols) {
+    const int w = W[u];
+    if (w >= 0) {
+      nb.word = w;
+      nb.t_is_centre = true;
+    }
+  }
+  return nb;
+}
+
+// Shared memory: per warp, (2*skip+1) slots of nvec float4 (one context-row
+// delta each).  Lane l only ever touches elements l, l+32, ... of a slot, so no
+// synchronisation is needed between the lanes of the owning warp.
+template <int NR>
+__global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
     pos_update_kernel(int dim, int ncols, const int *__restrict__ ncols_dev, int skip,
                       const int *__restrict__ W, const int *__restrict__ LB,
-                      const int *__restrict__ UB, float *A, float *B, float lrate, float vexp) {
-  const int lane = threadIdx.x & 31;
+                      const int *__restrict__ UB, float *A, float *B, float lrate, float vexp,
+                      HotRows hot) {
+  constexpr int kChunk = ChunkOf<NR>::value;
+  static_assert(Spread<kChunk>::FIN == 1, "one total per lane expected");
+  extern __shared__ float4 ring_storage[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = dim >> 2;
-  const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int slots = 2 * skip + 1;
+  float4 *ring = ring_storage + (size_t)warp * slots * nvec;
+  const unsigned gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const unsigned nwarps = (gridDim.x * blockDim.x) >> 5;
   if (ncols_dev) ncols = *ncols_dev;
+  const int per_warp = (ncols + (int)nwarps - 1) / (int)nwarps;
+  const int first = (int)gwarp * per_warp;
+  const int last = min(ncols, first + per_warp);
+  const int base = first - skip;  // lowest position that can own a slot
+  unsigned dirty = 0;             // bit s: slot s holds a pending delta
 
-  for (int i = gwarp; i < ncols; i += nwarps) {
-    const int wc = W[i];
-    if (wc < 0) continue;
-    const int lb = max(LB[i], -skip), ub = min(UB[i], skip);
-    const int wx = window_word(W, i, lb, ub, ncols, lane);
-    unsigned todo = __ballot_sync(kFullMask, wx >= 0);
-    if (todo == 0) continue;
-    // lane 31 never carries a context (the window has at most 31 offsets), so
-    // it evaluates the centre's scale while the others do their context's.
-    const int sid = (lane == 31) ? wc : wx;
-    const float sc = (sid >= 0) ? freq_scale(sid, vexp) : 0.f;
-    const float sa = __shfl_sync(kFullMask, sc, 31);
-
-    Row<NR> a, da;
-    row_load(a, A, wc, dim, nvec, lane);
-    row_zero(da);
-    while (todo) {
-      const int src = __ffs(todo) - 1;
-      todo &= todo - 1;
-      const int w = __shfl_sync(kFullMask, wx, src);
-      const float sb = __shfl_sync(kFullMask, sc, src);
-      Row<NR> b;
-      row_load(b, B, w, dim, nvec, lane);
-      const float g = lrate * (1.0f - sigmoid_guard(warp_sum(row_dot_partial(a, b))));
-      row_axpy(da, sa * g, b);
-      Row<NR> db;
-      row_zero(db);
-      row_axpy(db, sb * g, a);
-      row_red(B, w, dim, nvec, lane, db);
+  // B[W[u]] += slot of u, if it holds anything
+  auto retire = [&](int u) {
+    const int slot = (u - base) % slots;
+    if ((dirty >> slot) & 1u) {
+      dirty &= ~(1u << slot);
+      float *dst = update_target(B, hot.shadowB, hot.limit, W[u], dim, gwarp);
+      const float4 *sp = ring + slot * nvec;
+#pragma unroll
+      for (int q = 0; q < NR; q++) {
+        const int idx = lane + 32 * q;
+        if (idx < nvec) red_add_v4(dst + 4 * idx, sp[idx]);
+      }
     }
-    row_red(A, wc, dim, nvec, lane, da);
+  };
+
+  for (int t = first; t < last; t++) {
+    const int wt = W[t];
+    if (wt >= 0) {
+      const int lbt = max(LB[t], -skip), ubt = min(UB[t], skip);
+      const Neighbour nb = look_at_neighbour(W, t, lbt, ubt, skip, ncols, lane);
+      unsigned todo = __ballot_sync(kFullMask, nb.t_is_centre);
+      if (todo) {
+        // lane 31 never carries a neighbour (at most 31 offsets), so it
+        // evaluates the centre's scale while the others do their context's
+        const int sid = (lane == 31) ? wt : nb.word;
+        const float sc = (sid >= 0) ? freq_scale(sid, vexp) : 0.f;
+        const float sa = __shfl_sync(kFullMask, sc, 31);
+        Row<NR> a, da;
+        row_load(a, A, wt, dim, nvec, lane);
+        row_zero(da);
+        while (todo) {
+          int src[kChunk];
+          Row<NR> rows[kChunk];
+          const float dot = chunk_dots(todo, src, rows, a, B, nb.word, dim, nvec, lane);
+          const float mine = lrate * (1.0f - sigmoid_guard(dot));
+#pragma unroll
+          for (int c = 0; c < kChunk; c++) {
+            if (src[c] < 0) continue;
+            const float g = __shfl_sync(kFullMask, mine, Spread<kChunk>::lane_of(c));
+            const float sb = __shfl_sync(kFullMask, sc, src[c]);
+            row_axpy(da, sa * g, rows[c]);
+            // context side: slot(u) += (sb * g) * a
+            const int slot = (t + src[c] - skip - base) % slots;
+            float4 *sp = ring + slot * nvec;
+            const float coef = sb * g;
+            const bool pending = (dirty >> slot) & 1u;
+            dirty |= 1u << slot;
+#pragma unroll
+            for (int q = 0; q < NR; q++) {
+              const int idx = lane + 32 * q;
+              if (idx < nvec) {
+                float4 v = pending ? sp[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+                v.x = fmaf(coef, a.v[q].x, v.x);
+                v.y = fmaf(coef, a.v[q].y, v.y);
+                v.z = fmaf(coef, a.v[q].z, v.z);
+                v.w = fmaf(coef, a.v[q].w, v.w);
+                sp[idx] = v;
+              }
+            }
+          }
+        }
+        row_red_to(update_target(A, hot.shadowA, hot.limit, wt, dim, gwarp), nvec, lane, da);
+      }
+    }
+    // no later centre of this warp reaches position t - skip
+    if (t - skip >= base && dirty) retire(t - skip);
   }
+  for (int u = max(last - skip, base); u < last + skip && dirty; u++) retire(u);
 }
 
 // Adds this block's double partial sum into scratch[0]; the block that
@@ -140,34 +306,34 @@ __global__ void __launch_bounds__(kPosThreads)
                     const int *__restrict__ W, const int *__restrict__ LB,
                     const int *__restrict__ UB, const float *__restrict__ A,
                     const float *__restrict__ B, EvalScratch *scratch, float *retval) {
-  const int lane = threadIdx.x & 31;
+  constexpr int kChunk = ChunkOf<NR>::value;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = dim >> 2;
-  const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int nwarps = (gridDim.x * blockDim.x) >> 5;
   if (ncols_dev) ncols = *ncols_dev;
+  const int per_block = (ncols + gridDim.x - 1) / gridDim.x;
+  const int first = blockIdx.x * per_block;
+  const int last = min(ncols, first + per_block);
   double acc = 0.0;
 
-  for (int i = gwarp; i < ncols; i += nwarps) {
-    const int wc = W[i];
-    if (wc < 0) continue;
-    const int lb = max(LB[i], -skip), ub = min(UB[i], skip);
-    const int wx = window_word(W, i, lb, ub, ncols, lane);
-    unsigned todo = __ballot_sync(kFullMask, wx >= 0);
+  for (int t = first + warp; t < last; t += (int)(blockDim.x >> 5)) {
+    const int wt = W[t];
+    if (wt < 0) continue;
+    const int lbt = max(LB[t], -skip), ubt = min(UB[t], skip);
+    const Neighbour nb = look_at_neighbour(W, t, lbt, ubt, skip, ncols, lane);
+    unsigned todo = __ballot_sync(kFullMask, nb.t_is_centre);
     if (todo == 0) continue;
-    Row<NR> a;
-    row_load(a, A, wc, dim, nvec, lane);
-    float mine = 0.f;
+    Row<NR> own;
+    row_load(own, A, wt, dim, nvec, lane);
     while (todo) {
-      const int src = __ffs(todo) - 1;
-      todo &= todo - 1;
-      const int w = __shfl_sync(kFullMask, wx, src);
-      Row<NR> b;
-      row_load(b, B, w, dim, nvec, lane);
-      const float p = warp_sum(row_dot_partial(a, b));
-      if (lane == src) mine = p;
+      int src[kChunk];
+      Row<NR> rows[kChunk];
+      const float dot = chunk_dots(todo, src, rows, own, B, nb.word, dim, nvec, lane);
+      // the lane that holds a pair's dot product scores it (networks/Word2Vec.scala:995)
+#pragma unroll
+      for (int c = 0; c < kChunk; c++)
+        if (src[c] >= 0 && lane == Spread<kChunk>::lane_of(c))
+          acc += log(fmax((double)sigmoid_guard(dot), 1e-20));
     }
-    // each context lane scores its own pair (networks/Word2Vec.scala:995)
-    if (wx >= 0) acc += log(fmax((double)sigmoid_guard(mine), 1e-20));
   }
   finish_eval_sum(acc, scratch, retval);
 }
@@ -266,7 +432,7 @@ template <int NWA, int NWB, int NR>
 __global__ void __launch_bounds__(kNegThreads)
     neg_update_kernel(int dim, int ncols, const int *__restrict__ ncols_dev, int nwords,
                       const int *__restrict__ WA, const int *__restrict__ WB, float *A, float *B,
-                      float lrate, float vexp) {
+                      float lrate, float vexp, HotRows hot) {
   using S = Spread<NWA * NWB>;
   const int lane = threadIdx.x & 31;
   const int nvec = dim >> 2;
@@ -315,7 +481,8 @@ __global__ void __launch_bounds__(kNegThreads)
       row_zero(d);
 #pragma unroll
       for (int k = 0; k < NWB; k++) row_axpy(d, sa * g[j * NWB + k], b[k]);
-      if (wa[j] >= 0) row_red(A, wa[j], dim, nvec, lane, d);
+      if (wa[j] >= 0)
+        row_red_to(update_target(A, hot.shadowA, hot.limit, wa[j], dim, gwarp), nvec, lane, d);
     }
 #pragma unroll
     for (int k = 0; k < NWB; k++) {
@@ -324,7 +491,8 @@ __global__ void __launch_bounds__(kNegThreads)
       row_zero(d);
 #pragma unroll
       for (int j = 0; j < NWA; j++) row_axpy(d, sb * g[j * NWB + k], a[j]);
-      if (wb[k] >= 0) row_red(B, wb[k], dim, nvec, lane, d);
+      if (wb[k] >= 0)
+        row_red_to(update_target(B, hot.shadowB, hot.limit, wb[k], dim, gwarp), nvec, lane, d);
     }
   }
 }
@@ -494,6 +662,61 @@ int eval_scratch(EvalScratch **out) {
   return 0;
 }
 
+// Replica rows for the hot ids: 64 rows per level and matrix, sized for the
+// widest supported row.  One buffer per (host thread, device) for the
+// synchronous entry points; a minibatch context owns its own.
+constexpr int kHotMaxLevels = 6;
+constexpr int kHotMaxDim = 1280;
+
+int hot_levels_default() {
+  static int levels = [] {
+    const char *e = getenv("W2V_HOT_LEVELS");
+    int v = e ? atoi(e) : kHotMaxLevels;
+    return v < 0 ? 0 : (v > kHotMaxLevels ? kHotMaxLevels : v);
+  }();
+  return levels;
+}
+
+size_t hot_rows_bytes() { return sizeof(float) * 2 * 64 * kHotMaxLevels * (size_t)kHotMaxDim; }
+
+HotRows hot_rows_at(float *buffer, int levels) {
+  HotRows h;
+  h.shadowA = buffer;
+  h.shadowB = buffer ? buffer + (size_t)64 * kHotMaxLevels * kHotMaxDim : nullptr;
+  h.limit = (buffer && levels > 0) ? (1 << levels) : 0;
+  return h;
+}
+
+int thread_hot_rows(HotRows *out) {
+  constexpr int kMaxDev = 64;
+  thread_local float *per_dev[kMaxDev] = {nullptr};
+  const int levels = hot_levels_default();
+  if (levels == 0) {
+    *out = hot_rows_at(nullptr, 0);
+    return 0;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDev) return (int)cudaErrorInvalidDevice;
+  if (!per_dev[dev]) {
+    float *p = nullptr;
+    e = cudaMalloc(&p, hot_rows_bytes());
+    if (e != cudaSuccess) return (int)e;
+    e = cudaMemset(p, 0, hot_rows_bytes());
+    if (e != cudaSuccess) return (int)e;
+    per_dev[dev] = p;
+  }
+  *out = hot_rows_at(per_dev[dev], levels);
+  return 0;
+}
+
+static void fold_hot_rows(int dim, const HotRows &hot, float *A, float *B, cudaStream_t stream) {
+  if (hot.limit <= 1) return;
+  hot_fold_kernel<<<dim3(hot.limit - 1, 2), 128, 0, stream>>>(dim, hot, A, B);
+  count_launch(1);
+}
+
 static inline bool vector_ok(int dim, const void *A, const void *B) {
   return dim > 0 && (dim & 3) == 0 && dim <= 1280 && ((uintptr_t)A & 15) == 0 &&
          ((uintptr_t)B & 15) == 0;
@@ -521,16 +744,46 @@ static inline int grid_for(int work_items, int threads, int blocks_per_sm) {
     default: { constexpr int NR = 10; CALL; } break; \
   }
 
+template <int NR>
+static cudaError_t launch_pos_update(int grid, size_t smem, cudaStream_t stream, int dim, int ncols,
+                                     const int *ncols_dev, int skip, const int *W, const int *LB,
+                                     const int *UB, float *A, float *B, float lrate, float vexp,
+                                     const HotRows &hot) {
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(pos_update_kernel<NR>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  pos_update_kernel<NR><<<grid, kPosThreads, smem, stream>>>(dim, ncols, ncols_dev, skip, W, LB, UB, A,
+                                                             B, lrate, vexp, hot);
+  return cudaSuccess;
+}
+
+// Launch shape of the positive update for rows of `dim` floats and window
+// half-width `skip`: shared memory per block, or 0 when the ring does not fit.
+static size_t pos_ring_bytes(int dim, int skip) {
+  return (size_t)(kPosThreads / 32) * (2 * skip + 1) * (size_t)dim * sizeof(float);
+}
+
 int pos_update_async(int dim, int ncols, const int *ncols_dev, int skip, const int *W,
                      const int *LB, const int *UB, float *A, float *B, float lrate, float vexp,
-                     cudaStream_t stream) {
+                     const HotRows &hot, cudaStream_t stream) {
   if (ncols <= 0) return 0;
   if (skip < 1 || skip > 15) return 1;
-  if (vector_ok(dim, A, B)) {
+  const size_t smem = pos_ring_bytes(dim, skip);
+  if (vector_ok(dim, A, B) && smem <= 227 * 1024) {
     const int nr = (dim / 4 + 31) / 32;
-    const int grid = grid_for(ncols, kPosThreads, 8);
-    W2V_NR_SWITCH(nr, (pos_update_kernel<NR><<<grid, kPosThreads, 0, stream>>>(
-                          dim, ncols, ncols_dev, skip, W, LB, UB, A, B, lrate, vexp)));
+    const int resident = (int)std::min<size_t>(4, (227 * 1024) / smem);
+    // enough warps to fill the GPU, but stretches of at least ~64 positions so
+    // that the window edges between stretches stay a small share of the work
+    int grid = device_sm_count() * resident;
+    const int max_grid = std::max(1, ncols / (64 * (kPosThreads / 32)));
+    grid = std::max(1, std::min(grid, max_grid));
+    cudaError_t e = cudaSuccess;
+    W2V_NR_SWITCH(nr, (e = launch_pos_update<NR>(grid, smem, stream, dim, ncols, ncols_dev, skip, W,
+                                                 LB, UB, A, B, lrate, vexp, hot)));
+    if (e != cudaSuccess) return (int)e;
+    fold_hot_rows(dim, hot, A, B, stream);
   } else {
     const int grid = grid_for(ncols, kGenericThreads, 16);
     pos_update_generic_kernel<<<grid, kGenericThreads, 0, stream>>>(dim, ncols, ncols_dev, skip, W,
@@ -565,7 +818,7 @@ int pos_eval_async(int dim, int ncols, const int *ncols_dev, int skip, const int
 template <int NWA, int NWB>
 static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int nwords,
                         const int *WA, const int *WB, float *A, float *B, float lrate, float vexp,
-                        float *retval, cudaStream_t stream) {
+                        float *retval, const HotRows &hot, cudaStream_t stream) {
   EvalScratch *scratch = nullptr;
   if (eval) {
     int err = eval_scratch(&scratch);
@@ -586,11 +839,12 @@ static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int
       }
     } else {
       switch (nr) {
-        case 1: neg_update_kernel<NWA, NWB, 1><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp); break;
-        case 2: neg_update_kernel<NWA, NWB, 2><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp); break;
-        case 3: neg_update_kernel<NWA, NWB, (kMaxNr >= 3 ? 3 : 1)><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp); break;
-        default: neg_update_kernel<NWA, NWB, (kMaxNr >= 4 ? 4 : 1)><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp); break;
+        case 1: neg_update_kernel<NWA, NWB, 1><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot); break;
+        case 2: neg_update_kernel<NWA, NWB, 2><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot); break;
+        case 3: neg_update_kernel<NWA, NWB, (kMaxNr >= 3 ? 3 : 1)><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot); break;
+        default: neg_update_kernel<NWA, NWB, (kMaxNr >= 4 ? 4 : 1)><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot); break;
       }
+      fold_hot_rows(dim, hot, A, B, stream);
     }
   } else {
     const int grid = grid_for(ncols, kGenericThreads, 8);
@@ -607,31 +861,31 @@ static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int
 
 static int neg_any(bool eval, int dim, int ncols, const int *ncols_dev, int nwords, int nwa,
                    int nwb, const int *WA, const int *WB, float *A, float *B, float lrate,
-                   float vexp, float *retval, cudaStream_t stream) {
+                   float vexp, float *retval, const HotRows &hot, cudaStream_t stream) {
   if (ncols <= 0) return 0;
   if (dim <= 0) return 1;
   const int which = nwa * 10000 + nwb;
   switch (which) {
-    case 50001: return neg_dispatch<5, 1>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, stream);
-    case 50005: return neg_dispatch<5, 5>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, stream);
-    case 100005: return neg_dispatch<10, 5>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, stream);
-    case 50010: return neg_dispatch<5, 10>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, stream);
+    case 50001: return neg_dispatch<5, 1>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, stream);
+    case 50005: return neg_dispatch<5, 5>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, stream);
+    case 100005: return neg_dispatch<10, 5>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, stream);
+    case 50010: return neg_dispatch<5, 10>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, stream);
     default: return 1;
   }
 }
 
 int neg_update_async(int dim, int ncols, const int *ncols_dev, int nwords, int nwa, int nwb,
                      const int *WA, const int *WB, float *A, float *B, float lrate, float vexp,
-                     cudaStream_t stream) {
+                     const HotRows &hot, cudaStream_t stream) {
   return neg_any(false, dim, ncols, ncols_dev, nwords, nwa, nwb, WA, WB, A, B, lrate, vexp, nullptr,
-                 stream);
+                 hot, stream);
 }
 
 int neg_eval_async(int dim, int ncols, const int *ncols_dev, int nwa, int nwb, const int *WA,
                    const int *WB, const float *A, const float *B, float *retval,
                    cudaStream_t stream) {
   return neg_any(true, dim, ncols, ncols_dev, 0x7fffffff, nwa, nwb, WA, WB, const_cast<float *>(A),
-                 const_cast<float *>(B), 0.f, 0.f, retval, stream);
+                 const_cast<float *>(B), 0.f, 0.f, retval, hot_rows_at(nullptr, 0), stream);
 }
 
 bool neg_shape_supported(int nwa, int nwb) {
@@ -667,8 +921,11 @@ int word2vecPos(int nrows, int ncols, int shift, int *W, int *LB, int *UB, float
     printf("word2vecPos too many rows %d\n", nrows);
     return 1;
   }
+  w2v::HotRows hot;
+  int err = w2v::thread_hot_rows(&hot);
+  if (err) return err;
   return finish_sync(w2v::pos_update_async(nrows, ncols, nullptr, shift, W, LB, UB, A, B, lrate,
-                                           vexp, cudaStreamPerThread));
+                                           vexp, hot, cudaStreamPerThread));
 }
 
 int word2vecNeg(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A, float *B,
@@ -677,8 +934,11 @@ int word2vecNeg(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float 
     printf("word2vec unsupport size combination %d %d\n", nwa, nwb);
     return 1;
   }
+  w2v::HotRows hot;
+  int err = w2v::thread_hot_rows(&hot);
+  if (err) return err;
   return finish_sync(w2v::neg_update_async(nrows, ncols, nullptr, 0x7fffffff, nwa, nwb, WA, WB, A,
-                                           B, lrate, vexp, cudaStreamPerThread));
+                                           B, lrate, vexp, hot, cudaStreamPerThread));
 }
 
 int word2vecNegFilt(int nrows, int ncols, int nwords, int nwa, int nwb, int *WA, int *WB, float *A,
@@ -687,8 +947,11 @@ int word2vecNegFilt(int nrows, int ncols, int nwords, int nwa, int nwb, int *WA,
     printf("word2vec unsupport size combination %d %d\n", nwa, nwb);
     return 1;
   }
+  w2v::HotRows hot;
+  int err = w2v::thread_hot_rows(&hot);
+  if (err) return err;
   return finish_sync(w2v::neg_update_async(nrows, ncols, nullptr, nwords, nwa, nwb, WA, WB, A, B,
-                                           lrate, vexp, cudaStreamPerThread));
+                                           lrate, vexp, hot, cudaStreamPerThread));
 }
 
 int word2vecEvalPos(int nrows, int ncols, int shift, int *W, int *LB, int *UB, float *A, float *B,

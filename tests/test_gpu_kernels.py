@@ -187,20 +187,30 @@ def test_zero_learning_rate_is_the_identity_on_conflicting_input(cumach):
 
 
 def test_conflicting_updates_lose_nothing(oracle, cumach):
-    """Hot rows: many units update the same row.  With a tiny learning rate the
-    gradients barely depend on read order, so the atomically accumulated result
-    must match the sequential one closely; a lost update would show as a gap of
-    the size of one delta."""
-    dim, vocab, ncols = 100, 40, 6000
-    A, B = random_model(vocab, dim, 5, scale=0.5)
+    """Hot rows: every row is updated by about 25 columns at once.  With a small
+    learning rate the gradients barely depend on the order in which concurrent
+    units read the rows (sequential and fully parallel evaluation differ by
+    about 1e-3 here), so the atomically accumulated result must match the
+    sequential one closely; a single lost row update would leave a gap of about
+    1/25 = 4e-2."""
+    dim, vocab, ncols = 100, 40, 200
+    A, B = random_model(vocab, dim, 5, scale=0.01)
     WA, WB = random_neg(ncols, vocab, 5, 5, 6)
-    lr = 1e-6
+    lr = 2e-5
     A_ref, B_ref = A.copy(), B.copy()
     oracle.word2vecNeg(dim, ncols, 5, 5, WA, WB, A_ref, B_ref, lr, 0.0, 1)
     dA, dB = dev(A), dev(B)
     assert cumach.word2vecNeg(dim, ncols, 5, 5, dev(WA), dev(WB), dA, dB, lr, 0.0) == 0
-    assert rel_err(dA.cpu().numpy() - A, A_ref - A) <= 2e-3
-    assert rel_err(dB.cpu().numpy() - B, B_ref - B) <= 2e-3
+    assert rel_err(dA.cpu().numpy() - A, A_ref - A) <= 5e-3
+    assert rel_err(dB.cpu().numpy() - B, B_ref - B) <= 5e-3
+    # the same for positive pairs: every position is a centre with a full window
+    W, LB, UB = random_pos(1000, vocab, 5, 7, drop=0.0, doc_len=1000)
+    A_ref, B_ref = A.copy(), B.copy()
+    oracle.word2vecPos(dim, 1000, 5, W, LB, UB, A_ref, B_ref, lr, 0.0, 1)
+    dA, dB = dev(A), dev(B)
+    assert cumach.word2vecPos(dim, 1000, 5, dev(W), dev(LB), dev(UB), dA, dB, lr, 0.0) == 0
+    assert rel_err(dA.cpu().numpy() - A, A_ref - A) <= 1e-2
+    assert rel_err(dB.cpu().numpy() - B, B_ref - B) <= 1e-2
 
 
 def test_golden_fixtures_on_gpu_conflict_free_prefix(oracle, cumach):

@@ -428,6 +428,11 @@ int w2v_wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64_t 
   W2V_CHECK(cudaGetLastError());
   mark(c, 1, stream);
   W2V_CHECK(cudaStreamSynchronize(stream));
+  {
+    // everything enqueued by earlier calls has finished: did a staged kernel give up?
+    const int fault = w2v::take_stage_fault();
+    if (fault) return fault;
+  }
   c->npairs = c->counts_host[0];
   c->ngroups = c->counts_host[1];
   if (c->npairs > 0) {
@@ -523,7 +528,8 @@ int w2v_dobatch_host(w2v_ctx *c, const int *tokens_host, float *A, float *B, int
   if (err) return err;
   W2V_CHECK(cudaStreamSynchronize(stream));
   if (npairs_host) *npairs_host = c->npairs;
-  return (int)cudaGetLastError();
+  W2V_CHECK(cudaGetLastError());
+  return w2v::take_stage_fault();
 }
 
 int w2v_evalbatch_host(w2v_ctx *c, const int *tokens_host, const float *A, const float *B,

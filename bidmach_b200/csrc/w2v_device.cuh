@@ -201,4 +201,136 @@ __device__ __forceinline__ void column_dots(const Row<NR> (&a)[NWA], const Row<N
   Spread<NWA * NWB>::reduce(p, lane);
 }
 
+// ---------------------------------------------------------------------------
+// Packed fp32x2 arithmetic (sm_100 executes two fp32 FMAs per instruction on a
+// 64-bit register pair) and rows held as such pairs.
+// ---------------------------------------------------------------------------
+typedef unsigned long long u64;
+
+__device__ __forceinline__ u64 fma2(u64 a, u64 b, u64 c) {
+  u64 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ u64 pack2(float x, float y) {
+  u64 d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(x), "f"(y));
+  return d;
+}
+__device__ __forceinline__ void unpack2(u64 v, float &x, float &y) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(v));
+}
+
+template <int NR>
+struct PRow {
+  u64 v[NR][2];  // vector q of the lane = {v[q][0], v[q][1]} = 4 floats
+};
+
+template <int NR>
+__device__ __forceinline__ void prow_zero(PRow<NR> &r) {
+#pragma unroll
+  for (int q = 0; q < NR; q++) r.v[q][0] = r.v[q][1] = 0ull;
+}
+
+// Row from a 16-byte aligned base (global or shared); nvec = dim / 4.
+template <int NR>
+__device__ __forceinline__ void prow_load(PRow<NR> &r, const void *base, int nvec, int lane) {
+  const ulonglong2 *p = reinterpret_cast<const ulonglong2 *>(base);
+#pragma unroll
+  for (int q = 0; q < NR; q++) {
+    const int idx = lane + 32 * q;
+    const ulonglong2 t = (idx < nvec) ? p[idx] : make_ulonglong2(0ull, 0ull);
+    r.v[q][0] = t.x;
+    r.v[q][1] = t.y;
+  }
+}
+
+template <int NR>
+__device__ __forceinline__ float prow_dot_partial(const PRow<NR> &a, const PRow<NR> &b) {
+  u64 s0 = 0ull, s1 = 0ull;
+#pragma unroll
+  for (int q = 0; q < NR; q++) {
+    s0 = fma2(a.v[q][0], b.v[q][0], s0);
+    s1 = fma2(a.v[q][1], b.v[q][1], s1);
+  }
+  float x0, y0, x1, y1;
+  unpack2(s0, x0, y0);
+  unpack2(s1, x1, y1);
+  return (x0 + y0) + (x1 + y1);
+}
+
+// acc += c * x
+template <int NR>
+__device__ __forceinline__ void prow_axpy(PRow<NR> &acc, float c, const PRow<NR> &x) {
+  const u64 cc = pack2(c, c);
+#pragma unroll
+  for (int q = 0; q < NR; q++) {
+    acc.v[q][0] = fma2(cc, x.v[q][0], acc.v[q][0]);
+    acc.v[q][1] = fma2(cc, x.v[q][1], acc.v[q][1]);
+  }
+}
+
+// dst[0..dim) += r   (atomic, 128 bits at a time)
+template <int NR>
+__device__ __forceinline__ void prow_red_to(float *dst, int nvec, int lane, const PRow<NR> &r) {
+#pragma unroll
+  for (int q = 0; q < NR; q++) {
+    const int idx = lane + 32 * q;
+    if (idx < nvec) {
+      float4 v;
+      unpack2(r.v[q][0], v.x, v.y);
+      unpack2(r.v[q][1], v.z, v.w);
+      red_add_v4(dst + 4 * idx, v);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Bulk asynchronous copies (TMA, untiled form) global -> shared, completion
+// signalled on an mbarrier in shared memory.  Addresses and sizes must be
+// multiples of 16 bytes.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_addr(const void *p) {
+  return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(u64 *bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(u64 *bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(u64 *bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Waits for the phase with the given parity, giving up after `limit` polls.
+__device__ __forceinline__ bool mbar_wait_bounded(u64 *bar, unsigned parity, int limit) {
+  for (int spins = 0; spins < limit; spins++)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void bulk_load_row(void *smem_dst, const void *gsrc, unsigned bytes,
+                                              u64 *bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_addr(smem_dst)),
+      "l"(gsrc), "r"(bytes), "r"(smem_addr(bar))
+      : "memory");
+}
+__device__ __forceinline__ void async_proxy_fence() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 }  // namespace w2v

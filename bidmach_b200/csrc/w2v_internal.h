@@ -27,6 +27,7 @@ HotRows hot_rows_at(float *zeroed_buffer, int levels);
 int thread_hot_rows(HotRows *out);
 
 int eval_scratch(EvalScratch **out);
+int take_stage_fault();  // nonzero (cudaErrorLaunchTimeout) if a staged kernel gave up waiting
 int device_sm_count();
 long long launch_count();
 void count_launch(int n);

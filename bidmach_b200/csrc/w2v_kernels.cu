@@ -497,6 +497,227 @@ __global__ void __launch_bounds__(kNegThreads)
   }
 }
 
+// ---------------------------------------------------------------------------
+// Negative pairs, staged: the rows of a column are brought into shared memory
+// by bulk asynchronous copies (one per row, completion counted on an mbarrier)
+// one column ahead of the arithmetic, so a warp never waits for global memory
+// in the middle of a column.  Each warp is its own pipeline: two stages, one
+// being filled while the other is consumed.  The smaller side of the column
+// (NX rows) is held in registers, the larger side (NY rows) is streamed from
+// the stage twice: once for the dot products, once for the updates.
+//
+// Shared memory per warp: 128-byte header (mbarrier per stage, word ids per
+// stage) + 2 stages of (NWA + NWB) rows.
+// ---------------------------------------------------------------------------
+constexpr int kStagedMaxThreads = 256;
+constexpr int kStagedHeader = 256;
+constexpr int kWaitPolls = 1 << 20;  // polls of a stage's barrier before giving up
+
+static __device__ int g_stage_fault;  // set when a stage never arrived; checked by the host
+
+// Columns whose rows all fit in registers (up to 10 rows of 3 vectors per lane)
+// are consumed "resident": the warp moves the whole stage into registers and
+// immediately starts the copies of its next column into the same stage, so one
+// stage per warp is enough.  Wider columns are "streamed": the smaller side is
+// held in registers, the larger side is read from the stage twice (dot
+// products, then updates) while the next column lands in a second stage.
+template <int NWA, int NWB, int NR>
+struct StagedShape {
+  static constexpr bool resident = (NWA + NWB <= 10) && (NR <= 3);
+  static constexpr int stages = resident ? 1 : 2;
+};
+
+__host__ __device__ inline size_t staged_warp_bytes(int nrows_per_col, int dim, int stages) {
+  return kStagedHeader + (size_t)stages * nrows_per_col * dim * sizeof(float);
+}
+
+template <int NWA, int NWB, int NR>
+__global__ void __launch_bounds__(kStagedMaxThreads, 1)
+    neg_update_staged_kernel(int dim, int ncols, const int *__restrict__ ncols_dev, int nwords,
+                             const int *__restrict__ WA, const int *__restrict__ WB, float *A,
+                             float *B, float lrate, float vexp, HotRows hot) {
+  using S = Spread<NWA * NWB>;
+  using Shape = StagedShape<NWA, NWB, NR>;
+  constexpr int NROWS = NWA + NWB;
+  constexpr int NST = Shape::stages;
+  constexpr bool HOLD_B = (NWB <= NWA);     // which side stays in registers when streaming
+  constexpr int NX = HOLD_B ? NWB : NWA;    // held rows
+  constexpr int NY = HOLD_B ? NWA : NWB;    // other rows
+  constexpr int XOFF = HOLD_B ? NWA : 0;    // first held row inside a stage
+  constexpr int YOFF = HOLD_B ? 0 : NWA;    // first other row inside a stage
+  extern __shared__ __align__(128) unsigned char staged_smem[];
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec = dim >> 2;
+  const unsigned rowbytes = (unsigned)dim * 4u;
+  const size_t stage_bytes = (size_t)NROWS * rowbytes;
+  unsigned char *mine = staged_smem + (size_t)warp * staged_warp_bytes(NROWS, dim, NST);
+  u64 *bars = reinterpret_cast<u64 *>(mine);            // [NST]
+  int *ids = reinterpret_cast<int *>(mine + 64);        // [NST][16]
+  unsigned char *stages = mine + kStagedHeader;
+  const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  if (ncols_dev) ncols = *ncols_dev;
+  float *const MX = HOLD_B ? B : A, *const MY = HOLD_B ? A : B;
+  float *const SX = HOLD_B ? hot.shadowB : hot.shadowA, *const SY = HOLD_B ? hot.shadowA : hot.shadowB;
+
+  if (lane == 0)
+    for (int st = 0; st < NST; st++) mbar_init(&bars[st], 1);
+  mbar_init_fence();
+  __syncwarp();
+
+  const int mycols = (gwarp < ncols) ? (ncols - gwarp + nwarps - 1) / nwarps : 0;
+
+  // Starts the copies of a column (word ids in `w`, one per lane) into stage `st`.
+  auto fill = [&](int st, int w) {
+    if (lane < 16) ids[st * 16 + lane] = w;
+    async_proxy_fence();  // earlier reads of this stage come before the new writes
+    const bool want = (lane < NROWS) && (w >= 0);
+    const unsigned wanted = __ballot_sync(kFullMask, want);
+    if (lane == 0) mbar_arrive_expect_tx(&bars[st], (unsigned)__popc(wanted) * rowbytes);
+    __syncwarp();
+    if (want) {
+      const float *src = (lane < NWA ? A : B) + (int64_t)w * dim;
+      bulk_load_row(stages + st * stage_bytes + (size_t)lane * rowbytes, src, rowbytes, &bars[st]);
+    }
+  };
+  auto ids_of = [&](int i) {
+    return column_word<NWA, NWB>(WA, WB, gwarp + (int64_t)i * nwarps, nwords, lane);
+  };
+
+  if (mycols > 0) fill(0, ids_of(0));
+  int ahead = (mycols > 1) ? ids_of(1) : -1;  // word ids of the next column to fill
+
+  for (int i = 0; i < mycols; i++) {
+    const int st = i % NST;
+    if (NST == 2 && i + 1 < mycols) {
+      fill(st ^ 1, ahead);
+      if (i + 2 < mycols) ahead = ids_of(i + 2);
+    }
+    if (!mbar_wait_bounded(&bars[st], (unsigned)(i / NST) & 1u, kWaitPolls)) {
+      // the copies never completed: report, give a stage that is still being
+      // filled a bounded chance to land so nothing is in flight into this
+      // block, and stop
+      if (lane == 0) atomicExch(&g_stage_fault, 1);
+      if (NST == 2 && i + 1 < mycols)
+        mbar_wait_bounded(&bars[st ^ 1], (unsigned)((i + 1) / NST) & 1u, kWaitPolls);
+      return;
+    }
+    const int myw = (lane < 16) ? ids[st * 16 + lane] : -1;
+    const float mysc = (myw >= 0) ? freq_scale(myw, vexp) : 0.f;
+    const unsigned char *stage = stages + st * stage_bytes;
+
+    PRow<NR> X[NX];
+    int wx[NX];
+#pragma unroll
+    for (int x = 0; x < NX; x++) {
+      wx[x] = __shfl_sync(kFullMask, myw, XOFF + x);
+      if (wx[x] >= 0)
+        prow_load(X[x], stage + (size_t)(XOFF + x) * rowbytes, nvec, lane);
+      else
+        prow_zero(X[x]);
+    }
+    float p[NWA * NWB];
+
+    if (Shape::resident) {
+      PRow<NR> Y[NY];
+      int wy[NY];
+#pragma unroll
+      for (int y = 0; y < NY; y++) {
+        wy[y] = __shfl_sync(kFullMask, myw, YOFF + y);
+        if (wy[y] >= 0)
+          prow_load(Y[y], stage + (size_t)(YOFF + y) * rowbytes, nvec, lane);
+        else
+          prow_zero(Y[y]);
+      }
+      __syncwarp();  // the stage is in registers: refill it with the next column right away
+      if (i + 1 < mycols) {
+        fill(0, ahead);
+        if (i + 2 < mycols) ahead = ids_of(i + 2);
+      }
+#pragma unroll
+      for (int y = 0; y < NY; y++)
+#pragma unroll
+        for (int x = 0; x < NX; x++)
+          p[HOLD_B ? (y * NWB + x) : (x * NWB + y)] = prow_dot_partial(X[x], Y[y]);
+      S::reduce(p, lane);
+#pragma unroll
+      for (int q = 0; q < S::FIN; q++) p[q] = -lrate * sigmoid_guard(p[q]);
+      float g[NWA * NWB];
+#pragma unroll
+      for (int idx = NWA * NWB - 1; idx >= 0; idx--)
+        g[idx] = __shfl_sync(kFullMask, p[S::slot_of(idx)], S::lane_of(idx));
+#pragma unroll
+      for (int y = 0; y < NY; y++) {
+        const float sy = __shfl_sync(kFullMask, mysc, YOFF + y);
+        PRow<NR> d;
+        prow_zero(d);
+#pragma unroll
+        for (int x = 0; x < NX; x++) prow_axpy(d, sy * g[HOLD_B ? (y * NWB + x) : (x * NWB + y)], X[x]);
+        if (wy[y] >= 0) prow_red_to(update_target(MY, SY, hot.limit, wy[y], dim, gwarp), nvec, lane, d);
+      }
+#pragma unroll
+      for (int x = 0; x < NX; x++) {
+        const float sxx = __shfl_sync(kFullMask, mysc, XOFF + x);
+        PRow<NR> d;
+        prow_zero(d);
+#pragma unroll
+        for (int y = 0; y < NY; y++) prow_axpy(d, sxx * g[HOLD_B ? (y * NWB + x) : (x * NWB + y)], Y[y]);
+        if (wx[x] >= 0) prow_red_to(update_target(MX, SX, hot.limit, wx[x], dim, gwarp), nvec, lane, d);
+      }
+    } else {
+      float sx[NX];
+#pragma unroll
+      for (int x = 0; x < NX; x++) sx[x] = __shfl_sync(kFullMask, mysc, XOFF + x);
+#pragma unroll
+      for (int y = 0; y < NY; y++) {
+        const int wy = __shfl_sync(kFullMask, myw, YOFF + y);
+        PRow<NR> Y;
+        if (wy >= 0)
+          prow_load(Y, stage + (size_t)(YOFF + y) * rowbytes, nvec, lane);
+        else
+          prow_zero(Y);
+#pragma unroll
+        for (int x = 0; x < NX; x++)
+          p[HOLD_B ? (y * NWB + x) : (x * NWB + y)] = prow_dot_partial(X[x], Y);
+      }
+      S::reduce(p, lane);
+#pragma unroll
+      for (int q = 0; q < S::FIN; q++) p[q] = -lrate * sigmoid_guard(p[q]);
+      float g[NWA * NWB];
+#pragma unroll
+      for (int idx = NWA * NWB - 1; idx >= 0; idx--)
+        g[idx] = __shfl_sync(kFullMask, p[S::slot_of(idx)], S::lane_of(idx));
+      PRow<NR> dX[NX];
+#pragma unroll
+      for (int x = 0; x < NX; x++) prow_zero(dX[x]);
+#pragma unroll
+      for (int y = 0; y < NY; y++) {
+        const int wy = __shfl_sync(kFullMask, myw, YOFF + y);
+        const float sy = __shfl_sync(kFullMask, mysc, YOFF + y);
+        PRow<NR> Y, dY;
+        if (wy >= 0)
+          prow_load(Y, stage + (size_t)(YOFF + y) * rowbytes, nvec, lane);
+        else
+          prow_zero(Y);
+        prow_zero(dY);
+#pragma unroll
+        for (int x = 0; x < NX; x++) {
+          const float gxy = g[HOLD_B ? (y * NWB + x) : (x * NWB + y)];
+          prow_axpy(dY, sy * gxy, X[x]);
+          prow_axpy(dX[x], sx[x] * gxy, Y);
+        }
+        if (wy >= 0) prow_red_to(update_target(MY, SY, hot.limit, wy, dim, gwarp), nvec, lane, dY);
+      }
+#pragma unroll
+      for (int x = 0; x < NX; x++)
+        if (wx[x] >= 0)
+          prow_red_to(update_target(MX, SX, hot.limit, wx[x], dim, gwarp), nvec, lane, dX[x]);
+      __syncwarp();  // every lane is done with this stage before it is refilled
+    }
+  }
+}
+
 template <int NWA, int NWB, int NR>
 __global__ void __launch_bounds__(kNegThreads)
     neg_eval_kernel(int dim, int ncols, const int *__restrict__ ncols_dev,
@@ -815,6 +1036,43 @@ int pos_eval_async(int dim, int ncols, const int *ncols_dev, int skip, const int
   return (int)cudaGetLastError();
 }
 
+static bool neg_staged_enabled() {
+  static bool on = [] {
+    const char *e = getenv("W2V_NEG_IMPL");
+    return !(e && e[0] == 'r');  // "reg" selects the register-resident kernel
+  }();
+  return on;
+}
+
+template <int NWA, int NWB, int NR>
+static cudaError_t launch_neg_staged(int grid, int warps, size_t smem, cudaStream_t stream, int dim,
+                                     int ncols, const int *ncols_dev, int nwords, const int *WA,
+                                     const int *WB, float *A, float *B, float lrate, float vexp,
+                                     const HotRows &hot) {
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(neg_update_staged_kernel<NWA, NWB, NR>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  neg_update_staged_kernel<NWA, NWB, NR><<<grid, warps * 32, smem, stream>>>(
+      dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot);
+  return cudaSuccess;
+}
+
+// Reads and clears the flag a staged kernel raises when a stage never arrived.
+// Call after the stream has been synchronised.
+int take_stage_fault() {
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_stage_fault, sizeof(int));
+  if (e != cudaSuccess) return (int)e;
+  if (v) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_stage_fault, &zero, sizeof(int));
+    return (int)cudaErrorLaunchTimeout;
+  }
+  return 0;
+}
+
 template <int NWA, int NWB>
 static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int nwords,
                         const int *WA, const int *WB, float *A, float *B, float lrate, float vexp,
@@ -828,7 +1086,23 @@ static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int
   // rows of a column live in registers: (NWA + NWB) * nr vectors per lane, which
   // fits for up to 10 rows of 3 vectors or 15 rows of 2
   constexpr int kMaxNr = (NWA + NWB <= 10) ? 4 : 2;
-  if (vector_ok(dim, A, B) && nr <= kMaxNr) {
+  // staged update: as many warps per block (one block per SM) as shared memory holds
+  const int staged_stages = ((NWA + NWB <= 10) && nr <= 3) ? 1 : 2;  // StagedShape<...>::stages
+  const size_t per_warp = staged_warp_bytes(NWA + NWB, dim, staged_stages);
+  const int staged_warps = (int)std::min<size_t>(kStagedMaxThreads / 32, (227 * 1024) / per_warp);
+  if (!eval && vector_ok(dim, A, B) && nr <= 4 && staged_warps >= 2 && neg_staged_enabled()) {
+    const size_t smem = per_warp * staged_warps;
+    const int grid = std::max(1, std::min(device_sm_count(), (ncols + staged_warps - 1) / staged_warps));
+    cudaError_t e = cudaSuccess;
+    switch (nr) {
+      case 1: e = launch_neg_staged<NWA, NWB, 1>(grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot); break;
+      case 2: e = launch_neg_staged<NWA, NWB, 2>(grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot); break;
+      case 3: e = launch_neg_staged<NWA, NWB, 3>(grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot); break;
+      default: e = launch_neg_staged<NWA, NWB, 4>(grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot); break;
+    }
+    if (e != cudaSuccess) return (int)e;
+    fold_hot_rows(dim, hot, A, B, stream);
+  } else if (vector_ok(dim, A, B) && nr <= kMaxNr) {
     const int grid = grid_for(ncols, kNegThreads, 8);
     if (eval) {
       switch (nr) {
@@ -906,7 +1180,9 @@ static int finish_sync(int launch_err) {
   if (launch_err) return launch_err;
   cudaError_t e = cudaStreamSynchronize(cudaStreamPerThread);
   if (e != cudaSuccess) return (int)e;
-  return (int)cudaGetLastError();
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  return w2v::take_stage_fault();
 }
 
 extern "C" {

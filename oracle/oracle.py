@@ -410,3 +410,48 @@ class CpuWord2Vec:
         eneg = word2vecEvalNeg(o["dim"], WA.shape[0], o["nneg"], o["nreuse"], WA, WB, self.A,
                                self.B, self.nthreads)
         return eval_score(epos, eneg, o["nneg"], WB.size, o.get("eqPosNeg", False))
+
+
+def _draws(rng, n, nskip, nneg, nreuse):
+    """Uniform draws one CPU minibatch consumes (numpy generator; the reference
+    takes them from BIDMat's RNG, whose stream is not part of the checkout)."""
+    cap = 2 * nskip * n
+    return (rng.random(n, dtype=np.float32), rng.random(n, dtype=np.float32), rng.random(cap),
+            rng.random(cap // nreuse * nneg + nneg, dtype=np.float32))
+
+
+def cpu_learner_train(tokens, opts, batch_size, A, B, npasses=1, eval_step=11, seed=0, nthreads=1,
+                      impl="port"):
+    """Learner.nextPass (Learner.scala:173-252) driving the CPU model: returns the
+    eval-step scores.  Short last minibatches are handed over and skipped by the
+    model, as in the reference (networks/Word2Vec.scala:169,194)."""
+    model = CpuWord2Vec(opts, A, B, nthreads, impl)
+    rng = np.random.default_rng(seed)
+    o = model.o
+    here, scores = 0, []
+    nb = -(-tokens.shape[0] // batch_size)
+    for _ in range(npasses):
+        for istep in range(nb):
+            mb = tokens[istep * batch_size:(istep + 1) * batch_size]
+            here += batch_size
+            has_next = istep + 1 < nb
+            if mb.shape[0] != batch_size:
+                continue
+            d = _draws(rng, batch_size, o["nskip"], o["nneg"], o["nreuse"])
+            if is_eval_step(istep, eval_step, has_next):
+                scores.append(model.evalbatch(mb, *d))
+            else:
+                model.dobatch(mb, here, *d)
+    return scores
+
+
+def cpu_learner_predict(tokens, opts, batch_size, A, B, seed=1, nthreads=1):
+    """Learner.predict (Learner.scala:322-391): score of every full minibatch."""
+    model = CpuWord2Vec(opts, A, B, nthreads, "port")
+    rng = np.random.default_rng(seed)
+    o = model.o
+    out = []
+    for k in range(tokens.shape[0] // batch_size):
+        mb = tokens[k * batch_size:(k + 1) * batch_size]
+        out.append(model.evalbatch(mb, *_draws(rng, batch_size, o["nskip"], o["nneg"], o["nreuse"])))
+    return out

@@ -1,0 +1,66 @@
+"""End-to-end parity: training with the reference's minibatch schedule on the
+GPU path and on the CPU path (reference C kernels where built, else the port)
+from the same initial model must reach the same held-out log-likelihood per
+word within 1 %.  The two runs draw different random numbers (the reference's
+RNG streams are not reproducible outside BIDMat), so this is a statistical
+comparison, as BASELINE's end-to-end criterion is."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_pair(oracle, vocab, dim, ntrain, ntest, batch, corpus, seed=11, lrate=1e-3):
+    from bidmach_b200 import Learner, MatSource, Word2Vec
+    from bidmach_b200.learner import LearnerOpts
+    from bidmach_b200.word2vec import Opts
+    train, test = corpus(ntrain, 1), corpus(ntest, 2)
+    o = Opts(dim=dim, vocabSize=vocab, nskip=5, nneg=5, nreuse=5, lrate=lrate, texp=0.5, vexp=0.5,
+             wsample=1e-4, seed=seed)
+    model = Word2Vec(o)
+    learner = Learner(MatSource(train, batch), model, LearnerOpts(npasses=1, evalStep=11))
+    learner.train()
+    gpu_scores = learner.predict(MatSource(test, batch))
+    gpu_ll = float(np.mean(gpu_scores))
+
+    B = oracle.library_init_model(seed, dim, vocab)          # same start as the GPU run
+    A = np.zeros_like(B)
+    od = dict(dim=dim, vocabSize=vocab, nskip=5, nneg=5, nreuse=5, lrate=lrate, texp=0.5, vexp=0.5,
+              wsample=1e-4, wexpt=0.75)
+    impl = "reference" if oracle.have_reference() else "port"
+    threads = min(16, os.cpu_count() or 1)
+    cpu_eval = oracle.cpu_learner_train(train, od, batch, A, B, npasses=1, eval_step=11, seed=3,
+                                        nthreads=threads, impl=impl)
+    cpu_ll = float(np.mean(oracle.cpu_learner_predict(test, od, batch, A, B, seed=4, nthreads=threads)))
+    return gpu_ll, cpu_ll, learner.reslist, cpu_eval
+
+
+def test_config1_zipf_heldout_ll_within_one_percent(oracle):
+    """BASELINE configs[0] at a fifth of its length: vocab 10k, dim 100, Zipf(1.0)
+    tokens, window 5, 5 negatives, 100k-token minibatches, one pass."""
+    from bidmach_b200.corpus import zipf_corpus
+    vocab, dim, batch = 10_000, 100, 100_000
+    gpu_ll, cpu_ll, gpu_eval, cpu_eval = _run_pair(
+        oracle, vocab, dim, 2_000_000, 300_000, batch,
+        lambda n, s: zipf_corpus(vocab, n, 1.0, seed=s, doc_len=1000), lrate=0.01)
+    assert len(gpu_eval) == len(cpu_eval) == 3                 # isteps 1, 12 and the last
+    assert gpu_ll < 0 and cpu_ll < 0
+    assert abs(gpu_ll - cpu_ll) <= 0.01 * abs(cpu_ll), (gpu_ll, cpu_ll)
+    # the untrained model scores 2*log(1/2) per pair; training must have moved away from it
+    assert gpu_ll > 2 * np.log(0.5) + 0.03
+
+
+def test_topic_corpus_heldout_ll_within_one_percent(oracle):
+    """Same comparison on a corpus with co-occurrence structure (the topic-model
+    generator of BASELINE configs[3], scaled down)."""
+    from bidmach_b200.corpus import TopicCorpus
+    vocab, dim, batch = 5_000, 100, 50_000
+    tc = TopicCorpus(vocab, 50, s=1.07, alpha=0.1, doc_len=1000, seed=5, rank_sample_docs=2000)
+    gpu_ll, cpu_ll, _, _ = _run_pair(
+        oracle, vocab, dim, 1_500_000, 200_000, batch,
+        lambda n, s: tc.tokens(s * 100_000, n // 1000), lrate=0.002)
+    assert abs(gpu_ll - cpu_ll) <= 0.01 * abs(cpu_ll), (gpu_ll, cpu_ll)
+    assert gpu_ll > 2 * np.log(0.5) + 0.1

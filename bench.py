@@ -69,7 +69,7 @@ class ClockSampler:
         self.t0 = self.t1 = None
 
     def window_open(self):
-        self.t0 = time.monotonic()
+        self.t0, self.t1 = time.monotonic(), None
 
     def window_close(self):
         self.t1 = time.monotonic()
@@ -90,17 +90,23 @@ class ClockSampler:
 
     def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+
+    def summary(self):
+        """Clocks and throttle reasons of the samples inside the last window."""
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        inside = [r for (t, r) in self.rows if self.t0 is None or (self.t0 <= t <= (self.t1 or t))]
+        rows = list(self.rows)
+        inside = [r for (t, r) in rows if self.t0 is None or (self.t0 <= t <= (self.t1 or t))]
         if not inside:  # region shorter than the sampling period: take the nearest sample
-            inside = [r for (_, r) in self.rows[-1:]]
+            inside = [r for (_, r) in rows[-1:]]
         for r in inside:
             try:
                 sm.append(float(r[1]))
@@ -231,6 +237,8 @@ def run_ours(args):
     lib = _lib.load()
     w = WORKLOAD
     N = w["ntokens"]
+    sampler = ClockSampler(local)   # runs for the whole job; each timed region reads its own window
+    sampler.start()
 
     o = Opts(dim=w["dim"], vocabSize=w["vocab"], nskip=w["nskip"], nneg=w["nneg"], nreuse=w["nreuse"],
              lrate=w["lrate"], texp=w["texp"], vexp=w["vexp"], wsample=w["wsample"], seed=17 + rank)
@@ -258,6 +266,12 @@ def run_ours(args):
         pos = first_pos
         for s in range(nsteps):
             pos += N
+            if args.mode == "eval":
+                if host_path:
+                    model.evalbatchg([host[s % POOL].numpy()], 0, pos)
+                else:
+                    model.evalbatch([devt[s % POOL]], 0, pos)
+                continue
             if host_path:
                 model.dobatchg([host[s % POOL].numpy()], 0, pos)
             else:
@@ -267,8 +281,6 @@ def run_ours(args):
         return pos
 
     def timed(host_path, pos):
-        sampler = ClockSampler(local)
-        sampler.start()
         pos = run_steps(args.warmup, host_path, pos)
         sync_all()
         lib.w2v_set_timing(model._ctx, 0 if host_path else 1)
@@ -280,7 +292,7 @@ def run_ours(args):
         e1.record(stream)
         sync_all()
         sampler.window_close()
-        clocks = sampler.stop()
+        clocks = sampler.summary()
         ms = e0.elapsed_time(e1)
         t = torch.tensor([ms], device="cuda", dtype=torch.float64)
         if world > 1:
@@ -292,6 +304,7 @@ def run_ours(args):
     tm = _lib.W2VTiming()
     lib.w2v_get_timing(model._ctx, tm)
     ms_e2e, _, clocks_e2e, pos = timed(True, pos)
+    sampler.stop()
 
     if rank != 0:
         if world > 1:
@@ -299,6 +312,27 @@ def run_ours(args):
         return
 
     K = args.steps
+    if args.mode == "eval":
+        nb = max(1, tm.eval_batches)
+        row = 4 * w["dim"]
+        eg, ep = tm.eval_groups / nb, tm.eval_pairs / nb
+        line = {"metric": "SGNS eval (log-likelihood scoring) words/sec at vocab 1M dim 300",
+                "value": world * N * K / (ms_dev * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K,
+                "warmup": args.warmup, "ms_per_step": ms_dev / K, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": config_dict(args, extra={"workload": "configs[2]: scoring path, fixed random matrices"}),
+                "e2e": {"value": world * N * K / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 8 * N,
+                        "d2h_bytes_per_step": 8},
+                "gpu_launches": int(launches),
+                "phases": {"prep_ms": tm.prep_ms / nb, "permute_ms": tm.permute_ms / nb,
+                           "evalpos_ms": tm.evalpos_ms / nb, "evalneg_ms": tm.evalneg_ms / nb,
+                           "evalneg_algorithmic_gbs": eg * (w["nneg"] + w["nreuse"]) * row / (tm.evalneg_ms / nb) / 1e6,
+                           "evalpos_algorithmic_gbs": (N + ep) * row / (tm.evalpos_ms / nb) / 1e6},
+                "clocks": clocks}
+        print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     value = world * N * K / (ms_dev * 1e-3)
     e2e_value = world * N * K / (ms_e2e * 1e-3)
     peak, peak_kind = measured_peak_gbs()
@@ -312,7 +346,7 @@ def run_ours(args):
     # positive kernel, same accounting: (centres-with-pairs + pairs) rows read and written;
     # every token is kept in this workload, so centres ~ tokens
     pos_bytes = 2.0 * (N + pairs) * row
-    roofline = {"bound": "hbm", "kernel": "neg_update_kernel<5,5,3>", "achieved": achieved, "peak": peak,
+    roofline = {"bound": "hbm", "kernel": "neg_update_staged_kernel<5,5,3>", "achieved": achieved, "peak": peak,
                 "peak_kind": peak_kind, "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
                 "traffic": NEG_DRAM_TRAFFIC_BYTES, "algorithmic_bytes_per_launch": neg_bytes,
                 "avg_launch_ms": neg_s * 1e3}
@@ -352,11 +386,13 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=48)
+    ap.add_argument("--steps", type=int, default=96)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sync-every", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--mode", default="train", choices=["train", "eval"],
+                    help="eval: time the scoring path (evalbatch) instead of the update path")
     ap.add_argument("--vocab", type=int, default=None, help="override the workload's vocabulary (profiling)")
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per minibatch (profiling)")
     args = ap.parse_args()

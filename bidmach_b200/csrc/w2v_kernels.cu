@@ -137,22 +137,22 @@ struct PosBlocksOf {
 // with `own` after the spreading reduction: lane Spread::lane_of(c) holds dot c.
 template <int NR, int kChunk>
 __device__ __forceinline__ float chunk_dots(unsigned &todo, int (&src)[kChunk],
-                                            Row<NR> (&rows)[kChunk], const Row<NR> &own,
+                                            PRow<NR> (&rows)[kChunk], const PRow<NR> &own,
                                             const float *M, int wnb, int dim, int nvec, int lane) {
 #pragma unroll
   for (int c = 0; c < kChunk; c++) {
     if (todo) {
       src[c] = __ffs(todo) - 1;
       todo &= todo - 1;
-      row_load(rows[c], M, __shfl_sync(kFullMask, wnb, src[c]), dim, nvec, lane);
+      prow_load(rows[c], M + (int64_t)__shfl_sync(kFullMask, wnb, src[c]) * dim, nvec, lane);
     } else {
       src[c] = -1;
-      row_zero(rows[c]);
+      prow_zero(rows[c]);
     }
   }
   float p[kChunk];
 #pragma unroll
-  for (int c = 0; c < kChunk; c++) p[c] = row_dot_partial(own, rows[c]);
+  for (int c = 0; c < kChunk; c++) p[c] = prow_dot_partial(own, rows[c]);
   Spread<kChunk>::reduce(p, lane);
   return p[0];
 }
@@ -189,11 +189,11 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
                       HotRows hot) {
   constexpr int kChunk = ChunkOf<NR>::value;
   static_assert(Spread<kChunk>::FIN == 1, "one total per lane expected");
-  extern __shared__ float4 ring_storage[];
+  extern __shared__ ulonglong2 ring_storage[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = dim >> 2;
   const int slots = 2 * skip + 1;
-  float4 *ring = ring_storage + (size_t)warp * slots * nvec;
+  ulonglong2 *ring = ring_storage + (size_t)warp * slots * nvec;
   const unsigned gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const unsigned nwarps = (gridDim.x * blockDim.x) >> 5;
   if (ncols_dev) ncols = *ncols_dev;
@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
     if ((dirty >> slot) & 1u) {
       dirty &= ~(1u << slot);
       float *dst = update_target(B, hot.shadowB, hot.limit, W[u], dim, gwarp);
-      const float4 *sp = ring + slot * nvec;
+      const float4 *sp = reinterpret_cast<const float4 *>(ring + slot * nvec);
 #pragma unroll
       for (int q = 0; q < NR; q++) {
         const int idx = lane + 32 * q;
@@ -230,12 +230,12 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
         const int sid = (lane == 31) ? wt : nb.word;
         const float sc = (sid >= 0) ? freq_scale(sid, vexp) : 0.f;
         const float sa = __shfl_sync(kFullMask, sc, 31);
-        Row<NR> a, da;
-        row_load(a, A, wt, dim, nvec, lane);
-        row_zero(da);
+        PRow<NR> a, da;
+        prow_load(a, A + (int64_t)wt * dim, nvec, lane);
+        prow_zero(da);
         while (todo) {
           int src[kChunk];
-          Row<NR> rows[kChunk];
+          PRow<NR> rows[kChunk];
           const float dot = chunk_dots(todo, src, rows, a, B, nb.word, dim, nvec, lane);
           const float mine = lrate * (1.0f - sigmoid_guard(dot));
 #pragma unroll
@@ -243,28 +243,26 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
             if (src[c] < 0) continue;
             const float g = __shfl_sync(kFullMask, mine, Spread<kChunk>::lane_of(c));
             const float sb = __shfl_sync(kFullMask, sc, src[c]);
-            row_axpy(da, sa * g, rows[c]);
+            prow_axpy(da, sa * g, rows[c]);
             // context side: slot(u) += (sb * g) * a
             const int slot = (t + src[c] - skip - base) % slots;
-            float4 *sp = ring + slot * nvec;
-            const float coef = sb * g;
+            ulonglong2 *sp = ring + slot * nvec;
+            const u64 coef = pack2(sb * g, sb * g);
             const bool pending = (dirty >> slot) & 1u;
             dirty |= 1u << slot;
 #pragma unroll
             for (int q = 0; q < NR; q++) {
               const int idx = lane + 32 * q;
               if (idx < nvec) {
-                float4 v = pending ? sp[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
-                v.x = fmaf(coef, a.v[q].x, v.x);
-                v.y = fmaf(coef, a.v[q].y, v.y);
-                v.z = fmaf(coef, a.v[q].z, v.z);
-                v.w = fmaf(coef, a.v[q].w, v.w);
+                ulonglong2 v = pending ? sp[idx] : make_ulonglong2(0ull, 0ull);
+                v.x = fma2(coef, a.v[q][0], v.x);
+                v.y = fma2(coef, a.v[q][1], v.y);
                 sp[idx] = v;
               }
             }
           }
         }
-        row_red_to(update_target(A, hot.shadowA, hot.limit, wt, dim, gwarp), nvec, lane, da);
+        prow_red_to(update_target(A, hot.shadowA, hot.limit, wt, dim, gwarp), nvec, lane, da);
       }
     }
     // no later centre of this warp reaches position t - skip
@@ -322,11 +320,11 @@ __global__ void __launch_bounds__(kPosThreads)
     const Neighbour nb = look_at_neighbour(W, t, lbt, ubt, skip, ncols, lane);
     unsigned todo = __ballot_sync(kFullMask, nb.t_is_centre);
     if (todo == 0) continue;
-    Row<NR> own;
-    row_load(own, A, wt, dim, nvec, lane);
+    PRow<NR> own;
+    prow_load(own, A + (int64_t)wt * dim, nvec, lane);
     while (todo) {
       int src[kChunk];
-      Row<NR> rows[kChunk];
+      PRow<NR> rows[kChunk];
       const float dot = chunk_dots(todo, src, rows, own, B, nb.word, dim, nvec, lane);
       // the lane that holds a pair's dot product scores it (networks/Word2Vec.scala:995)
 #pragma unroll

@@ -45,9 +45,9 @@ POOL = 4             # distinct minibatches per rank, cycled
 CPU_SAMPLE = 500_000  # tokens of one minibatch the CPU arms process per step
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the negative-update
-# kernel on this workload, from an ncu capture (see the summary under profiles/);
-# None until a capture exists.
-NEG_DRAM_TRAFFIC_BYTES = None
+# kernel on this workload (6.63 GB read + 6.79 GB written), from a one-pass ncu
+# capture of the full-size workload; see profiles/update_kernels_zipf_vocab1M_dim300.md.
+NEG_DRAM_TRAFFIC_BYTES = 13.42e9
 
 
 def measured_peak_gbs():

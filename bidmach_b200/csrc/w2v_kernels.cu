@@ -507,7 +507,7 @@ __global__ void __launch_bounds__(kNegThreads)
 // Shared memory per warp: 128-byte header (mbarrier per stage, word ids per
 // stage) + 2 stages of (NWA + NWB) rows.
 // ---------------------------------------------------------------------------
-constexpr int kStagedMaxThreads = 256;
+constexpr int kStagedMaxThreads = 384;
 constexpr int kStagedHeader = 256;
 constexpr int kWaitPolls = 1 << 20;  // polls of a stage's barrier before giving up
 

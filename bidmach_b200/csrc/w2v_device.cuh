@@ -28,6 +28,8 @@ __device__ __forceinline__ float sigmoid_guard(float x) {
 // jni/src/DNN127.cu:145,149 forms the same value from the row offset).
 __device__ __forceinline__ float freq_scale(int id, float vexp) {
   if (vexp == 0.0f) return 1.0f;
+  if (vexp == 0.5f) return sqrtf((float)(1 + id));  // the reference's default exponent
+  if (vexp == 1.0f) return (float)(1 + id);
   return powf((float)(1 + id), vexp);
 }
 

@@ -53,6 +53,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <type_traits>
 
 #include "w2v_device.cuh"
 #include "w2v_internal.h"
@@ -233,15 +234,18 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
         PRow<NR> a, da;
         prow_load(a, A + (int64_t)wt * dim, nvec, lane);
         prow_zero(da);
-        while (todo) {
-          int src[kChunk];
-          PRow<NR> rows[kChunk];
-          const float dot = chunk_dots(todo, src, rows, a, B, nb.word, dim, nvec, lane);
+        // the contexts are taken kChunk at a time; a remainder of one or two
+        // gets a narrower pass so that it does not pay for kChunk rows
+        auto take = [&](auto width) {
+          constexpr int CH = decltype(width)::value;
+          int src[CH];
+          PRow<NR> rows[CH];
+          const float dot = chunk_dots<NR, CH>(todo, src, rows, a, B, nb.word, dim, nvec, lane);
           const float mine = lrate * (1.0f - sigmoid_guard(dot));
 #pragma unroll
-          for (int c = 0; c < kChunk; c++) {
+          for (int c = 0; c < CH; c++) {
             if (src[c] < 0) continue;
-            const float g = __shfl_sync(kFullMask, mine, Spread<kChunk>::lane_of(c));
+            const float g = __shfl_sync(kFullMask, mine, Spread<CH>::lane_of(c));
             const float sb = __shfl_sync(kFullMask, sc, src[c]);
             prow_axpy(da, sa * g, rows[c]);
             // context side: slot(u) += (sb * g) * a
@@ -261,6 +265,12 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
               }
             }
           }
+        };
+        while (todo) {
+          if (kChunk > 2 && __popc(todo) <= 2)
+            take(std::integral_constant<int, 2>());
+          else
+            take(std::integral_constant<int, kChunk>());
         }
         prow_red_to(update_target(A, hot.shadowA, hot.limit, wt, dim, gwarp), nvec, lane, da);
       }

@@ -20,6 +20,8 @@ struct HotRows {
   float *shadowA;
   float *shadowB;
   int limit;
+  int rmax;        // replicas of id 0 (a power of two); level L ids have rmax >> L
+  int fold_every;  // in-kernel folding period (0 = only the fold kernel folds)
 };
 size_t hot_rows_bytes();
 int hot_levels_default();

@@ -43,9 +43,13 @@
 //
 // Hot rows: under a Zipf-like draw a handful of word ids receive a large share
 // of all updates, and atomic adds to one address serialise in L2.  Updates to
-// the most frequent ids (id + 1 < 2^levels; ids are frequency ranks) are
-// therefore spread over up to 64 replica rows in a small side buffer and
-// folded into the model by a tiny kernel that follows the update kernel.
+// the most frequent ids (id + 1 < 2^levels, 15 ids by default; ids are
+// frequency ranks) are therefore spread over replica rows in a small side
+// buffer (16 for id 0, 8 for ids 1-2, 4 for ids 3-6, 2 for ids 7-14).  While
+// the update kernel runs, every warp periodically moves the contents of one
+// replica row into the model ("continuous folding"), so that readers of a hot
+// row see its updates within microseconds, as they would with plain atomics;
+// a tiny kernel folds what is left after the update kernel.
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -81,12 +85,13 @@ __device__ __forceinline__ int window_word(const int *__restrict__ W, int i, int
 
 // Destination of an update to row w of matrix M: the row itself, or for a hot
 // id one of its replica rows in the side buffer (picked by the warp's number).
-__device__ __forceinline__ float *update_target(float *M, float *shadow, int hot_limit, int w,
+__device__ __forceinline__ float *update_target(float *M, float *shadow, const HotRows &hot, int w,
                                                 int dim, unsigned pick) {
-  if (w + 1 < hot_limit) {
+  if (w + 1 < hot.limit) {
+    // level L holds the 2^L ids with 2^L <= id + 1 < 2^(L+1), each with rmax >> L replicas
     const int level = 31 - __clz(w + 1);
-    const int reps = 64 >> level;
-    const int row = 64 * level + (w + 1 - (1 << level)) * reps + (int)(pick & (unsigned)(reps - 1));
+    const int reps = hot.rmax >> level;
+    const int row = hot.rmax * level + (w + 1 - (1 << level)) * reps + (int)(pick & (unsigned)(reps - 1));
     return shadow + (int64_t)row * dim;
   }
   return M + (int64_t)w * dim;
@@ -101,6 +106,42 @@ __device__ __forceinline__ void row_red_to(float *p, int nvec, int lane, const R
   }
 }
 
+// Continuous folding.  Every so often a warp takes one replica row (round
+// robin over all of them), atomically swaps its contents for zeros and adds
+// what it took to the model row the replica stands for.  Replicas therefore
+// hold only the last few microseconds of updates, and readers of a hot row see
+// its updates almost as soon as they would without replicas; what is left at
+// the end of the kernel is collected by hot_fold_kernel.
+__device__ __forceinline__ void exch_zero_v4(float *addr, u64 &lo, u64 &hi) {
+  // two 64-bit exchanges: every float is independent, so 8-byte atomicity is enough
+  lo = atomicExch(reinterpret_cast<u64 *>(addr), 0ull);
+  hi = atomicExch(reinterpret_cast<u64 *>(addr) + 1, 0ull);
+}
+
+__device__ __forceinline__ void fold_one_replica(const HotRows &hot, float *A, float *B, int dim,
+                                                 int nvec, int lane, unsigned turn) {
+  const int levels = 31 - __clz(hot.limit);
+  const int per_matrix = hot.rmax * levels;
+  const int r = (int)(turn % (unsigned)(2 * per_matrix));
+  const bool in_b = r >= per_matrix;
+  const int row = in_b ? r - per_matrix : r;
+  const int level = row / hot.rmax, reps = hot.rmax >> level;
+  const int id = (1 << level) - 1 + (row - level * hot.rmax) / reps;
+  float *src = (in_b ? hot.shadowB : hot.shadowA) + (int64_t)row * dim;
+  float *dst = (in_b ? B : A) + (int64_t)id * dim;
+  for (int idx = lane; idx < nvec; idx += 32) {
+    u64 lo, hi;
+    exch_zero_v4(src + 4 * idx, lo, hi);
+    if (lo | hi) {  // untouched replicas (also those of ids beyond the vocabulary) stay out of the model
+      float4 v;
+      unpack2(lo, v.x, v.y);
+      unpack2(hi, v.z, v.w);
+      red_add_v4(dst + 4 * idx, v);
+    }
+  }
+}
+
+
 // Folds the replica rows of the hot ids back into the model and clears them.
 // grid = (hot ids, 2 matrices).
 __global__ void hot_fold_kernel(int dim, HotRows hot, float *A, float *B) {
@@ -108,8 +149,8 @@ __global__ void hot_fold_kernel(int dim, HotRows hot, float *A, float *B) {
   float *M = blockIdx.y ? B : A;
   float *S = blockIdx.y ? hot.shadowB : hot.shadowA;
   const int level = 31 - __clz(h + 1);
-  const int reps = 64 >> level;
-  float *base = S + (int64_t)(64 * level + (h + 1 - (1 << level)) * reps) * dim;
+  const int reps = hot.rmax >> level;
+  float *base = S + (int64_t)(hot.rmax * level + (h + 1 - (1 << level)) * reps) * dim;
   for (int c = threadIdx.x; c < dim; c += blockDim.x) {
     float sum = 0.f;
     for (int r = 0; r < reps; r++) {
@@ -209,7 +250,7 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
     const int slot = (u - base) % slots;
     if ((dirty >> slot) & 1u) {
       dirty &= ~(1u << slot);
-      float *dst = update_target(B, hot.shadowB, hot.limit, W[u], dim, gwarp);
+      float *dst = update_target(B, hot.shadowB, hot, W[u], dim, gwarp);
       const float4 *sp = reinterpret_cast<const float4 *>(ring + slot * nvec);
 #pragma unroll
       for (int q = 0; q < NR; q++) {
@@ -272,11 +313,13 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
           else
             take(std::integral_constant<int, kChunk>());
         }
-        prow_red_to(update_target(A, hot.shadowA, hot.limit, wt, dim, gwarp), nvec, lane, da);
+        prow_red_to(update_target(A, hot.shadowA, hot, wt, dim, gwarp), nvec, lane, da);
       }
     }
     // no later centre of this warp reaches position t - skip
     if (t - skip >= base && dirty) retire(t - skip);
+    if (hot.fold_every > 0 && ((t - first) % (2 * hot.fold_every)) == 2 * hot.fold_every - 1)
+      fold_one_replica(hot, A, B, dim, nvec, lane, gwarp * 3u + (unsigned)((t - first) / (2 * hot.fold_every)));
   }
   for (int u = max(last - skip, base); u < last + skip && dirty; u++) retire(u);
 }
@@ -447,6 +490,7 @@ __global__ void __launch_bounds__(kNegThreads)
   const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
   if (ncols_dev) ncols = *ncols_dev;
+  int done = 0;
 
   for (int col = gwarp; col < ncols; col += nwarps) {
     const int myw = column_word<NWA, NWB>(WA, WB, col, nwords, lane);
@@ -490,7 +534,7 @@ __global__ void __launch_bounds__(kNegThreads)
 #pragma unroll
       for (int k = 0; k < NWB; k++) row_axpy(d, sa * g[j * NWB + k], b[k]);
       if (wa[j] >= 0)
-        row_red_to(update_target(A, hot.shadowA, hot.limit, wa[j], dim, gwarp), nvec, lane, d);
+        row_red_to(update_target(A, hot.shadowA, hot, wa[j], dim, gwarp), nvec, lane, d);
     }
 #pragma unroll
     for (int k = 0; k < NWB; k++) {
@@ -500,8 +544,10 @@ __global__ void __launch_bounds__(kNegThreads)
 #pragma unroll
       for (int j = 0; j < NWA; j++) row_axpy(d, sb * g[j * NWB + k], a[j]);
       if (wb[k] >= 0)
-        row_red_to(update_target(B, hot.shadowB, hot.limit, wb[k], dim, gwarp), nvec, lane, d);
+        row_red_to(update_target(B, hot.shadowB, hot, wb[k], dim, gwarp), nvec, lane, d);
     }
+    if (hot.fold_every > 0 && (++done % hot.fold_every) == 0)
+      fold_one_replica(hot, A, B, dim, nvec, lane, (unsigned)gwarp * 5u + (unsigned)(done / hot.fold_every));
   }
 }
 
@@ -662,7 +708,7 @@ __global__ void __launch_bounds__(kStagedMaxThreads, 1)
         prow_zero(d);
 #pragma unroll
         for (int x = 0; x < NX; x++) prow_axpy(d, sy * g[HOLD_B ? (y * NWB + x) : (x * NWB + y)], X[x]);
-        if (wy[y] >= 0) prow_red_to(update_target(MY, SY, hot.limit, wy[y], dim, gwarp), nvec, lane, d);
+        if (wy[y] >= 0) prow_red_to(update_target(MY, SY, hot, wy[y], dim, gwarp), nvec, lane, d);
       }
 #pragma unroll
       for (int x = 0; x < NX; x++) {
@@ -671,7 +717,7 @@ __global__ void __launch_bounds__(kStagedMaxThreads, 1)
         prow_zero(d);
 #pragma unroll
         for (int y = 0; y < NY; y++) prow_axpy(d, sxx * g[HOLD_B ? (y * NWB + x) : (x * NWB + y)], Y[y]);
-        if (wx[x] >= 0) prow_red_to(update_target(MX, SX, hot.limit, wx[x], dim, gwarp), nvec, lane, d);
+        if (wx[x] >= 0) prow_red_to(update_target(MX, SX, hot, wx[x], dim, gwarp), nvec, lane, d);
       }
     } else {
       float sx[NX];
@@ -715,14 +761,16 @@ __global__ void __launch_bounds__(kStagedMaxThreads, 1)
           prow_axpy(dY, sy * gxy, X[x]);
           prow_axpy(dX[x], sx[x] * gxy, Y);
         }
-        if (wy >= 0) prow_red_to(update_target(MY, SY, hot.limit, wy, dim, gwarp), nvec, lane, dY);
+        if (wy >= 0) prow_red_to(update_target(MY, SY, hot, wy, dim, gwarp), nvec, lane, dY);
       }
 #pragma unroll
       for (int x = 0; x < NX; x++)
         if (wx[x] >= 0)
-          prow_red_to(update_target(MX, SX, hot.limit, wx[x], dim, gwarp), nvec, lane, dX[x]);
+          prow_red_to(update_target(MX, SX, hot, wx[x], dim, gwarp), nvec, lane, dX[x]);
       __syncwarp();  // every lane is done with this stage before it is refilled
     }
+    if (hot.fold_every > 0 && (i % hot.fold_every) == hot.fold_every - 1)
+      fold_one_replica(hot, A, B, dim, nvec, lane, (unsigned)gwarp * 5u + (unsigned)(i / hot.fold_every));
   }
 }
 
@@ -900,7 +948,7 @@ constexpr int kHotMaxDim = 1280;
 int hot_levels_default() {
   static int levels = [] {
     const char *e = getenv("W2V_HOT_LEVELS");
-    int v = e ? atoi(e) : kHotMaxLevels;
+    int v = e ? atoi(e) : 4;
     return v < 0 ? 0 : (v > kHotMaxLevels ? kHotMaxLevels : v);
   }();
   return levels;
@@ -912,7 +960,24 @@ HotRows hot_rows_at(float *buffer, int levels) {
   HotRows h;
   h.shadowA = buffer;
   h.shadowB = buffer ? buffer + (size_t)64 * kHotMaxLevels * kHotMaxDim : nullptr;
+  static const int rmax = [] {
+    const char *e = getenv("W2V_HOT_REPS");
+    int v = e ? atoi(e) : 16;
+    int p2 = 2;
+    while (p2 * 2 <= v && p2 < 64) p2 *= 2;
+    return p2;
+  }();
+  h.rmax = rmax;
+  while (levels > 0 && (rmax >> (levels - 1)) < 1) levels--;  // every level needs at least one replica
   h.limit = (buffer && levels > 0) ? (1 << levels) : 0;
+  // a warp folds one replica row every `fold_every` columns (negative kernel) or
+  // every 2 * fold_every positions (positive kernel); 0 leaves everything to the
+  // fold kernel that follows the update kernel
+  static const int every = [] {
+    const char *e = getenv("W2V_FOLD_EVERY");
+    return e ? atoi(e) : 64;
+  }();
+  h.fold_every = h.limit > 1 ? every : 0;
   return h;
 }
 

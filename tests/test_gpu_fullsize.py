@@ -1,0 +1,141 @@
+"""The kernels at the sizes of the benchmark configurations (vocab 1M, dim 300,
+minibatches of 1M tokens), checked through size-independent properties and,
+where the CPU oracle finishes in seconds, against it."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import conflict_free_neg, conflict_free_pos, rel_err
+
+pytestmark = pytest.mark.gpu
+
+V, D, N = 1_000_000, 300, 1_000_000
+THREADS = min(16, os.cpu_count() or 1)
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+@pytest.fixture(scope="module")
+def big_model():
+    rng = np.random.default_rng(1)
+    A = np.empty((V, D), np.float32)
+    B = np.empty((V, D), np.float32)
+    for M in (A, B):
+        rng.random(out=M, dtype=np.float32)
+        M -= np.float32(0.5)
+        M *= np.float32(0.5)
+    return A, B
+
+
+def test_neg_conflict_free_200k_columns_matches_oracle(oracle, big_model):
+    """Largest conflict-free negative-pair input the vocabulary allows: 200k columns
+    of 5+5 distinct words (BASELINE configs[1], second variant)."""
+    from bidmach_b200 import CUMACH
+    A, B = big_model
+    G = 200_000
+    WA, WB = conflict_free_neg(G, V, 5, 5, 3)
+    A_ref, B_ref = A.copy(), B.copy()
+    oracle.word2vecNeg(D, G, 5, 5, WA, WB, A_ref, B_ref, 0.02, 0.5, THREADS)  # conflict-free: threads cannot race
+    dA, dB = dev(A), dev(B)
+    assert CUMACH.word2vecNeg(D, G, 5, 5, dev(WA), dev(WB), dA, dB, 0.02, 0.5) == 0
+    gA, gB = dA.cpu().numpy(), dB.cpu().numpy()
+    assert rel_err(gA - A, A_ref - A) <= 1e-5 and rel_err(gB - B, B_ref - B) <= 1e-5
+    touched = np.zeros(V, bool)
+    touched[WA.ravel()] = True
+    assert np.array_equal(gA[~touched], A[~touched])
+
+
+def test_pos_conflict_free_1m_tokens_matches_oracle(oracle, big_model):
+    from bidmach_b200 import CUMACH
+    A, B = big_model
+    W, LB, UB = conflict_free_pos(N, V, 5, 4)
+    A_ref, B_ref = A.copy(), B.copy()
+    oracle.word2vecPos(D, N, 5, W, LB, UB, A_ref, B_ref, 0.05, 0.5, 1)
+    dA, dB = dev(A), dev(B)
+    assert CUMACH.word2vecPos(D, N, 5, dev(W), dev(LB), dev(UB), dA, dB, 0.05, 0.5) == 0
+    assert rel_err(dA.cpu().numpy() - A, A_ref - A) <= 1e-5
+    assert rel_err(dB.cpu().numpy() - B, B_ref - B) <= 1e-5
+
+
+def test_full_minibatch_preprocessing_properties(oracle):
+    """1M Zipf tokens through wordMats: the permuted context matrix is a permutation
+    of a prefix-complete multiset of the ordered context list, pair counts match the
+    CPU count, negatives follow min(V-1, int(V*u^4)), windows respect sentences."""
+    from bidmach_b200 import Word2Vec
+    from bidmach_b200.corpus import zipf_corpus
+    from bidmach_b200.word2vec import Opts
+    o = Opts(dim=D, vocabSize=V, wsample=1e-4, seed=9)
+    toks = zipf_corpus(V, N, 1.07, seed=2, doc_len=1000)
+    model = Word2Vec(o).init(N)
+    words, lb, ub, wa, wb = model.wordMats([dev(toks)], batch_id=5)
+    torch.cuda.synchronize()
+    words, lb, ub = words.cpu().numpy(), lb.cpu().numpy(), ub.cpu().numpy()
+    us, uw, _, un = oracle.library_uniforms(o.seed, 5, N, o.nskip, wa.numel())
+    o_words, o_lb, o_ub = oracle.wordmats_bounds(toks, V, o.nskip, oracle.salpha_of(o.wsample, V), us, uw)
+    assert np.array_equal(words, o_words) and np.array_equal(lb, o_lb) and np.array_equal(ub, o_ub)
+    ctx = model.last_contexts.cpu().numpy()
+    assert np.array_equal(ctx, oracle.ordered_contexts(words, lb, ub))
+    assert len(ctx) == oracle.count_pairs(words, lb, ub)
+    g = len(ctx) // o.nreuse
+    assert wb.shape == (g, o.nreuse) and wa.shape == (g, o.nneg)
+    # a permutation: dropping at most nreuse-1 contexts, nothing invented
+    have = np.bincount(wb.cpu().numpy().ravel(), minlength=V)
+    full = np.bincount(ctx, minlength=V)
+    assert (have <= full).all() and full.sum() - have.sum() == len(ctx) - g * o.nreuse
+    assert np.array_equal(wa.cpu().numpy().ravel(), oracle.negative_ids(un, oracle.expt_of(o.wexpt), V))
+    # windows never cross a sentence boundary
+    i = np.arange(N)
+    assert (toks[np.clip(i + lb, 0, N - 1), 1] == toks[:, 1]).all()
+    assert (toks[np.clip(i + ub, 0, N - 1), 1] == toks[:, 1]).all()
+    # heavy subsampling of the most frequent words, none of the rare ones
+    assert (words[toks[:, 0] == 0] >= 0).mean() < 0.1 and (words[toks[:, 0] > 1000] >= 0).all()
+
+
+def test_full_minibatch_scores_match_oracle_and_zero_lrate_is_identity(oracle, big_model):
+    """A real (conflicting) 1M-token minibatch: scores agree with the CPU oracle to
+    1e-5, and the update with learning rate 0 changes nothing in
+    the model (the update path itself is exercised)."""
+    from bidmach_b200 import _lib, Word2Vec
+    from bidmach_b200.corpus import zipf_corpus
+    from bidmach_b200.word2vec import Opts
+    A, B = big_model
+    o = Opts(dim=D, vocabSize=V, wsample=1.0, lrate=0.0, seed=3)
+    toks = zipf_corpus(V, N, 1.07, seed=4, doc_len=1000)
+    model = Word2Vec(o).init(N)
+    model.modelmats[0].copy_(dev(B) * 0.02)
+    model.modelmats[1].copy_(dev(A) * 0.02)
+    As, Bs = model.modelmats[1].cpu().numpy(), model.modelmats[0].cpu().numpy()
+    dt = dev(toks)
+    words, lb, ub, wa, wb = model.wordMats([dt], batch_id=1)
+    epos = model.evalPositives(5, words, lb, ub, model.modelmats[1], model.modelmats[0])
+    eneg = model.evalNegatives(5, 5, wa, wb, model.modelmats[1], model.modelmats[0])
+    want_pos = oracle.word2vecEvalPos(D, N, 5, words.cpu().numpy(), lb.cpu().numpy(), ub.cpu().numpy(), As, Bs, THREADS)
+    want_neg = oracle.word2vecEvalNeg(D, wa.shape[0], 5, 5, wa.cpu().numpy(), wb.cpu().numpy(), As, Bs, THREADS)
+    assert abs(epos - want_pos) <= 1e-5 * abs(want_pos)
+    assert abs(eneg - want_neg) <= 1e-5 * abs(want_neg)
+    model.dobatch([dt], 0, N)
+    torch.cuda.synchronize()
+    assert np.array_equal(model.modelmats[1].cpu().numpy(), As) and np.array_equal(model.modelmats[0].cpu().numpy(), Bs)
+
+
+def test_training_on_full_size_minibatches_improves_the_score():
+    """Reference-default options (subsampling 1e-4, vexp 0.5, lrate 1e-3 as in the
+    reference's script) on 1M-token Zipf minibatches: a few steps must raise the
+    held-out score above the untrained 2*log(1/2), and keep the model finite."""
+    from bidmach_b200 import Word2Vec
+    from bidmach_b200.corpus import zipf_corpus
+    from bidmach_b200.word2vec import Opts
+    o = Opts(dim=D, vocabSize=V, lrate=1e-3, seed=3)
+    m = Word2Vec(o).init(N)
+    held = dev(zipf_corpus(V, N, 1.07, seed=99))
+    before = m.evalbatch([held], 0, N)
+    assert abs(before - 2 * np.log(0.5)) < 1e-4
+    for k in range(5):
+        m.dobatch([dev(zipf_corpus(V, N, 1.07, seed=k))], 0, (k + 1) * N)
+    after = m.evalbatch([held], 0, N)
+    assert after > before + 2e-3, (before, after)
+    assert torch.isfinite(m.modelmats[0]).all() and float(m.modelmats[0].abs().max()) < 10

@@ -118,6 +118,7 @@ __device__ __forceinline__ void exch_zero_v4(float *addr, u64 &lo, u64 &hi) {
   hi = atomicExch(reinterpret_cast<u64 *>(addr) + 1, 0ull);
 }
 
+template <int NR>
 __device__ __forceinline__ void fold_one_replica(const HotRows &hot, float *A, float *B, int dim,
                                                  int nvec, int lane, unsigned turn) {
   const int levels = 31 - __clz(hot.limit);
@@ -129,18 +130,25 @@ __device__ __forceinline__ void fold_one_replica(const HotRows &hot, float *A, f
   const int id = (1 << level) - 1 + (row - level * hot.rmax) / reps;
   float *src = (in_b ? hot.shadowB : hot.shadowA) + (int64_t)row * dim;
   float *dst = (in_b ? B : A) + (int64_t)id * dim;
-  for (int idx = lane; idx < nvec; idx += 32) {
-    u64 lo, hi;
-    exch_zero_v4(src + 4 * idx, lo, hi);
-    if (lo | hi) {  // untouched replicas (also those of ids beyond the vocabulary) stay out of the model
+  // all exchanges first, so that their round trips overlap
+  u64 got[NR][2];
+#pragma unroll
+  for (int q = 0; q < NR; q++) {
+    const int idx = lane + 32 * q;
+    got[q][0] = got[q][1] = 0ull;
+    if (idx < nvec) exch_zero_v4(src + 4 * idx, got[q][0], got[q][1]);
+  }
+#pragma unroll
+  for (int q = 0; q < NR; q++) {
+    const int idx = lane + 32 * q;
+    if (idx < nvec && (got[q][0] | got[q][1])) {  // untouched replicas (also of ids beyond the vocabulary) stay out of the model
       float4 v;
-      unpack2(lo, v.x, v.y);
-      unpack2(hi, v.z, v.w);
+      unpack2(got[q][0], v.x, v.y);
+      unpack2(got[q][1], v.z, v.w);
       red_add_v4(dst + 4 * idx, v);
     }
   }
 }
-
 
 // Folds the replica rows of the hot ids back into the model and clears them.
 // grid = (hot ids, 2 matrices).
@@ -319,7 +327,7 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
     // no later centre of this warp reaches position t - skip
     if (t - skip >= base && dirty) retire(t - skip);
     if (hot.fold_every > 0 && ((t - first) % (2 * hot.fold_every)) == 2 * hot.fold_every - 1)
-      fold_one_replica(hot, A, B, dim, nvec, lane, gwarp * 3u + (unsigned)((t - first) / (2 * hot.fold_every)));
+      fold_one_replica<NR>(hot, A, B, dim, nvec, lane, gwarp * 3u + (unsigned)((t - first) / (2 * hot.fold_every)));
   }
   for (int u = max(last - skip, base); u < last + skip && dirty; u++) retire(u);
 }
@@ -547,7 +555,7 @@ __global__ void __launch_bounds__(kNegThreads)
         row_red_to(update_target(B, hot.shadowB, hot, wb[k], dim, gwarp), nvec, lane, d);
     }
     if (hot.fold_every > 0 && (++done % hot.fold_every) == 0)
-      fold_one_replica(hot, A, B, dim, nvec, lane, (unsigned)gwarp * 5u + (unsigned)(done / hot.fold_every));
+      fold_one_replica<NR>(hot, A, B, dim, nvec, lane, (unsigned)gwarp * 5u + (unsigned)(done / hot.fold_every));
   }
 }
 
@@ -770,7 +778,7 @@ __global__ void __launch_bounds__(kStagedMaxThreads, 1)
       __syncwarp();  // every lane is done with this stage before it is refilled
     }
     if (hot.fold_every > 0 && (i % hot.fold_every) == hot.fold_every - 1)
-      fold_one_replica(hot, A, B, dim, nvec, lane, (unsigned)gwarp * 5u + (unsigned)(i / hot.fold_every));
+      fold_one_replica<NR>(hot, A, B, dim, nvec, lane, (unsigned)gwarp * 5u + (unsigned)(i / hot.fold_every));
   }
 }
 

@@ -17,7 +17,7 @@ import dataclasses
 import numpy as np
 import torch
 
-from . import _lib
+from . import _lib, modelio
 from .cumach import CUMACH, cuda_error_string
 
 
@@ -265,6 +265,39 @@ class Word2Vec:
             else:
                 dist.all_reduce(m, op=dist.ReduceOp.SUM, group=group)
                 m.mul_(1.0 / dist.get_world_size(group))
+
+
+    # -- constructors and file formats of the companion object -----------------
+    @staticmethod
+    def learner(tokens, opts: "Opts | None" = None, batchSize: int = 1_000_000, lopts=None):
+        """Word2Vec.learner (Word2Vec.scala:1222-1245): a single-GPU learner over an
+        in-memory token matrix (int32 ``[ntokens, 2]``).  Returns (learner, opts)."""
+        from .learner import Learner, MatSource
+        opts = opts or Opts()
+        return Learner(MatSource(tokens, batchSize), Word2Vec(opts), lopts), opts
+
+    @staticmethod
+    def learnPar(tokens, opts: "Opts | None" = None, batchSize: int = 1_000_000, lopts=None, group=None):
+        """Word2Vec.learnPar (Word2Vec.scala:1312-1328): the data-parallel learner of
+        this rank (one process per GPU, ``torch.distributed`` initialised)."""
+        import torch.distributed as dist
+        from .learner import MatSource, ParLearner
+        opts = opts or Opts()
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        opts.seed = opts.seed + 7919 * rank   # every replica draws its own samples
+        return ParLearner(MatSource(tokens, batchSize, rank, world), Word2Vec(opts), lopts, group), opts
+
+    @staticmethod
+    def predictor(model: "Word2Vec", tokens, batchSize: int | None = None):
+        """Word2Vec.predictor (Word2Vec.scala:1282-1307): scores of a trained model on
+        held-out tokens; call ``.predict(source)`` on the first element."""
+        from .learner import Learner, MatSource
+        src = MatSource(tokens, batchSize or model.ncols)
+        return Learner(src, model), src
+
+    saveGoogleW2V = staticmethod(modelio.saveGoogleW2V)
+    readGoogleW2V = staticmethod(modelio.readGoogleW2V)
 
 
 def _host_i32(x) -> np.ndarray:

@@ -208,7 +208,9 @@ def config_dict(args, extra=None):
          "nneg": w["nneg"], "nreuse": w["nreuse"], "wsample": w["wsample"], "lrate": w["lrate"],
          "vexp": w["vexp"], "minibatch_pool": POOL,
          "parallelism": f"dp{args.gpus}: replicas, own minibatches, all-reduce(avg) of both matrices "
-                        f"every {args.sync_every} minibatches" if args.gpus > 1 else "single GPU",
+                        f"every {args.sync_every} minibatches"
+                        + (" (overlapped with the next minibatch)" if args.overlap_sync else " (blocking)")
+                        if args.gpus > 1 else "single GPU",
          "l2_policy": "inputs larger than L2: 2.4 GB of embedding rows gathered per Zipf draw; no flush"}
     if extra:
         c.update(extra)
@@ -276,8 +278,15 @@ def run_ours(args):
                 model.dobatchg([host[s % POOL].numpy()], 0, pos)
             else:
                 model.dobatch([devt[s % POOL]], 0, pos)
-            if world > 1 and (s + 1) % args.sync_every == 0:
-                model.mergeModelFn()
+            if world > 1:
+                if not args.overlap_sync:
+                    if (s + 1) % args.sync_every == 0:
+                        model.mergeModelFn()
+                else:   # the exchange runs beside the next minibatch and is folded in after it
+                    if s % args.sync_every == 0:
+                        model.finishMerge()
+                    if (s + 1) % args.sync_every == 0:
+                        model.startMerge()
         return pos
 
     def timed(host_path, pos):
@@ -289,6 +298,8 @@ def run_ours(args):
         sampler.window_open()
         e0.record(stream)
         pos = run_steps(args.steps, host_path, pos)
+        if world > 1:
+            model.finishMerge()   # an exchange still in flight belongs to the timed region
         e1.record(stream)
         sync_all()
         sampler.window_close()
@@ -390,6 +401,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sync-every", type=int, default=8)
+    ap.add_argument("--overlap-sync", action="store_true",
+                    help="multi-GPU: run the averaging all-reduce beside the next minibatch (snapshot + "
+                         "delayed correction) instead of blocking on it")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--mode", default="train", choices=["train", "eval"],
                     help="eval: time the scoring path (evalbatch) instead of the update path")

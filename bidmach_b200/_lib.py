@@ -66,6 +66,7 @@ SIGNATURES = {
     "w2v_evalbatch": (_I, [_P, _P, C.POINTER(W2VUniforms), _P, _P, C.c_uint64, C.POINTER(C.c_double), _P]),
     "w2v_dobatch_host": (_I, [_P, _P, _P, _P, C.c_int64, C.c_uint64, C.POINTER(C.c_int64), _P]),
     "w2v_evalbatch_host": (_I, [_P, _P, _P, _P, C.c_uint64, C.POINTER(C.c_double), _P]),
+    "w2v_apply_average": (_I, [_P, _P, _P, C.c_int64, _P]),
     "w2v_set_timing": (_I, [_P, _I]),
     "w2v_get_timing": (_I, [_P, C.POINTER(W2VTiming)]),
     "w2v_launch_count": (C.c_longlong, []),

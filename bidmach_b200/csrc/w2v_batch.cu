@@ -195,6 +195,21 @@ __global__ void init_model_kernel(int64_t n, int dim, Rng rng, float *__restrict
     if (e + k < n) B[e + k] = __fdiv_rn(__fadd_rn(u01(r.v[k]), -0.5f), fd);
 }
 
+// theta += avg - base, 16 bytes per thread and trip (all three 16-byte aligned)
+__global__ void apply_average_kernel(float4 *__restrict__ theta, const float4 *__restrict__ base,
+                                     const float4 *__restrict__ avg, int64_t nvec) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float4 t = theta[i];
+    const float4 b = base[i], a = avg[i];
+    t.x += a.x - b.x;
+    t.y += a.y - b.y;
+    t.z += a.z - b.z;
+    t.w += a.w - b.w;
+    theta[i] = t;
+  }
+}
+
 }  // namespace w2v
 
 // ---------------------------------------------------------------------------
@@ -384,6 +399,19 @@ int w2v_create(const w2v_opts *opts, int ncols, w2v_ctx **out) {
   }
   *out = c;
   return 0;
+}
+
+int w2v_apply_average(float *theta, const float *base, const float *avg, int64_t n, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (n <= 0) return 0;
+  if ((n & 3) || (((uintptr_t)theta | (uintptr_t)base | (uintptr_t)avg) & 15)) return 1;
+  const int threads = 256;
+  const int blocks = w2v::device_sm_count() * 8;
+  w2v::apply_average_kernel<<<blocks, threads, 0, stream>>>(
+      reinterpret_cast<float4 *>(theta), reinterpret_cast<const float4 *>(base),
+      reinterpret_cast<const float4 *>(avg), n / 4);
+  w2v::count_launch(1);
+  return (int)cudaGetLastError();
 }
 
 int w2v_init_model(const w2v_opts *o, float *A, float *B, void *stream_) {

@@ -59,6 +59,7 @@ class LearnerOpts:
     evalStep: int = 11
     updateAll: bool = False
     syncStep: int = 2
+    overlapSync: bool = False   # not in the reference: exchange beside the next minibatch
 
 
 def _scala_mod(a: int, b: int) -> int:
@@ -151,6 +152,18 @@ class ParLearner(Learner):
 
     def _after_train_step(self, istep_global: int):
         self._since_sync += 1
-        if self._since_sync >= self.opts.syncStep:
+        if self.opts.overlapSync:
+            if self._since_sync == 1:
+                self.model.finishMerge()        # the exchange started one minibatch ago
+            if self._since_sync >= self.opts.syncStep:
+                self.model.startMerge(self.group)
+                self._since_sync = 0
+        elif self._since_sync >= self.opts.syncStep:
             self.model.mergeModelFn(self.group)
             self._since_sync = 0
+
+    def train(self, do_init: bool = True):
+        super().train(do_init)
+        if self.opts.overlapSync:
+            self.model.finishMerge()
+        return self

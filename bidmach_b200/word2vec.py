@@ -95,6 +95,8 @@ class Word2Vec:
         self._ctx = None
         self._copts = None
         self._batches = 0
+        self._flat = None
+        self._merge = None   # state of an averaging exchange in flight
 
     # -- life cycle ---------------------------------------------------------
     def init(self, ncols: int, refresh: bool = True):
@@ -106,8 +108,9 @@ class Word2Vec:
         self._copts = o.to_c()
         with torch.cuda.device(self.device):
             if refresh or not self.modelmats:
-                mm0 = torch.empty(o.vocabSize, o.dim, dtype=torch.float32, device=self.device)
-                mm1 = torch.empty_like(mm0)
+                # both matrices in one buffer, so that one collective moves the whole model
+                self._flat = torch.empty(2, o.vocabSize, o.dim, dtype=torch.float32, device=self.device)
+                mm0, mm1 = self._flat[0], self._flat[1]
                 _check(lib.w2v_init_model(C.byref(self._copts), mm1.data_ptr(), mm0.data_ptr(),
                                           self._stream()), "w2v_init_model")
                 self.modelmats = [mm0, mm1]
@@ -253,19 +256,59 @@ class Word2Vec:
     def mergeModelFn(self, group=None):
         """Replaces Word2Vec.mergeModelFn (Word2Vec.scala:547-568), which averages a
         frequency-ranked prefix of each matrix through host-driven peer copies:
-        here both full matrices are averaged over the process group with one
-        all-reduce each (NCCL over NVLink when the group's backend is nccl)."""
+        here the whole model (both matrices, one buffer) is averaged over the
+        process group with one all-reduce (NCCL over NVLink when the group's
+        backend is nccl).  Blocks the compute stream until the average is in."""
         import torch.distributed as dist
         if not dist.is_initialized() or dist.get_world_size(group) == 1:
             return
+        self.finishMerge()
+        bufs = [self._flat] if getattr(self, "_flat", None) is not None else self.modelmats
         avg = dist.ReduceOp.AVG if dist.get_backend(group) == "nccl" else None
-        for m in self.modelmats:
+        for m in bufs:
             if avg is not None:
                 dist.all_reduce(m, op=avg, group=group)
             else:
                 dist.all_reduce(m, op=dist.ReduceOp.SUM, group=group)
                 m.mul_(1.0 / dist.get_world_size(group))
 
+    def startMerge(self, group=None):
+        """Overlapped form of mergeModelFn: snapshots the model, starts the
+        all-reduce of the snapshot on a side stream and returns; training goes
+        on.  ``finishMerge`` (called by the learner one minibatch later, or by the
+        next start) adds ``average - snapshot`` to the live model, so updates made
+        while the exchange was in flight are kept.  Needs two extra model-sized
+        buffers."""
+        import torch.distributed as dist
+        if not dist.is_initialized() or dist.get_world_size(group) == 1:
+            return
+        self.finishMerge()
+        if getattr(self, "_snap", None) is None:
+            self._snap = torch.empty_like(self._flat)
+            self._avg = torch.empty_like(self._flat)
+            self._comm = torch.cuda.Stream(device=self.device)
+        compute = torch.cuda.current_stream(self.device)
+        self._snap.copy_(self._flat)
+        taken = torch.cuda.Event()
+        taken.record(compute)
+        with torch.cuda.stream(self._comm):
+            self._comm.wait_event(taken)
+            self._avg.copy_(self._snap)
+            dist.all_reduce(self._avg, op=dist.ReduceOp.AVG, group=group)
+            done = torch.cuda.Event()
+            done.record(self._comm)
+        self._merge = done
+
+    def finishMerge(self):
+        if getattr(self, "_merge", None) is None:
+            return
+        compute = torch.cuda.current_stream(self.device)
+        compute.wait_event(self._merge)
+        self._merge = None
+        with torch.cuda.device(self.device):
+            _check(_lib.load().w2v_apply_average(self._flat.data_ptr(), self._snap.data_ptr(),
+                                                 self._avg.data_ptr(), self._flat.numel(),
+                                                 self._stream()), "w2v_apply_average")
 
     # -- constructors and file formats of the companion object -----------------
     @staticmethod

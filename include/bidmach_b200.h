@@ -207,6 +207,15 @@ int w2v_dobatch_host(w2v_ctx *ctx, const int *tokens_host, float *A, float *B, i
 int w2v_evalbatch_host(w2v_ctx *ctx, const int *tokens_host, const float *A, const float *B,
                        uint64_t batch_id, double *score_host, void *stream);
 
+/* Second half of an overlapped model average (multi-GPU): the caller snapshots
+ * its replica into `base`, averages the snapshots of all replicas into `avg`
+ * with an all-reduce that runs beside the following minibatches, and then
+ * folds the result into the live replica: theta += avg - base, elementwise over
+ * n floats (n a multiple of 4, pointers 16-byte aligned; else 1 is returned).
+ * With this the exchange of Word2Vec.mergeModelFn (networks/Word2Vec.scala:
+ * 547-568) no longer stalls training. */
+int w2v_apply_average(float *theta, const float *base, const float *avg, int64_t n, void *stream);
+
 /* Optional phase timers, the counterpart of the reference's per-phase
  * `times/delays` bookkeeping (networks/Word2Vec.scala:77-92): when switched on,
  * CUDA events are recorded at the phase boundaries of every minibatch and the

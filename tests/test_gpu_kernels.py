@@ -229,3 +229,19 @@ def test_golden_fixtures_on_gpu_conflict_free_prefix(oracle, cumach):
         assert cumach.word2vecEvalPos(dim, len(g["W"]), skip, dev(g["W"]), dev(g["LB"]), dev(g["UB"]),
                                       dev(A), dev(B), ret) == 0
         assert abs(ret.item() - want) <= TOL * abs(want)
+
+
+def test_apply_average_adds_the_difference():
+    """w2v_apply_average: theta += avg - base (second half of the overlapped model average)."""
+    from bidmach_b200 import _lib
+    lib = _lib.load()
+    torch.manual_seed(0)
+    theta = torch.randn(1000, 300, device="cuda")
+    base = torch.randn_like(theta)
+    avg = torch.randn_like(theta)
+    want = theta + (avg - base)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.w2v_apply_average(theta.data_ptr(), base.data_ptr(), avg.data_ptr(), theta.numel(), stream) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(theta, want, rtol=0, atol=1e-6)
+    assert lib.w2v_apply_average(theta.data_ptr(), base.data_ptr(), avg.data_ptr(), 7, stream) == 1

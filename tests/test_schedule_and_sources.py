@@ -178,3 +178,35 @@ def test_parlearner_syncs_every_syncstep_and_replicas_agree():
     # 21 batches -> 20 usable, 10 per rank; istep 1 and the last are eval-only: 8 train steps, 4 syncs
     assert got[0][1] == got[1][1] == 4 and got[0][2] == got[1][2] == 10
     assert torch.equal(got[0][3], got[1][3])
+
+
+def test_parlearner_overlapped_exchange_order():
+    """overlapSync: the exchange starts after every syncStep-th training minibatch
+    and is folded in right after the next one (or at the end of training)."""
+    from bidmach_b200.learner import LearnerOpts, MatSource, ParLearner
+
+    class M(_FakeModel):
+        def __init__(self):
+            super().__init__()
+            self.log = []
+
+        def dobatchg(self, mats, ipass, pos):
+            self.log.append("train")
+            return 0
+
+        def evalbatchg(self, mats, ipass, pos):
+            self.log.append("eval")
+            return 0.0
+
+        def startMerge(self, group=None):
+            self.log.append("start")
+
+        def finishMerge(self):
+            self.log.append("finish")
+
+    m = M()
+    toks = np.zeros((700, 2), np.int32)
+    ParLearner(MatSource(toks, 100), m, LearnerOpts(npasses=1, evalStep=11, syncStep=2, overlapSync=True)).train()
+    # minibatches: train, eval, train, train, train, train, eval(last)
+    assert m.log == ["train", "finish", "eval", "train", "start", "train", "finish", "train", "start",
+                     "train", "finish", "eval", "finish"]

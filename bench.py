@@ -409,11 +409,14 @@ def main():
                     help="eval: time the scoring path (evalbatch) instead of the update path")
     ap.add_argument("--vocab", type=int, default=None, help="override the workload's vocabulary (profiling)")
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per minibatch (profiling)")
+    ap.add_argument("--nneg", type=int, default=None, help="override the number of negatives (configs[4] uses 10)")
     args = ap.parse_args()
     if args.vocab:
         WORKLOAD["vocab"] = args.vocab
     if args.tokens:
         WORKLOAD["ntokens"] = args.tokens
+    if args.nneg:
+        WORKLOAD["nneg"] = args.nneg
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -571,7 +571,6 @@ __global__ void __launch_bounds__(kNegThreads)
 // Shared memory per warp: 128-byte header (mbarrier per stage, word ids per
 // stage) + 2 stages of (NWA + NWB) rows.
 // ---------------------------------------------------------------------------
-constexpr int kStagedMaxThreads = 384;
 constexpr int kStagedHeader = 256;
 constexpr int kWaitPolls = 1 << 20;  // polls of a stage's barrier before giving up
 
@@ -587,17 +586,24 @@ template <int NWA, int NWB, int NR>
 struct StagedShape {
   static constexpr bool resident = (NWA + NWB <= 10) && (NR <= 3);
   static constexpr int stages = resident ? 1 : 2;
+  // threads per block the kernel is compiled for: 12 warps leave 168 registers
+  // per thread, enough for a resident 10 x 3 column; the streamed shapes need up
+  // to 255 and get 8 warps
+  static constexpr int max_threads = (resident && NWA * NWB <= 25) ? 384 : 256;
 };
 
 __host__ __device__ inline size_t staged_warp_bytes(int nrows_per_col, int dim, int stages) {
   return kStagedHeader + (size_t)stages * nrows_per_col * dim * sizeof(float);
 }
 
-template <int NWA, int NWB, int NR>
-__global__ void __launch_bounds__(kStagedMaxThreads, 1)
+// EVAL = true turns the same pipeline into the scoring kernel (the name keeps
+// "update" for both): no updates, the lane that holds a pair's dot product adds
+// log(max(1 - sigmoid, 1e-20)).
+template <int NWA, int NWB, int NR, bool EVAL>
+__global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
     neg_update_staged_kernel(int dim, int ncols, const int *__restrict__ ncols_dev, int nwords,
-                             const int *__restrict__ WA, const int *__restrict__ WB, float *A,
-                             float *B, float lrate, float vexp, HotRows hot) {
+                      const int *__restrict__ WA, const int *__restrict__ WB, float *A, float *B,
+                      float lrate, float vexp, HotRows hot, EvalScratch *scratch, float *retval) {
   using S = Spread<NWA * NWB>;
   using Shape = StagedShape<NWA, NWB, NR>;
   constexpr int NROWS = NWA + NWB;
@@ -629,6 +635,7 @@ __global__ void __launch_bounds__(kStagedMaxThreads, 1)
   __syncwarp();
 
   const int mycols = (gwarp < ncols) ? (ncols - gwarp + nwarps - 1) / nwarps : 0;
+  double acc = 0.0;  // EVAL: this lane's share of the score
 
   // Starts the copies of a column (word ids in `w`, one per lane) into stage `st`.
   auto fill = [&](int st, int w) {
@@ -663,7 +670,7 @@ __global__ void __launch_bounds__(kStagedMaxThreads, 1)
       if (lane == 0) atomicExch(&g_stage_fault, 1);
       if (NST == 2 && i + 1 < mycols)
         mbar_wait_bounded(&bars[st ^ 1], (unsigned)((i + 1) / NST) & 1u, kWaitPolls);
-      return;
+      break;
     }
     const int myw = (lane < 16) ? ids[st * 16 + lane] : -1;
     const float mysc = (myw >= 0) ? freq_scale(myw, vexp) : 0.f;
@@ -703,6 +710,12 @@ __global__ void __launch_bounds__(kStagedMaxThreads, 1)
         for (int x = 0; x < NX; x++)
           p[HOLD_B ? (y * NWB + x) : (x * NWB + y)] = prow_dot_partial(X[x], Y[y]);
       S::reduce(p, lane);
+      if constexpr (EVAL) {
+#pragma unroll
+        for (int q = 0; q < S::FIN; q++)
+          if ((spread_valid_mask<NWA * NWB>(q) >> lane) & 1u)
+            acc += log(fmax((double)(1.0f - sigmoid_guard(p[q])), 1e-20));
+      } else {
 #pragma unroll
       for (int q = 0; q < S::FIN; q++) p[q] = -lrate * sigmoid_guard(p[q]);
       float g[NWA * NWB];
@@ -727,6 +740,7 @@ __global__ void __launch_bounds__(kStagedMaxThreads, 1)
         for (int y = 0; y < NY; y++) prow_axpy(d, sxx * g[HOLD_B ? (y * NWB + x) : (x * NWB + y)], Y[y]);
         if (wx[x] >= 0) prow_red_to(update_target(MX, SX, hot, wx[x], dim, gwarp), nvec, lane, d);
       }
+      }
     } else {
       float sx[NX];
 #pragma unroll
@@ -744,6 +758,12 @@ __global__ void __launch_bounds__(kStagedMaxThreads, 1)
           p[HOLD_B ? (y * NWB + x) : (x * NWB + y)] = prow_dot_partial(X[x], Y);
       }
       S::reduce(p, lane);
+      if constexpr (EVAL) {
+#pragma unroll
+        for (int q = 0; q < S::FIN; q++)
+          if ((spread_valid_mask<NWA * NWB>(q) >> lane) & 1u)
+            acc += log(fmax((double)(1.0f - sigmoid_guard(p[q])), 1e-20));
+      } else {
 #pragma unroll
       for (int q = 0; q < S::FIN; q++) p[q] = -lrate * sigmoid_guard(p[q]);
       float g[NWA * NWB];
@@ -775,11 +795,13 @@ __global__ void __launch_bounds__(kStagedMaxThreads, 1)
       for (int x = 0; x < NX; x++)
         if (wx[x] >= 0)
           prow_red_to(update_target(MX, SX, hot, wx[x], dim, gwarp), nvec, lane, dX[x]);
+      }
       __syncwarp();  // every lane is done with this stage before it is refilled
     }
-    if (hot.fold_every > 0 && (i % hot.fold_every) == hot.fold_every - 1)
+    if (!EVAL && hot.fold_every > 0 && (i % hot.fold_every) == hot.fold_every - 1)
       fold_one_replica<NR>(hot, A, B, dim, nvec, lane, (unsigned)gwarp * 5u + (unsigned)(i / hot.fold_every));
   }
+  if constexpr (EVAL) finish_eval_sum(acc, scratch, retval);
 }
 
 template <int NWA, int NWB, int NR>
@@ -787,7 +809,9 @@ __global__ void __launch_bounds__(kNegThreads)
     neg_eval_kernel(int dim, int ncols, const int *__restrict__ ncols_dev,
                     const int *__restrict__ WA, const int *__restrict__ WB,
                     const float *__restrict__ A, const float *__restrict__ B,
-                    EvalScratch *scratch, float *retval) {
+                    EvalScratch *scratch, float *retval, int wa_stride, int wb_stride) {
+  // wa_stride / wb_stride: words per column in WA / WB (NWA / NWB, or more when
+  // this launch scores one half of a wider column)
   using S = Spread<NWA * NWB>;
   const int lane = threadIdx.x & 31;
   const int nvec = dim >> 2;
@@ -797,7 +821,11 @@ __global__ void __launch_bounds__(kNegThreads)
   double acc = 0.0;
 
   for (int col = gwarp; col < ncols; col += nwarps) {
-    const int myw = column_word<NWA, NWB>(WA, WB, col, 0x7fffffff, lane);
+    int myw = -1;
+    if (lane < NWA)
+      myw = WA[(int64_t)col * wa_stride + lane];
+    else if (lane < NWA + NWB)
+      myw = WB[(int64_t)col * wb_stride + (lane - NWA)];
     Row<NR> a[NWA], b[NWB];
 #pragma unroll
     for (int j = 0; j < NWA; j++)
@@ -1125,19 +1153,33 @@ static bool neg_staged_enabled() {
   return on;
 }
 
-template <int NWA, int NWB, int NR>
+template <int NWA, int NWB, int NR, bool EVAL>
 static cudaError_t launch_neg_staged(int grid, int warps, size_t smem, cudaStream_t stream, int dim,
                                      int ncols, const int *ncols_dev, int nwords, const int *WA,
                                      const int *WB, float *A, float *B, float lrate, float vexp,
-                                     const HotRows &hot) {
+                                     const HotRows &hot, EvalScratch *scratch, float *retval) {
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(neg_update_staged_kernel<NWA, NWB, NR>,
+    cudaError_t e = cudaFuncSetAttribute(neg_update_staged_kernel<NWA, NWB, NR, EVAL>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  neg_update_staged_kernel<NWA, NWB, NR><<<grid, warps * 32, smem, stream>>>(
-      dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot);
+  neg_update_staged_kernel<NWA, NWB, NR, EVAL><<<grid, warps * 32, smem, stream>>>(
+      dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval);
   return cudaSuccess;
+}
+
+template <int NWA, int NWB, int NR>
+static cudaError_t launch_neg_staged_any(bool eval, int grid, int warps, size_t smem,
+                                         cudaStream_t stream, int dim, int ncols,
+                                         const int *ncols_dev, int nwords, const int *WA,
+                                         const int *WB, float *A, float *B, float lrate, float vexp,
+                                         const HotRows &hot, EvalScratch *scratch, float *retval) {
+  return eval ? launch_neg_staged<NWA, NWB, NR, true>(grid, warps, smem, stream, dim, ncols, ncols_dev,
+                                                      nwords, WA, WB, A, B, lrate, vexp, hot, scratch,
+                                                      retval)
+              : launch_neg_staged<NWA, NWB, NR, false>(grid, warps, smem, stream, dim, ncols, ncols_dev,
+                                                       nwords, WA, WB, A, B, lrate, vexp, hot, scratch,
+                                                       retval);
 }
 
 // Reads and clears the flag a staged kernel raises when a stage never arrived.
@@ -1168,29 +1210,49 @@ static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int
   // fits for up to 10 rows of 3 vectors or 15 rows of 2
   constexpr int kMaxNr = (NWA + NWB <= 10) ? 4 : 2;
   // staged update: as many warps per block (one block per SM) as shared memory holds
-  const int staged_stages = ((NWA + NWB <= 10) && nr <= 3) ? 1 : 2;  // StagedShape<...>::stages
+  const bool staged_resident = (NWA + NWB <= 10) && nr <= 3;  // StagedShape<NWA, NWB, nr>::resident
+  const int staged_stages = staged_resident ? 1 : 2;
+  const int staged_max_threads = (staged_resident && NWA * NWB <= 25) ? 384 : 256;
   const size_t per_warp = staged_warp_bytes(NWA + NWB, dim, staged_stages);
-  const int staged_warps = (int)std::min<size_t>(kStagedMaxThreads / 32, (227 * 1024) / per_warp);
-  if (!eval && vector_ok(dim, A, B) && nr <= 4 && staged_warps >= 2 && neg_staged_enabled()) {
+  const int staged_warps = (int)std::min<size_t>(staged_max_threads / 32, (227 * 1024) / per_warp);
+  // scoring keeps the register-resident kernel where it exists (more warps per SM, and nothing to
+  // prefetch around); the staged pipeline scores the shapes that kernel cannot hold
+  const bool want_staged = eval ? (nr > kMaxNr) : true;
+  if constexpr (NWA + NWB == 15) {
+    // scoring a 10+5 column = scoring its two 5+5 halves, which the register-resident kernel holds
+    if (eval && vector_ok(dim, A, B) && nr >= 3 && nr <= 4) {
+      const int grid = grid_for(ncols, kNegThreads, 8);
+      for (int half = 0; half < 2; half++) {
+        const int *wa = WA + (NWA == 10 ? 5 * half : 0), *wb = WB + (NWB == 10 ? 5 * half : 0);
+        if (nr == 3)
+          neg_eval_kernel<5, 5, 3><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, wa, wb, A, B, scratch, retval, NWA, NWB);
+        else
+          neg_eval_kernel<5, 5, 4><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, wa, wb, A, B, scratch, retval, NWA, NWB);
+      }
+      count_launch(2);
+      return (int)cudaGetLastError();
+    }
+  }
+  if (want_staged && vector_ok(dim, A, B) && nr <= 4 && staged_warps >= 2 && neg_staged_enabled()) {
     const size_t smem = per_warp * staged_warps;
     const int grid = std::max(1, std::min(device_sm_count(), (ncols + staged_warps - 1) / staged_warps));
     cudaError_t e = cudaSuccess;
     switch (nr) {
-      case 1: e = launch_neg_staged<NWA, NWB, 1>(grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot); break;
-      case 2: e = launch_neg_staged<NWA, NWB, 2>(grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot); break;
-      case 3: e = launch_neg_staged<NWA, NWB, 3>(grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot); break;
-      default: e = launch_neg_staged<NWA, NWB, 4>(grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot); break;
+      case 1: e = launch_neg_staged_any<NWA, NWB, 1>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval); break;
+      case 2: e = launch_neg_staged_any<NWA, NWB, 2>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval); break;
+      case 3: e = launch_neg_staged_any<NWA, NWB, 3>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval); break;
+      default: e = launch_neg_staged_any<NWA, NWB, 4>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval); break;
     }
     if (e != cudaSuccess) return (int)e;
-    fold_hot_rows(dim, hot, A, B, stream);
+    if (!eval) fold_hot_rows(dim, hot, A, B, stream);
   } else if (vector_ok(dim, A, B) && nr <= kMaxNr) {
     const int grid = grid_for(ncols, kNegThreads, 8);
     if (eval) {
       switch (nr) {
-        case 1: neg_eval_kernel<NWA, NWB, 1><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, WA, WB, A, B, scratch, retval); break;
-        case 2: neg_eval_kernel<NWA, NWB, 2><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, WA, WB, A, B, scratch, retval); break;
-        case 3: neg_eval_kernel<NWA, NWB, (kMaxNr >= 3 ? 3 : 1)><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, WA, WB, A, B, scratch, retval); break;
-        default: neg_eval_kernel<NWA, NWB, (kMaxNr >= 4 ? 4 : 1)><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, WA, WB, A, B, scratch, retval); break;
+        case 1: neg_eval_kernel<NWA, NWB, 1><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, WA, WB, A, B, scratch, retval, NWA, NWB); break;
+        case 2: neg_eval_kernel<NWA, NWB, 2><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, WA, WB, A, B, scratch, retval, NWA, NWB); break;
+        case 3: neg_eval_kernel<NWA, NWB, (kMaxNr >= 3 ? 3 : 1)><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, WA, WB, A, B, scratch, retval, NWA, NWB); break;
+        default: neg_eval_kernel<NWA, NWB, (kMaxNr >= 4 ? 4 : 1)><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, WA, WB, A, B, scratch, retval, NWA, NWB); break;
       }
     } else {
       switch (nr) {

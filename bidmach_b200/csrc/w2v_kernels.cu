@@ -563,13 +563,10 @@ __global__ void __launch_bounds__(kNegThreads)
 // Negative pairs, staged: the rows of a column are brought into shared memory
 // by bulk asynchronous copies (one per row, completion counted on an mbarrier)
 // one column ahead of the arithmetic, so a warp never waits for global memory
-// in the middle of a column.  Each warp is its own pipeline: two stages, one
-// being filled while the other is consumed.  The smaller side of the column
-// (NX rows) is held in registers, the larger side (NY rows) is streamed from
-// the stage twice: once for the dot products, once for the updates.
+// in the middle of a column.  Each warp is its own pipeline with one stage.
 //
-// Shared memory per warp: 128-byte header (mbarrier per stage, word ids per
-// stage) + 2 stages of (NWA + NWB) rows.
+// Shared memory per warp: 256-byte header (mbarrier, word ids of the staged
+// column) + one stage of (NWA + NWB) rows.
 // ---------------------------------------------------------------------------
 constexpr int kStagedHeader = 256;
 constexpr int kWaitPolls = 1 << 20;  // polls of a stage's barrier before giving up
@@ -578,18 +575,17 @@ static __device__ int g_stage_fault;  // set when a stage never arrived; checked
 
 // Columns whose rows all fit in registers (up to 10 rows of 3 vectors per lane)
 // are consumed "resident": the warp moves the whole stage into registers and
-// immediately starts the copies of its next column into the same stage, so one
-// stage per warp is enough.  Wider columns are "streamed": the smaller side is
-// held in registers, the larger side is read from the stage twice (dot
-// products, then updates) while the next column lands in a second stage.
+// immediately starts the copies of its next column into the same stage.  Wider
+// columns are "streamed": the smaller side is held in registers, the larger
+// side is read from the stage three times (dot products, its own deltas, the
+// held side's deltas, by which time the held rows' registers are free to carry
+// them), and the stage is refilled when the column is done.
 template <int NWA, int NWB, int NR>
 struct StagedShape {
   static constexpr bool resident = (NWA + NWB <= 10) && (NR <= 3);
-  static constexpr int stages = resident ? 1 : 2;
-  // threads per block the kernel is compiled for: 12 warps leave 168 registers
-  // per thread, enough for a resident 10 x 3 column; the streamed shapes need up
-  // to 255 and get 8 warps
-  static constexpr int max_threads = (resident && NWA * NWB <= 25) ? 384 : 256;
+  static constexpr int stages = 1;
+  // threads per block the kernel is compiled for: 12 warps leave 168 registers per thread
+  static constexpr int max_threads = 384;
 };
 
 __host__ __device__ inline size_t staged_warp_bytes(int nrows_per_col, int dim, int stages) {
@@ -659,17 +655,10 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
 
   for (int i = 0; i < mycols; i++) {
     const int st = i % NST;
-    if (NST == 2 && i + 1 < mycols) {
-      fill(st ^ 1, ahead);
-      if (i + 2 < mycols) ahead = ids_of(i + 2);
-    }
     if (!mbar_wait_bounded(&bars[st], (unsigned)(i / NST) & 1u, kWaitPolls)) {
-      // the copies never completed: report, give a stage that is still being
-      // filled a bounded chance to land so nothing is in flight into this
-      // block, and stop
+      // the copies never completed within the limit (this warp has no other
+      // copy in flight): report and stop
       if (lane == 0) atomicExch(&g_stage_fault, 1);
-      if (NST == 2 && i + 1 < mycols)
-        mbar_wait_bounded(&bars[st ^ 1], (unsigned)((i + 1) / NST) & 1u, kWaitPolls);
       break;
     }
     const int myw = (lane < 16) ? ids[st * 16 + lane] : -1;
@@ -770,33 +759,42 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
 #pragma unroll
       for (int idx = NWA * NWB - 1; idx >= 0; idx--)
         g[idx] = __shfl_sync(kFullMask, p[S::slot_of(idx)], S::lane_of(idx));
-      PRow<NR> dX[NX];
-#pragma unroll
-      for (int x = 0; x < NX; x++) prow_zero(dX[x]);
+      // rows of the streamed side: their deltas need the held rows only
 #pragma unroll
       for (int y = 0; y < NY; y++) {
         const int wy = __shfl_sync(kFullMask, myw, YOFF + y);
         const float sy = __shfl_sync(kFullMask, mysc, YOFF + y);
-        PRow<NR> Y, dY;
-        if (wy >= 0)
-          prow_load(Y, stage + (size_t)(YOFF + y) * rowbytes, nvec, lane);
-        else
-          prow_zero(Y);
+        PRow<NR> dY;
         prow_zero(dY);
 #pragma unroll
-        for (int x = 0; x < NX; x++) {
-          const float gxy = g[HOLD_B ? (y * NWB + x) : (x * NWB + y)];
-          prow_axpy(dY, sy * gxy, X[x]);
-          prow_axpy(dX[x], sx[x] * gxy, Y);
-        }
+        for (int x = 0; x < NX; x++)
+          prow_axpy(dY, sy * g[HOLD_B ? (y * NWB + x) : (x * NWB + y)], X[x]);
         if (wy >= 0) prow_red_to(update_target(MY, SY, hot, wy, dim, gwarp), nvec, lane, dY);
+      }
+      // rows of the held side: the held rows themselves are dead by now, their
+      // registers carry the deltas while the other side streams by once more
+#pragma unroll
+      for (int x = 0; x < NX; x++) prow_zero(X[x]);
+#pragma unroll
+      for (int y = 0; y < NY; y++) {
+        const int wy = __shfl_sync(kFullMask, myw, YOFF + y);
+        if (wy < 0) continue;
+        PRow<NR> Y;
+        prow_load(Y, stage + (size_t)(YOFF + y) * rowbytes, nvec, lane);
+#pragma unroll
+        for (int x = 0; x < NX; x++)
+          prow_axpy(X[x], sx[x] * g[HOLD_B ? (y * NWB + x) : (x * NWB + y)], Y);
       }
 #pragma unroll
       for (int x = 0; x < NX; x++)
         if (wx[x] >= 0)
-          prow_red_to(update_target(MX, SX, hot, wx[x], dim, gwarp), nvec, lane, dX[x]);
+          prow_red_to(update_target(MX, SX, hot, wx[x], dim, gwarp), nvec, lane, X[x]);
       }
-      __syncwarp();  // every lane is done with this stage before it is refilled
+      __syncwarp();  // every lane is done with this stage: start the copies of the next column
+      if (i + 1 < mycols) {
+        fill(0, ahead);
+        if (i + 2 < mycols) ahead = ids_of(i + 2);
+      }
     }
     if (!EVAL && hot.fold_every > 0 && (i % hot.fold_every) == hot.fold_every - 1)
       fold_one_replica<NR>(hot, A, B, dim, nvec, lane, (unsigned)gwarp * 5u + (unsigned)(i / hot.fold_every));
@@ -1210,9 +1208,7 @@ static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int
   // fits for up to 10 rows of 3 vectors or 15 rows of 2
   constexpr int kMaxNr = (NWA + NWB <= 10) ? 4 : 2;
   // staged update: as many warps per block (one block per SM) as shared memory holds
-  const bool staged_resident = (NWA + NWB <= 10) && nr <= 3;  // StagedShape<NWA, NWB, nr>::resident
-  const int staged_stages = staged_resident ? 1 : 2;
-  const int staged_max_threads = (staged_resident && NWA * NWB <= 25) ? 384 : 256;
+  const int staged_stages = 1, staged_max_threads = 384;  // StagedShape<...>::stages, ::max_threads
   const size_t per_warp = staged_warp_bytes(NWA + NWB, dim, staged_stages);
   const int staged_warps = (int)std::min<size_t>(staged_max_threads / 32, (227 * 1024) / per_warp);
   // scoring keeps the register-resident kernel where it exists (more warps per SM, and nothing to

@@ -573,19 +573,17 @@ constexpr int kWaitPolls = 1 << 20;  // polls of a stage's barrier before giving
 
 static __device__ int g_stage_fault;  // set when a stage never arrived; checked by the host
 
-// Columns whose rows all fit in registers (up to 10 rows of 3 vectors per lane)
-// are consumed "resident": the warp moves the whole stage into registers and
-// immediately starts the copies of its next column into the same stage.  Wider
-// columns are "streamed": the smaller side is held in registers, the larger
-// side is read from the stage three times (dot products, its own deltas, the
-// held side's deltas, by which time the held rows' registers are free to carry
-// them), and the stage is refilled when the column is done.
+// The smaller side of the column (NX rows) is held in registers, the larger
+// side (NY rows) is read from the stage three times: for the dot products, for
+// its own deltas (which need the held rows only), and for the deltas of the
+// held side, by which time the held rows' registers are free to carry them.
+// The stage is refilled with the warp's next column when the column is done.
 template <int NWA, int NWB, int NR>
 struct StagedShape {
-  static constexpr bool resident = (NWA + NWB <= 10) && (NR <= 3);
-  static constexpr int stages = 1;
-  // threads per block the kernel is compiled for: 12 warps leave 168 registers per thread
-  static constexpr int max_threads = 384;
+  static constexpr int held = (NWB <= NWA) ? NWB : NWA;
+  // threads per block the kernel is compiled for: 16 warps (128 registers per
+  // thread) when the held rows and the pair coefficients are few, else 12 (168)
+  static constexpr int max_threads = (held * NR <= 15 && NWA * NWB <= 25) ? 512 : 384;
 };
 
 __host__ __device__ inline size_t staged_warp_bytes(int nrows_per_col, int dim, int stages) {
@@ -601,9 +599,8 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
                       const int *__restrict__ WA, const int *__restrict__ WB, float *A, float *B,
                       float lrate, float vexp, HotRows hot, EvalScratch *scratch, float *retval) {
   using S = Spread<NWA * NWB>;
-  using Shape = StagedShape<NWA, NWB, NR>;
   constexpr int NROWS = NWA + NWB;
-  constexpr int NST = Shape::stages;
+  constexpr int NST = 1;
   constexpr bool HOLD_B = (NWB <= NWA);     // which side stays in registers when streaming
   constexpr int NX = HOLD_B ? NWB : NWA;    // held rows
   constexpr int NY = HOLD_B ? NWA : NWB;    // other rows
@@ -677,60 +674,7 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
     }
     float p[NWA * NWB];
 
-    if (Shape::resident) {
-      PRow<NR> Y[NY];
-      int wy[NY];
-#pragma unroll
-      for (int y = 0; y < NY; y++) {
-        wy[y] = __shfl_sync(kFullMask, myw, YOFF + y);
-        if (wy[y] >= 0)
-          prow_load(Y[y], stage + (size_t)(YOFF + y) * rowbytes, nvec, lane);
-        else
-          prow_zero(Y[y]);
-      }
-      __syncwarp();  // the stage is in registers: refill it with the next column right away
-      if (i + 1 < mycols) {
-        fill(0, ahead);
-        if (i + 2 < mycols) ahead = ids_of(i + 2);
-      }
-#pragma unroll
-      for (int y = 0; y < NY; y++)
-#pragma unroll
-        for (int x = 0; x < NX; x++)
-          p[HOLD_B ? (y * NWB + x) : (x * NWB + y)] = prow_dot_partial(X[x], Y[y]);
-      S::reduce(p, lane);
-      if constexpr (EVAL) {
-#pragma unroll
-        for (int q = 0; q < S::FIN; q++)
-          if ((spread_valid_mask<NWA * NWB>(q) >> lane) & 1u)
-            acc += log(fmax((double)(1.0f - sigmoid_guard(p[q])), 1e-20));
-      } else {
-#pragma unroll
-      for (int q = 0; q < S::FIN; q++) p[q] = -lrate * sigmoid_guard(p[q]);
-      float g[NWA * NWB];
-#pragma unroll
-      for (int idx = NWA * NWB - 1; idx >= 0; idx--)
-        g[idx] = __shfl_sync(kFullMask, p[S::slot_of(idx)], S::lane_of(idx));
-#pragma unroll
-      for (int y = 0; y < NY; y++) {
-        const float sy = __shfl_sync(kFullMask, mysc, YOFF + y);
-        PRow<NR> d;
-        prow_zero(d);
-#pragma unroll
-        for (int x = 0; x < NX; x++) prow_axpy(d, sy * g[HOLD_B ? (y * NWB + x) : (x * NWB + y)], X[x]);
-        if (wy[y] >= 0) prow_red_to(update_target(MY, SY, hot, wy[y], dim, gwarp), nvec, lane, d);
-      }
-#pragma unroll
-      for (int x = 0; x < NX; x++) {
-        const float sxx = __shfl_sync(kFullMask, mysc, XOFF + x);
-        PRow<NR> d;
-        prow_zero(d);
-#pragma unroll
-        for (int y = 0; y < NY; y++) prow_axpy(d, sxx * g[HOLD_B ? (y * NWB + x) : (x * NWB + y)], Y[y]);
-        if (wx[x] >= 0) prow_red_to(update_target(MX, SX, hot, wx[x], dim, gwarp), nvec, lane, d);
-      }
-      }
-    } else {
+    {
       float sx[NX];
 #pragma unroll
       for (int x = 0; x < NX; x++) sx[x] = __shfl_sync(kFullMask, mysc, XOFF + x);
@@ -1156,6 +1100,12 @@ static cudaError_t launch_neg_staged(int grid, int warps, size_t smem, cudaStrea
                                      int ncols, const int *ncols_dev, int nwords, const int *WA,
                                      const int *WB, float *A, float *B, float lrate, float vexp,
                                      const HotRows &hot, EvalScratch *scratch, float *retval) {
+  // never more threads than the kernel was compiled for
+  constexpr int kMaxWarps = StagedShape<NWA, NWB, NR>::max_threads / 32;
+  if (warps > kMaxWarps) {
+    warps = kMaxWarps;
+    smem = staged_warp_bytes(NWA + NWB, dim, 1) * warps;
+  }
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(neg_update_staged_kernel<NWA, NWB, NR, EVAL>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -1208,7 +1158,9 @@ static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int
   // fits for up to 10 rows of 3 vectors or 15 rows of 2
   constexpr int kMaxNr = (NWA + NWB <= 10) ? 4 : 2;
   // staged update: as many warps per block (one block per SM) as shared memory holds
-  const int staged_stages = 1, staged_max_threads = 384;  // StagedShape<...>::stages, ::max_threads
+  const int staged_stages = 1;
+  const int staged_held = (NWB <= NWA) ? NWB : NWA;  // as StagedShape<NWA, NWB, nr>
+  const int staged_max_threads = (staged_held * nr <= 15 && NWA * NWB <= 25) ? 512 : 384;
   const size_t per_warp = staged_warp_bytes(NWA + NWB, dim, staged_stages);
   const int staged_warps = (int)std::min<size_t>(staged_max_threads / 32, (227 * 1024) / per_warp);
   // scoring keeps the register-resident kernel where it exists (more warps per SM, and nothing to

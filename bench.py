@@ -45,9 +45,9 @@ POOL = 4             # distinct minibatches per rank, cycled
 CPU_SAMPLE = 500_000  # tokens of one minibatch the CPU arms process per step
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the negative-update
-# kernel on this workload (6.63 GB read + 6.79 GB written), from a one-pass ncu
+# kernel on this workload (6.48 GB read + 6.82 GB written), from a one-pass ncu
 # capture of the full-size workload; see profiles/update_kernels_zipf_vocab1M_dim300.md.
-NEG_DRAM_TRAFFIC_BYTES = 13.42e9
+NEG_DRAM_TRAFFIC_BYTES = 13.30e9
 
 
 def measured_peak_gbs():
@@ -357,7 +357,7 @@ def run_ours(args):
     # positive kernel, same accounting: (centres-with-pairs + pairs) rows read and written;
     # every token is kept in this workload, so centres ~ tokens
     pos_bytes = 2.0 * (N + pairs) * row
-    roofline = {"bound": "hbm", "kernel": "neg_update_staged_kernel<5,5,3>", "achieved": achieved, "peak": peak,
+    roofline = {"bound": "hbm", "kernel": "neg_update_staged_kernel<5,5,3,false>", "achieved": achieved, "peak": peak,
                 "peak_kind": peak_kind, "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
                 "traffic": NEG_DRAM_TRAFFIC_BYTES, "algorithmic_bytes_per_launch": neg_bytes,
                 "avg_launch_ms": neg_s * 1e3}

@@ -250,12 +250,13 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
   const int per_warp = (ncols + (int)nwarps - 1) / (int)nwarps;
   const int first = (int)gwarp * per_warp;
   const int last = min(ncols, first + per_warp);
-  const int base = first - skip;  // lowest position that can own a slot
   unsigned dirty = 0;             // bit s: slot s holds a pending delta
 
-  // B[W[u]] += slot of u, if it holds anything
-  auto retire = [&](int u) {
-    const int slot = (u - base) % slots;
+  // Slot of position t - skip, the oldest position of the current window; it
+  // advances by one per position, so no division is needed to find a slot.
+  int wslot = 0;
+  // B[W[u]] += the given slot (which belongs to position u), if it holds anything
+  auto retire = [&](int u, int slot) {
     if ((dirty >> slot) & 1u) {
       dirty &= ~(1u << slot);
       float *dst = update_target(B, hot.shadowB, hot, W[u], dim, gwarp);
@@ -298,7 +299,8 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
             const float sb = __shfl_sync(kFullMask, sc, src[c]);
             prow_axpy(da, sa * g, rows[c]);
             // context side: slot(u) += (sb * g) * a
-            const int slot = (t + src[c] - skip - base) % slots;
+            int slot = wslot + src[c];  // position t - skip + src[c]
+            if (slot >= slots) slot -= slots;
             ulonglong2 *sp = ring + slot * nvec;
             const u64 coef = pack2(sb * g, sb * g);
             const bool pending = (dirty >> slot) & 1u;
@@ -325,11 +327,15 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
       }
     }
     // no later centre of this warp reaches position t - skip
-    if (t - skip >= base && dirty) retire(t - skip);
+    if (dirty) retire(t - skip, wslot);
+    wslot = (wslot + 1 == slots) ? 0 : wslot + 1;
     if (hot.fold_every > 0 && ((t - first) % (2 * hot.fold_every)) == 2 * hot.fold_every - 1)
       fold_one_replica<NR>(hot, A, B, dim, nvec, lane, gwarp * 3u + (unsigned)((t - first) / (2 * hot.fold_every)));
   }
-  for (int u = max(last - skip, base); u < last + skip && dirty; u++) retire(u);
+  for (int k = 0; k < slots && dirty; k++) {  // positions last - skip ... last + skip
+    retire(last - skip + k, wslot);
+    wslot = (wslot + 1 == slots) ? 0 : wslot + 1;
+  }
 }
 
 // Adds this block's double partial sum into scratch[0]; the block that

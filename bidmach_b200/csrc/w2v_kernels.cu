@@ -831,16 +831,14 @@ __global__ void __launch_bounds__(kGenericThreads)
     }
     S::reduce(p, lane);
 
-    if (EVAL) {
+    if constexpr (EVAL) {
 #pragma unroll
       for (int q = 0; q < S::FIN; q++) {
         const unsigned valid = spread_valid_mask<NWA * NWB>(q);
         if ((valid >> lane) & 1u)
           acc += log(fmax((double)(1.0f - sigmoid_guard(p[q])), 1e-20));
       }
-      continue;
-    }
-
+    } else {
 #pragma unroll
     for (int q = 0; q < S::FIN; q++) p[q] = -lrate * sigmoid_guard(p[q]);
     float g[NWA * NWB];
@@ -873,6 +871,7 @@ __global__ void __launch_bounds__(kGenericThreads)
         for (int j = 0; j < NWA; j++) d = fmaf(sb[k] * g[j * NWB + k], av[j], d);
         if (wb[k] >= 0) atomicAdd(B + (int64_t)wb[k] * dim + c, d);
       }
+    }
     }
   }
   if (EVAL) finish_eval_sum(acc, scratch, retval);

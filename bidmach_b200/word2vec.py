@@ -283,9 +283,13 @@ class Word2Vec:
         if not dist.is_initialized() or dist.get_world_size(group) == 1:
             return
         self.finishMerge()
+        world = dist.get_world_size(group)
+        n = self._flat.numel()
         if getattr(self, "_snap", None) is None:
             self._snap = torch.empty_like(self._flat)
             self._avg = torch.empty_like(self._flat)
+            self._shard = (torch.empty(n // world, dtype=torch.float32, device=self.device)
+                           if n % world == 0 else None)
             self._comm = torch.cuda.Stream(device=self.device)
         compute = torch.cuda.current_stream(self.device)
         self._snap.copy_(self._flat)
@@ -293,8 +297,14 @@ class Word2Vec:
         taken.record(compute)
         with torch.cuda.stream(self._comm):
             self._comm.wait_event(taken)
-            self._avg.copy_(self._snap)
-            dist.all_reduce(self._avg, op=dist.ReduceOp.AVG, group=group)
+            if self._shard is not None:
+                # all-reduce as reduce-scatter + all-gather: both out of place, so the
+                # snapshot survives without a second model-sized copy
+                dist.reduce_scatter_tensor(self._shard, self._snap.view(-1), op=dist.ReduceOp.AVG, group=group)
+                dist.all_gather_into_tensor(self._avg.view(-1), self._shard, group=group)
+            else:
+                self._avg.copy_(self._snap)
+                dist.all_reduce(self._avg, op=dist.ReduceOp.AVG, group=group)
             done = torch.cuda.Event()
             done.record(self._comm)
         self._merge = done

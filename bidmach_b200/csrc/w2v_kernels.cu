@@ -580,9 +580,9 @@ constexpr int kWaitPolls = 1 << 20;  // polls of a stage's barrier before giving
 static __device__ int g_stage_fault;  // set when a stage never arrived; checked by the host
 
 // The smaller side of the column (NX rows) is held in registers, the larger
-// side (NY rows) is read from the stage three times: for the dot products, for
-// its own deltas (which need the held rows only), and for the deltas of the
-// held side, by which time the held rows' registers are free to carry them.
+// side (NY rows) is read from the stage twice: for the dot products and for the
+// deltas of the held side, by which time the held rows' registers are free to
+// carry them; its own deltas need the held rows only.
 // The stage is refilled with the warp's next column when the column is done.
 template <int NWA, int NWB, int NR>
 struct StagedShape {

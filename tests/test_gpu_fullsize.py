@@ -139,3 +139,37 @@ def test_training_on_full_size_minibatches_improves_the_score():
     after = m.evalbatch([held], 0, N)
     assert after > before + 2e-3, (before, after)
     assert torch.isfinite(m.modelmats[0]).all() and float(m.modelmats[0].abs().max()) < 10
+
+
+def test_heldout_score_matches_cpu_reference_at_benchmark_scale(oracle):
+    """End-to-end criterion at the benchmark's scale: vocab 1M, dim 300, six
+    1M-token Zipf(1.07) minibatches with the reference's default options; the
+    GPU path and the reference's CPU kernels (all host cores, its own racy
+    multi-threading) start from the same model and must reach the same held-out
+    score within 1 %."""
+    from bidmach_b200 import Word2Vec
+    from bidmach_b200.corpus import zipf_cdf, zipf_corpus
+    from bidmach_b200.word2vec import Opts
+    seed, nbatches = 3, 6
+    cdf = zipf_cdf(V, 1.07)
+    batches = [zipf_corpus(V, N, 1.07, seed=k, cdf=cdf) for k in range(nbatches)]
+    held = zipf_corpus(V, N, 1.07, seed=99, cdf=cdf)
+
+    o = Opts(dim=D, vocabSize=V, lrate=1e-3, seed=seed)
+    m = Word2Vec(o).init(N)
+    for k, b in enumerate(batches):
+        m.dobatchg([b], 0, (k + 1) * N)
+    gpu = m.evalbatchg([held], 0, N)
+
+    B = oracle.library_init_model(seed, D, V)
+    A = np.zeros_like(B)
+    od = dict(dim=D, vocabSize=V, nskip=5, nneg=5, nreuse=5, lrate=1e-3, texp=0.5, vexp=0.5,
+              wsample=1e-4, wexpt=0.75)
+    impl = "reference" if oracle.have_reference() else "port"
+    cpu_model = oracle.CpuWord2Vec(od, A, B, THREADS, impl)
+    rng = np.random.default_rng(5)
+    for k, b in enumerate(batches):
+        cpu_model.dobatch(b, (k + 1) * N, *oracle._draws(rng, N, 5, 5, 5))
+    cpu = cpu_model.evalbatch(held, *oracle._draws(rng, N, 5, 5, 5))
+    assert cpu > 2 * np.log(0.5) + 2e-3            # the CPU run learnt something
+    assert abs(gpu - cpu) <= 0.01 * abs(cpu), (gpu, cpu)

@@ -360,7 +360,9 @@ def run_ours(args):
     roofline = {"bound": "hbm", "kernel": "neg_update_staged_kernel<5,5,3,false>", "achieved": achieved, "peak": peak,
                 "peak_kind": peak_kind, "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
                 "traffic": NEG_DRAM_TRAFFIC_BYTES, "algorithmic_bytes_per_launch": neg_bytes,
-                "avg_launch_ms": neg_s * 1e3}
+                "avg_launch_ms": neg_s * 1e3,
+                # the same fraction from the measured DRAM bytes instead of the algorithmic ones
+                "dram_frac": (NEG_DRAM_TRAFFIC_BYTES / neg_s / 1e9 / peak) if neg_s > 0 else None}
     phases = {"prep_ms": tm.prep_ms / nb, "permute_ms": tm.permute_ms / nb, "pos_ms": tm.pos_ms / nb,
               "neg_ms": tm.neg_ms / nb, "pairs_per_step": pairs, "groups_per_step": groups,
               "pos_algorithmic_gbs": pos_bytes / pos_s / 1e9 if pos_s > 0 else None,

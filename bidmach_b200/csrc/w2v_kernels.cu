@@ -1188,7 +1188,9 @@ static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int
   }
   if (want_staged && vector_ok(dim, A, B) && nr <= 4 && staged_warps >= 2 && neg_staged_enabled()) {
     const size_t smem = per_warp * staged_warps;
-    const int grid = std::max(1, std::min(device_sm_count(), (ncols + staged_warps - 1) / staged_warps));
+    // at least 8 columns per warp: a small launch then still applies its updates in several
+    // rounds instead of computing every column from the same stale rows
+    const int grid = std::max(1, std::min(device_sm_count(), (ncols + 8 * staged_warps - 1) / (8 * staged_warps)));
     cudaError_t e = cudaSuccess;
     switch (nr) {
       case 1: e = launch_neg_staged_any<NWA, NWB, 1>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval); break;

@@ -1,0 +1,97 @@
+"""Edge cases of the whole-minibatch calls (w2v_dobatch / w2v_evalbatch) through
+the host mirror: empty pair sets, one-token minibatches, out-of-vocabulary
+text, short windows, minibatches of the wrong length."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _model(n, **kw):
+    from bidmach_b200 import Word2Vec
+    from bidmach_b200.word2vec import Opts
+    o = Opts(dim=100, vocabSize=500, wsample=1.0, lrate=0.01, seed=1)
+    for k, v in kw.items():
+        setattr(o, k, v)
+    return Word2Vec(o).init(n)
+
+
+def _toks(n, vocab, seed=0, doc=20):
+    rng = np.random.default_rng(seed)
+    t = np.empty((n, 2), np.int32)
+    t[:, 0] = rng.integers(0, vocab, n)
+    t[:, 1] = np.arange(n) // doc
+    return t
+
+
+def test_all_out_of_vocabulary_minibatch_is_a_no_op():
+    m = _model(256)
+    before = [x.clone() for x in m.modelmats]
+    toks = _toks(256, 500)
+    toks[:, 0] += 1000                      # every id >= vocabSize
+    assert m.dobatchg([toks], 0, 256) == 0
+    assert m.evalbatchg([toks], 0, 256) == 0.0
+    assert all(torch.equal(a, b) for a, b in zip(before, m.modelmats))
+
+
+def test_one_token_per_sentence_yields_no_pairs():
+    m = _model(128)
+    toks = _toks(128, 500, doc=1)           # every window is clipped to the token itself
+    assert m.dobatchg([toks], 0, 128) == 0
+    words, lb, ub, wa, wb = m.wordMats([torch.from_numpy(toks).cuda()])
+    assert int(lb.abs().max()) == 0 and int(ub.abs().max()) == 0 and wa.numel() == 0 and wb.numel() == 0
+
+
+def test_single_token_minibatch_and_fewer_pairs_than_nreuse():
+    m = _model(1)
+    assert m.dobatchg([_toks(1, 500)], 0, 1) == 0
+    m3 = _model(2)                          # two pairs < nreuse: no group, positives still train
+    before = m3.modelmats[1].clone()
+    toks = _toks(2, 500, seed=3, doc=3)
+    n = m3.dobatchg([toks], 0, 2)
+    assert n == 2
+    words, lb, ub, wa, wb = m3.wordMats([torch.from_numpy(toks).cuda()])
+    assert wa.numel() == 0
+    assert not torch.equal(before, m3.modelmats[1]) or float(m3.modelmats[0].abs().sum()) > 0
+
+
+def test_minibatch_of_another_length_is_skipped_like_the_reference():
+    m = _model(200)
+    before = [x.clone() for x in m.modelmats]
+    assert m.dobatchg([_toks(150, 500)], 0, 150) == 0
+    m.dobatch([torch.from_numpy(_toks(150, 500)).cuda()], 0, 150)
+    assert m.evalbatch([torch.from_numpy(_toks(150, 500)).cuda()], 0, 150) == 0.0
+    assert all(torch.equal(a, b) for a, b in zip(before, m.modelmats))
+
+
+@pytest.mark.parametrize("nskip,nneg,nreuse", [(2, 5, 5), (3, 10, 5), (5, 5, 10), (5, 5, 1)])
+def test_pipeline_runs_for_every_supported_shape(oracle, nskip, nneg, nreuse):
+    n = 3000
+    m = _model(n, nskip=nskip, nneg=nneg, nreuse=nreuse, dim=300)
+    toks = _toks(n, 500, seed=nskip, doc=37)
+    dt = torch.from_numpy(toks).cuda()
+    s0 = m.evalbatch([dt], 0, n)
+    # A is zero, so every dot is 0; the positive sum covers the few pairs the grouping drops too
+    assert s0 == pytest.approx(2 * np.log(0.5), abs=2e-3)
+    pairs = m.dobatchg([toks], 0, n)
+    words, lb, ub, wa, wb = m.wordMats([dt])
+    assert int(ub.max()) <= nskip and int(lb.min()) >= -nskip
+    assert pairs > 0
+    assert wa.shape[1] == nneg and wb.shape[1] == nreuse
+    assert wb.shape[0] == wa.shape[0] == m.last_contexts.numel() // nreuse   # this call drew its own windows
+    for _ in range(7):
+        m.dobatch([dt], 0, n)
+    assert m.evalbatch([dt], 0, n) > s0 + 0.1                   # training on it raises its score
+    assert torch.isfinite(m.modelmats[0]).all() and torch.isfinite(m.modelmats[1]).all()
+
+
+def test_unsupported_options_are_refused():
+    from bidmach_b200 import Word2Vec
+    from bidmach_b200.word2vec import Opts
+    with pytest.raises(RuntimeError):
+        Word2Vec(Opts(dim=100, vocabSize=100, nneg=7, nreuse=3)).init(64)
+    with pytest.raises(NotImplementedError):
+        Word2Vec(Opts(nSlices=2))
+    with pytest.raises(RuntimeError):
+        Word2Vec(Opts(useGPU=False))

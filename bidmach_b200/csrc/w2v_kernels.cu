@@ -228,9 +228,30 @@ __device__ __forceinline__ Neighbour look_at_neighbour(const int *__restrict__ W
   return nb;
 }
 
+// Only the last of a lane's NR vectors can fall off the end of a row (NR is
+// ceil(nvec / 32)), so one flag per lane replaces a bounds test per access.
+template <int NR>
+__device__ __forceinline__ bool vec_ok(int q, bool tail) {
+  return q < NR - 1 || tail;
+}
+
+// prow_load for a lane that already knows whether its last vector exists;
+// `base` points at the lane's first vector.
+template <int NR>
+__device__ __forceinline__ void prow_load_lane(PRow<NR> &r, const ulonglong2 *base, bool tail) {
+#pragma unroll
+  for (int q = 0; q < NR; q++) {
+    ulonglong2 t = make_ulonglong2(0ull, 0ull);
+    if (vec_ok<NR>(q, tail)) t = base[32 * q];
+    r.v[q][0] = t.x;
+    r.v[q][1] = t.y;
+  }
+}
+
 // Shared memory: per warp, (2*skip+1) slots of nvec float4 (one context-row
-// delta each).  Lane l only ever touches elements l, l+32, ... of a slot, so no
-// synchronisation is needed between the lanes of the owning warp.
+// delta each), all zero whenever they hold nothing.  Lane l only ever touches
+// elements l, l+32, ... of a slot, so no synchronisation is needed between the
+// lanes of the owning warp.
 template <int NR>
 __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
     pos_update_kernel(int dim, int ncols, const int *__restrict__ ncols_dev, int skip,
@@ -238,12 +259,12 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
                       const int *__restrict__ UB, float *A, float *B, float lrate, float vexp,
                       HotRows hot) {
   constexpr int kChunk = ChunkOf<NR>::value;
-  static_assert(Spread<kChunk>::FIN == 1, "one total per lane expected");
   extern __shared__ ulonglong2 ring_storage[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = dim >> 2;
+  const bool tail = lane + 32 * (NR - 1) < nvec;
   const int slots = 2 * skip + 1;
-  ulonglong2 *ring = ring_storage + (size_t)warp * slots * nvec;
+  ulonglong2 *ring = ring_storage + (size_t)warp * slots * nvec + lane;  // this lane's part of slot 0
   const unsigned gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const unsigned nwarps = (gridDim.x * blockDim.x) >> 5;
   if (ncols_dev) ncols = *ncols_dev;
@@ -251,23 +272,33 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
   const int first = (int)gwarp * per_warp;
   const int last = min(ncols, first + per_warp);
   unsigned dirty = 0;             // bit s: slot s holds a pending delta
+  for (int s = 0; s < slots; s++) {
+#pragma unroll
+    for (int q = 0; q < NR; q++)
+      if (vec_ok<NR>(q, tail)) ring[s * nvec + 32 * q] = make_ulonglong2(0ull, 0ull);
+  }
 
   // Slot of position t - skip, the oldest position of the current window; it
   // advances by one per position, so no division is needed to find a slot.
   int wslot = 0;
-  // B[W[u]] += the given slot (which belongs to position u), if it holds anything
+  // B[W[u]] += the given slot (which belongs to position u), if it holds
+  // anything; the slot is left zeroed for the position that takes it next
   auto retire = [&](int u, int slot) {
     if ((dirty >> slot) & 1u) {
       dirty &= ~(1u << slot);
-      float *dst = update_target(B, hot.shadowB, hot, W[u], dim, gwarp);
-      const float4 *sp = reinterpret_cast<const float4 *>(ring + slot * nvec);
+      float *dst = update_target(B, hot.shadowB, hot, W[u], dim, gwarp) + 4 * lane;
+      ulonglong2 *sp = ring + slot * nvec;
 #pragma unroll
       for (int q = 0; q < NR; q++) {
-        const int idx = lane + 32 * q;
-        if (idx < nvec) red_add_v4(dst + 4 * idx, sp[idx]);
+        if (vec_ok<NR>(q, tail)) {
+          red_add_v4(dst + 128 * q, *reinterpret_cast<const float4 *>(sp + 32 * q));
+          sp[32 * q] = make_ulonglong2(0ull, 0ull);
+        }
       }
     }
   };
+  int until_fold = 2 * hot.fold_every;
+  unsigned fold_turn = gwarp * 3u;
 
   for (int t = first; t < last; t++) {
     const int wt = W[t];
@@ -282,19 +313,29 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
         const float sc = (sid >= 0) ? freq_scale(sid, vexp) : 0.f;
         const float sa = __shfl_sync(kFullMask, sc, 31);
         PRow<NR> a, da;
-        prow_load(a, A + (int64_t)wt * dim, nvec, lane);
+        prow_load_lane(a, reinterpret_cast<const ulonglong2 *>(A + (int64_t)wt * dim) + lane, tail);
         prow_zero(da);
-        // the contexts are taken kChunk at a time; a remainder of one or two
-        // gets a narrower pass so that it does not pay for kChunk rows
+        // CH contexts at a time: their rows are loaded together, the CH dot
+        // products are reduced together and one lane each evaluates a sigmoid
         auto take = [&](auto width) {
           constexpr int CH = decltype(width)::value;
+          static_assert(Spread<CH>::FIN == 1, "one total per lane expected");
           int src[CH];
           PRow<NR> rows[CH];
-          const float dot = chunk_dots<NR, CH>(todo, src, rows, a, B, nb.word, dim, nvec, lane);
-          const float mine = lrate * (1.0f - sigmoid_guard(dot));
+          float p[CH];
 #pragma unroll
           for (int c = 0; c < CH; c++) {
-            if (src[c] < 0) continue;
+            src[c] = __ffs(todo) - 1;
+            todo &= todo - 1;
+            const int64_t w = __shfl_sync(kFullMask, nb.word, src[c]);
+            prow_load_lane(rows[c], reinterpret_cast<const ulonglong2 *>(B + w * dim) + lane, tail);
+          }
+#pragma unroll
+          for (int c = 0; c < CH; c++) p[c] = prow_dot_partial(a, rows[c]);
+          Spread<CH>::reduce(p, lane);
+          const float mine = lrate * (1.0f - sigmoid_guard(p[0]));
+#pragma unroll
+          for (int c = 0; c < CH; c++) {
             const float g = __shfl_sync(kFullMask, mine, Spread<CH>::lane_of(c));
             const float sb = __shfl_sync(kFullMask, sc, src[c]);
             prow_axpy(da, sa * g, rows[c]);
@@ -303,25 +344,28 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
             if (slot >= slots) slot -= slots;
             ulonglong2 *sp = ring + slot * nvec;
             const u64 coef = pack2(sb * g, sb * g);
-            const bool pending = (dirty >> slot) & 1u;
             dirty |= 1u << slot;
 #pragma unroll
             for (int q = 0; q < NR; q++) {
-              const int idx = lane + 32 * q;
-              if (idx < nvec) {
-                ulonglong2 v = pending ? sp[idx] : make_ulonglong2(0ull, 0ull);
+              if (vec_ok<NR>(q, tail)) {
+                ulonglong2 v = sp[32 * q];
                 v.x = fma2(coef, a.v[q][0], v.x);
                 v.y = fma2(coef, a.v[q][1], v.y);
-                sp[idx] = v;
+                sp[32 * q] = v;
               }
             }
           }
         };
-        while (todo) {
-          if (kChunk > 2 && __popc(todo) <= 2)
-            take(std::integral_constant<int, 2>());
-          else
-            take(std::integral_constant<int, kChunk>());
+        // a window larger than one chunk is split evenly (6 contexts as 3 + 3, not 5 + 1)
+        int cnt = __popc(todo);
+        while (cnt > 0) {
+          const int n = cnt > kChunk ? min(kChunk, (cnt + 1) >> 1) : cnt;
+          cnt -= n;
+          if (n == 1) take(std::integral_constant<int, 1>());
+          if constexpr (kChunk >= 2) { if (n == 2) take(std::integral_constant<int, 2>()); }
+          if constexpr (kChunk >= 3) { if (n == 3) take(std::integral_constant<int, 3>()); }
+          if constexpr (kChunk >= 4) { if (n == 4) take(std::integral_constant<int, 4>()); }
+          if constexpr (kChunk >= 5) { if (n == 5) take(std::integral_constant<int, 5>()); }
         }
         prow_red_to(update_target(A, hot.shadowA, hot, wt, dim, gwarp), nvec, lane, da);
       }
@@ -329,8 +373,10 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
     // no later centre of this warp reaches position t - skip
     if (dirty) retire(t - skip, wslot);
     wslot = (wslot + 1 == slots) ? 0 : wslot + 1;
-    if (hot.fold_every > 0 && ((t - first) % (2 * hot.fold_every)) == 2 * hot.fold_every - 1)
-      fold_one_replica<NR>(hot, A, B, dim, nvec, lane, gwarp * 3u + (unsigned)((t - first) / (2 * hot.fold_every)));
+    if (hot.fold_every > 0 && --until_fold == 0) {
+      until_fold = 2 * hot.fold_every;
+      fold_one_replica<NR>(hot, A, B, dim, nvec, lane, fold_turn++);
+    }
   }
   for (int k = 0; k < slots && dirty; k++) {  // positions last - skip ... last + skip
     retire(last - skip + k, wslot);

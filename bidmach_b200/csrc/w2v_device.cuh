@@ -24,6 +24,10 @@ __device__ __forceinline__ float sigmoid_guard(float x) {
   return e / (1.0f + e);
 }
 
+// log(max(v, 1e-20)) of one pair's probability, evaluated in fp32 as the
+// reference kernels do (jni/src/DNN127.cu:318); the sums are kept in double.
+__device__ __forceinline__ double pair_score(float v) { return (double)logf(fmaxf(v, 1.0e-20f)); }
+
 // (1 + id)^vexp, the per-word learning-rate scale (BIDMach_CPUMACH.c:33,42;
 // jni/src/DNN127.cu:145,149 forms the same value from the row offset).
 __device__ __forceinline__ float freq_scale(int id, float vexp) {
@@ -214,6 +218,11 @@ __device__ __forceinline__ u64 fma2(u64 a, u64 b, u64 c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
   return d;
 }
+__device__ __forceinline__ u64 mul2(u64 a, u64 b) {
+  u64 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 __device__ __forceinline__ u64 pack2(float x, float y) {
   u64 d;
   asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(x), "f"(y));
@@ -249,16 +258,29 @@ __device__ __forceinline__ void prow_load(PRow<NR> &r, const void *base, int nve
 
 template <int NR>
 __device__ __forceinline__ float prow_dot_partial(const PRow<NR> &a, const PRow<NR> &b) {
-  u64 s0 = 0ull, s1 = 0ull;
+  // one packed accumulator: many dot products are always in flight, so the
+  // longer dependency chain costs nothing and the final sum is one add
+  u64 s = mul2(a.v[0][0], b.v[0][0]);
+  s = fma2(a.v[0][1], b.v[0][1], s);
+#pragma unroll
+  for (int q = 1; q < NR; q++) {
+    s = fma2(a.v[q][0], b.v[q][0], s);
+    s = fma2(a.v[q][1], b.v[q][1], s);
+  }
+  float x, y;
+  unpack2(s, x, y);
+  return x + y;
+}
+
+// acc = c * x
+template <int NR>
+__device__ __forceinline__ void prow_scale(PRow<NR> &acc, float c, const PRow<NR> &x) {
+  const u64 cc = pack2(c, c);
 #pragma unroll
   for (int q = 0; q < NR; q++) {
-    s0 = fma2(a.v[q][0], b.v[q][0], s0);
-    s1 = fma2(a.v[q][1], b.v[q][1], s1);
+    acc.v[q][0] = mul2(cc, x.v[q][0]);
+    acc.v[q][1] = mul2(cc, x.v[q][1]);
   }
-  float x0, y0, x1, y1;
-  unpack2(s0, x0, y0);
-  unpack2(s1, x1, y1);
-  return (x0 + y0) + (x1 + y1);
 }
 
 // acc += c * x

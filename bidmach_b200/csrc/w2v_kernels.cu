@@ -182,31 +182,6 @@ struct PosBlocksOf {
   static constexpr int value = NR <= 3 ? 4 : (NR <= 5 ? 2 : 1);
 };
 
-// Takes up to kChunk set bits out of `todo` (lane numbers of neighbours), loads
-// their rows from M and returns the per-lane share of the kChunk dot products
-// with `own` after the spreading reduction: lane Spread::lane_of(c) holds dot c.
-template <int NR, int kChunk>
-__device__ __forceinline__ float chunk_dots(unsigned &todo, int (&src)[kChunk],
-                                            PRow<NR> (&rows)[kChunk], const PRow<NR> &own,
-                                            const float *M, int wnb, int dim, int nvec, int lane) {
-#pragma unroll
-  for (int c = 0; c < kChunk; c++) {
-    if (todo) {
-      src[c] = __ffs(todo) - 1;
-      todo &= todo - 1;
-      prow_load(rows[c], M + (int64_t)__shfl_sync(kFullMask, wnb, src[c]) * dim, nvec, lane);
-    } else {
-      src[c] = -1;
-      prow_zero(rows[c]);
-    }
-  }
-  float p[kChunk];
-#pragma unroll
-  for (int c = 0; c < kChunk; c++) p[c] = prow_dot_partial(own, rows[c]);
-  Spread<kChunk>::reduce(p, lane);
-  return p[0];
-}
-
 // What lane `lane` sees at offset lane - skip from position t: the word there
 // and whether t, as a centre, pairs with it.
 struct Neighbour {
@@ -245,6 +220,20 @@ __device__ __forceinline__ void prow_load_lane(PRow<NR> &r, const ulonglong2 *ba
     if (vec_ok<NR>(q, tail)) t = base[32 * q];
     r.v[q][0] = t.x;
     r.v[q][1] = t.y;
+  }
+}
+
+// dst[...] += r, `dst` pointing at the lane's first vector of the destination row.
+template <int NR>
+__device__ __forceinline__ void prow_red_lane(float *dst, bool tail, const PRow<NR> &r) {
+#pragma unroll
+  for (int q = 0; q < NR; q++) {
+    if (vec_ok<NR>(q, tail)) {
+      float4 v;
+      unpack2(r.v[q][0], v.x, v.y);
+      unpack2(r.v[q][1], v.z, v.w);
+      red_add_v4(dst + 128 * q, v);
+    }
   }
 }
 
@@ -367,7 +356,7 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
           if constexpr (kChunk >= 4) { if (n == 4) take(std::integral_constant<int, 4>()); }
           if constexpr (kChunk >= 5) { if (n == 5) take(std::integral_constant<int, 5>()); }
         }
-        prow_red_to(update_target(A, hot.shadowA, hot, wt, dim, gwarp), nvec, lane, da);
+        prow_red_lane(update_target(A, hot.shadowA, hot, wt, dim, gwarp) + 4 * lane, tail, da);
       }
     }
     // no later centre of this warp reaches position t - skip
@@ -420,12 +409,15 @@ __global__ void __launch_bounds__(kPosThreads)
   constexpr int kChunk = ChunkOf<NR>::value;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = dim >> 2;
+  const bool tail = lane + 32 * (NR - 1) < nvec;
   if (ncols_dev) ncols = *ncols_dev;
   const int per_block = (ncols + gridDim.x - 1) / gridDim.x;
   const int first = blockIdx.x * per_block;
   const int last = min(ncols, first + per_block);
   double acc = 0.0;
 
+  // neighbouring positions go to the warps of one block: their windows overlap,
+  // so most context rows are found in L1
   for (int t = first + warp; t < last; t += (int)(blockDim.x >> 5)) {
     const int wt = W[t];
     if (wt < 0) continue;
@@ -434,16 +426,33 @@ __global__ void __launch_bounds__(kPosThreads)
     unsigned todo = __ballot_sync(kFullMask, nb.t_is_centre);
     if (todo == 0) continue;
     PRow<NR> own;
-    prow_load(own, A + (int64_t)wt * dim, nvec, lane);
-    while (todo) {
-      int src[kChunk];
-      PRow<NR> rows[kChunk];
-      const float dot = chunk_dots(todo, src, rows, own, B, nb.word, dim, nvec, lane);
-      // the lane that holds a pair's dot product scores it (networks/Word2Vec.scala:995)
+    prow_load_lane(own, reinterpret_cast<const ulonglong2 *>(A + (int64_t)wt * dim) + lane, tail);
+    auto take = [&](auto width) {
+      constexpr int CH = decltype(width)::value;
+      PRow<NR> rows[CH];
+      float p[CH];
 #pragma unroll
-      for (int c = 0; c < kChunk; c++)
-        if (src[c] >= 0 && lane == Spread<kChunk>::lane_of(c))
-          acc += log(fmax((double)sigmoid_guard(dot), 1e-20));
+      for (int c = 0; c < CH; c++) {
+        const int src = __ffs(todo) - 1;
+        todo &= todo - 1;
+        const int64_t w = __shfl_sync(kFullMask, nb.word, src);
+        prow_load_lane(rows[c], reinterpret_cast<const ulonglong2 *>(B + w * dim) + lane, tail);
+      }
+#pragma unroll
+      for (int c = 0; c < CH; c++) p[c] = prow_dot_partial(own, rows[c]);
+      Spread<CH>::reduce(p, lane);
+      // the lane that holds a pair's dot product scores it (networks/Word2Vec.scala:995)
+      if ((spread_valid_mask<CH>(0) >> lane) & 1u) acc += pair_score(sigmoid_guard(p[0]));
+    };
+    int cnt = __popc(todo);
+    while (cnt > 0) {
+      const int n = cnt > kChunk ? min(kChunk, (cnt + 1) >> 1) : cnt;
+      cnt -= n;
+      if (n == 1) take(std::integral_constant<int, 1>());
+      if constexpr (kChunk >= 2) { if (n == 2) take(std::integral_constant<int, 2>()); }
+      if constexpr (kChunk >= 3) { if (n == 3) take(std::integral_constant<int, 3>()); }
+      if constexpr (kChunk >= 4) { if (n == 4) take(std::integral_constant<int, 4>()); }
+      if constexpr (kChunk >= 5) { if (n == 5) take(std::integral_constant<int, 5>()); }
     }
   }
   finish_eval_sum(acc, scratch, retval);
@@ -530,7 +539,7 @@ __global__ void __launch_bounds__(kGenericThreads)
       p = warp_sum(p);
       if (lane == src) mine = p;
     }
-    if (wx >= 0) acc += log(fmax((double)sigmoid_guard(mine), 1e-20));
+    if (wx >= 0) acc += pair_score(sigmoid_guard(mine));
   }
   finish_eval_sum(acc, scratch, retval);
 }
@@ -681,6 +690,9 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
 
   const int mycols = (gwarp < ncols) ? (ncols - gwarp + nwarps - 1) / nwarps : 0;
   double acc = 0.0;  // EVAL: this lane's share of the score
+  const bool tail = lane + 32 * (NR - 1) < nvec;
+  int until_fold = hot.fold_every;
+  unsigned fold_turn = (unsigned)gwarp * 5u;
 
   // Starts the copies of a column (word ids in `w`, one per lane) into stage `st`.
   auto fill = [&](int st, int w) {
@@ -712,94 +724,131 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
     }
     const int myw = (lane < 16) ? ids[st * 16 + lane] : -1;
     const float mysc = (myw >= 0) ? freq_scale(myw, vexp) : 0.f;
-    const unsigned char *stage = stages + st * stage_bytes;
+    const ulonglong2 *stage = reinterpret_cast<const ulonglong2 *>(stages + st * stage_bytes) + lane;
+    auto staged_row = [&](int r) {  // this lane's first vector of row r of the stage
+      return reinterpret_cast<const ulonglong2 *>(reinterpret_cast<const unsigned char *>(stage) +
+                                                  (size_t)r * rowbytes);
+    };
 
-    PRow<NR> X[NX];
-    int wx[NX];
+    auto refill = [&]() {
+      if (i + 1 < mycols) {
+        fill(0, ahead);
+        if (i + 2 < mycols) ahead = ids_of(i + 2);
+      }
+    };
+    // CHECKED = false: every word of the column is present (the usual case), so
+    // no row needs a test; CHECKED = true: masked words act as zero rows and
+    // receive no update.
+    auto column = [&](auto checked_t) {
+      constexpr bool CHECKED = decltype(checked_t)::value;
+      PRow<NR> X[NX];
+      int wx[NX];
 #pragma unroll
-    for (int x = 0; x < NX; x++) {
-      wx[x] = __shfl_sync(kFullMask, myw, XOFF + x);
-      if (wx[x] >= 0)
-        prow_load(X[x], stage + (size_t)(XOFF + x) * rowbytes, nvec, lane);
-      else
-        prow_zero(X[x]);
-    }
-    float p[NWA * NWB];
-
-    {
+      for (int x = 0; x < NX; x++) {
+        wx[x] = __shfl_sync(kFullMask, myw, XOFF + x);
+        if (!CHECKED || wx[x] >= 0)
+          prow_load_lane(X[x], staged_row(XOFF + x), tail);
+        else
+          prow_zero(X[x]);
+      }
+      float p[NWA * NWB];
       float sx[NX];
 #pragma unroll
       for (int x = 0; x < NX; x++) sx[x] = __shfl_sync(kFullMask, mysc, XOFF + x);
 #pragma unroll
       for (int y = 0; y < NY; y++) {
-        const int wy = __shfl_sync(kFullMask, myw, YOFF + y);
         PRow<NR> Y;
-        if (wy >= 0)
-          prow_load(Y, stage + (size_t)(YOFF + y) * rowbytes, nvec, lane);
+        if (!CHECKED || __shfl_sync(kFullMask, myw, YOFF + y) >= 0)
+          prow_load_lane(Y, staged_row(YOFF + y), tail);
         else
           prow_zero(Y);
 #pragma unroll
         for (int x = 0; x < NX; x++)
           p[HOLD_B ? (y * NWB + x) : (x * NWB + y)] = prow_dot_partial(X[x], Y);
       }
+      if constexpr (EVAL) {
+        __syncwarp();  // scoring needs the stage no longer: the next column's copies start now
+        refill();
+      }
       S::reduce(p, lane);
       if constexpr (EVAL) {
 #pragma unroll
         for (int q = 0; q < S::FIN; q++)
           if ((spread_valid_mask<NWA * NWB>(q) >> lane) & 1u)
-            acc += log(fmax((double)(1.0f - sigmoid_guard(p[q])), 1e-20));
+            acc += pair_score(1.0f - sigmoid_guard(p[q]));
       } else {
 #pragma unroll
-      for (int q = 0; q < S::FIN; q++) p[q] = -lrate * sigmoid_guard(p[q]);
-      float g[NWA * NWB];
+        for (int q = 0; q < S::FIN; q++) p[q] = -lrate * sigmoid_guard(p[q]);
+        float g[NWA * NWB];
 #pragma unroll
-      for (int idx = NWA * NWB - 1; idx >= 0; idx--)
-        g[idx] = __shfl_sync(kFullMask, p[S::slot_of(idx)], S::lane_of(idx));
-      // rows of the streamed side: their deltas need the held rows only
+        for (int idx = NWA * NWB - 1; idx >= 0; idx--)
+          g[idx] = __shfl_sync(kFullMask, p[S::slot_of(idx)], S::lane_of(idx));
+        // rows of the streamed side: their deltas need the held rows only
 #pragma unroll
-      for (int y = 0; y < NY; y++) {
-        const int wy = __shfl_sync(kFullMask, myw, YOFF + y);
-        const float sy = __shfl_sync(kFullMask, mysc, YOFF + y);
-        PRow<NR> dY;
-        prow_zero(dY);
+        for (int y = 0; y < NY; y++) {
+          const int wy = __shfl_sync(kFullMask, myw, YOFF + y);
+          const float sy = __shfl_sync(kFullMask, mysc, YOFF + y);
+          PRow<NR> dY;
+          prow_scale(dY, sy * g[HOLD_B ? (y * NWB + 0) : (0 * NWB + y)], X[0]);
+#pragma unroll
+          for (int x = 1; x < NX; x++)
+            prow_axpy(dY, sy * g[HOLD_B ? (y * NWB + x) : (x * NWB + y)], X[x]);
+          if (!CHECKED || wy >= 0)
+            prow_red_lane(update_target(MY, SY, hot, wy, dim, gwarp) + 4 * lane, tail, dY);
+        }
+        // rows of the held side: the held rows themselves are dead by now, their
+        // registers carry the deltas while the other side streams by once more
+        if constexpr (CHECKED) {
+#pragma unroll
+          for (int x = 0; x < NX; x++) prow_zero(X[x]);
+        }
+#pragma unroll
+        for (int y = 0; y < NY; y++) {
+          if (CHECKED && __shfl_sync(kFullMask, myw, YOFF + y) < 0) continue;
+          PRow<NR> Y;
+          prow_load_lane(Y, staged_row(YOFF + y), tail);
+#pragma unroll
+          for (int x = 0; x < NX; x++) {
+            const float c = sx[x] * g[HOLD_B ? (y * NWB + x) : (x * NWB + y)];
+            if (!CHECKED && y == 0)
+              prow_scale(X[x], c, Y);
+            else
+              prow_axpy(X[x], c, Y);
+          }
+        }
 #pragma unroll
         for (int x = 0; x < NX; x++)
-          prow_axpy(dY, sy * g[HOLD_B ? (y * NWB + x) : (x * NWB + y)], X[x]);
-        if (wy >= 0) prow_red_to(update_target(MY, SY, hot, wy, dim, gwarp), nvec, lane, dY);
+          if (!CHECKED || wx[x] >= 0)
+            prow_red_lane(update_target(MX, SX, hot, wx[x], dim, gwarp) + 4 * lane, tail, X[x]);
       }
-      // rows of the held side: the held rows themselves are dead by now, their
-      // registers carry the deltas while the other side streams by once more
-#pragma unroll
-      for (int x = 0; x < NX; x++) prow_zero(X[x]);
-#pragma unroll
-      for (int y = 0; y < NY; y++) {
-        const int wy = __shfl_sync(kFullMask, myw, YOFF + y);
-        if (wy < 0) continue;
-        PRow<NR> Y;
-        prow_load(Y, stage + (size_t)(YOFF + y) * rowbytes, nvec, lane);
-#pragma unroll
-        for (int x = 0; x < NX; x++)
-          prow_axpy(X[x], sx[x] * g[HOLD_B ? (y * NWB + x) : (x * NWB + y)], Y);
-      }
-#pragma unroll
-      for (int x = 0; x < NX; x++)
-        if (wx[x] >= 0)
-          prow_red_to(update_target(MX, SX, hot, wx[x], dim, gwarp), nvec, lane, X[x]);
-      }
+    };
+    if (__all_sync(kFullMask, lane >= NROWS || myw >= 0))
+      column(std::false_type());
+    else
+      column(std::true_type());
+    if constexpr (!EVAL) {
       __syncwarp();  // every lane is done with this stage: start the copies of the next column
-      if (i + 1 < mycols) {
-        fill(0, ahead);
-        if (i + 2 < mycols) ahead = ids_of(i + 2);
-      }
+      refill();
     }
-    if (!EVAL && hot.fold_every > 0 && (i % hot.fold_every) == hot.fold_every - 1)
-      fold_one_replica<NR>(hot, A, B, dim, nvec, lane, (unsigned)gwarp * 5u + (unsigned)(i / hot.fold_every));
+    if (!EVAL && hot.fold_every > 0 && --until_fold == 0) {
+      until_fold = hot.fold_every;
+      fold_one_replica<NR>(hot, A, B, dim, nvec, lane, fold_turn++);
+    }
   }
   if constexpr (EVAL) finish_eval_sum(acc, scratch, retval);
 }
 
+// Scoring of the negative columns: the smaller side of a column is held in
+// registers, the rows of the other side stream through once, straight from
+// global memory (nothing is written, so there is nothing to stage around).
 template <int NWA, int NWB, int NR>
-__global__ void __launch_bounds__(kNegThreads)
+struct NegEvalShape {
+  static constexpr int held = (NWB <= NWA) ? NWB : NWA;
+  static constexpr int blocks = (held * NR <= 15) ? 4 : 2;  // resident blocks of kNegThreads per SM
+};
+
+template <int NWA, int NWB, int NR>
+__global__ void __launch_bounds__(kNegThreads, (NegEvalShape<NWA, NWB, NR>::blocks))
     neg_eval_kernel(int dim, int ncols, const int *__restrict__ ncols_dev,
                     const int *__restrict__ WA, const int *__restrict__ WB,
                     const float *__restrict__ A, const float *__restrict__ B,
@@ -807,33 +856,45 @@ __global__ void __launch_bounds__(kNegThreads)
   // wa_stride / wb_stride: words per column in WA / WB (NWA / NWB, or more when
   // this launch scores one half of a wider column)
   using S = Spread<NWA * NWB>;
+  constexpr bool HOLD_B = (NWB <= NWA);
+  constexpr int NX = HOLD_B ? NWB : NWA, NY = HOLD_B ? NWA : NWB;
+  constexpr int XOFF = HOLD_B ? NWA : 0, YOFF = HOLD_B ? 0 : NWA;
   const int lane = threadIdx.x & 31;
   const int nvec = dim >> 2;
+  const bool tail = lane + 32 * (NR - 1) < nvec;
   const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
   if (ncols_dev) ncols = *ncols_dev;
+  const float *const MX = HOLD_B ? B : A, *const MY = HOLD_B ? A : B;
   double acc = 0.0;
 
   for (int col = gwarp; col < ncols; col += nwarps) {
-    int myw = -1;
+    int myw = 0;
     if (lane < NWA)
       myw = WA[(int64_t)col * wa_stride + lane];
     else if (lane < NWA + NWB)
       myw = WB[(int64_t)col * wb_stride + (lane - NWA)];
-    Row<NR> a[NWA], b[NWB];
+    PRow<NR> X[NX];
 #pragma unroll
-    for (int j = 0; j < NWA; j++)
-      row_load(a[j], A, __shfl_sync(kFullMask, myw, j), dim, nvec, lane);
-#pragma unroll
-    for (int k = 0; k < NWB; k++)
-      row_load(b[k], B, __shfl_sync(kFullMask, myw, NWA + k), dim, nvec, lane);
+    for (int x = 0; x < NX; x++) {
+      const int64_t w = __shfl_sync(kFullMask, myw, XOFF + x);
+      prow_load_lane(X[x], reinterpret_cast<const ulonglong2 *>(MX + w * dim) + lane, tail);
+    }
     float p[NWA * NWB];
-    column_dots<NWA, NWB, NR>(a, b, p, lane);
+#pragma unroll
+    for (int y = 0; y < NY; y++) {
+      const int64_t w = __shfl_sync(kFullMask, myw, YOFF + y);
+      PRow<NR> Y;
+      prow_load_lane(Y, reinterpret_cast<const ulonglong2 *>(MY + w * dim) + lane, tail);
+#pragma unroll
+      for (int x = 0; x < NX; x++)
+        p[HOLD_B ? (y * NWB + x) : (x * NWB + y)] = prow_dot_partial(X[x], Y);
+    }
+    S::reduce(p, lane);
 #pragma unroll
     for (int q = 0; q < S::FIN; q++) {
       const unsigned valid = spread_valid_mask<NWA * NWB>(q);
-      if ((valid >> lane) & 1u)
-        acc += log(fmax((double)(1.0f - sigmoid_guard(p[q])), 1e-20));
+      if ((valid >> lane) & 1u) acc += pair_score(1.0f - sigmoid_guard(p[q]));
     }
   }
   finish_eval_sum(acc, scratch, retval);
@@ -882,7 +943,7 @@ __global__ void __launch_bounds__(kGenericThreads)
       for (int q = 0; q < S::FIN; q++) {
         const unsigned valid = spread_valid_mask<NWA * NWB>(q);
         if ((valid >> lane) & 1u)
-          acc += log(fmax((double)(1.0f - sigmoid_guard(p[q])), 1e-20));
+          acc += pair_score(1.0f - sigmoid_guard(p[q]));
       }
     } else {
 #pragma unroll

@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
     for (int q = 0; q < S::FIN; q++) {
       const unsigned valid = spread_valid_mask<NWA * NWB>(q);
-      if ((valid >> lane) & 1u) acc += log(fmax((double)(1.0f - sigmoid_guard(p[q])), 1e-20));
+      if ((valid >> lane) & 1u) acc += pair_score(1.0f - sigmoid_guard(p[q]));
     }
   }
 

@@ -60,6 +60,7 @@ class LearnerOpts:
     updateAll: bool = False
     syncStep: int = 2
     overlapSync: bool = False   # not in the reference: exchange beside the next minibatch
+    headSync: bool = False      # the reference's schedule: syncs average a growing head of the vocabulary
 
 
 def _scala_mod(a: int, b: int) -> int:
@@ -85,6 +86,9 @@ class Learner:
         self.model.init(self.datasource.batchSize)
 
     def _after_train_step(self, istep_global: int):
+        pass
+
+    def _after_minibatch(self):
         pass
 
     def train(self, do_init: bool = True):
@@ -113,6 +117,7 @@ class Learner:
             else:
                 self.model.dobatchg(mats, self.ipass, self.here)
                 self._after_train_step(istep)
+            self._after_minibatch()
             istep += 1
         self.ipass += 1
 
@@ -141,6 +146,7 @@ class ParLearner(Learner):
         super().__init__(datasource, model, opts)
         self.group = group
         self._since_sync = 0
+        self._istep = 0          # ParLearner's istep: minibatches handed out over all replicas
 
     def init(self):
         import torch.distributed as dist
@@ -150,7 +156,24 @@ class ParLearner(Learner):
                 dist.broadcast(m, src=dist.get_global_rank(self.group, 0) if self.group else 0,
                                group=self.group)
 
+    def _world(self) -> int:
+        import torch.distributed as dist
+        return dist.get_world_size(self.group) if dist.is_initialized() else 1
+
+    def _after_minibatch(self):
+        # Learner.scala:654-655: after every round of one minibatch per replica (scoring
+        # rounds included), `istep += nthreads;
+        # if ((istep/nthreads) % syncStep == 0) syncmodels(..., istep/syncStep, ...)`
+        if not self.opts.headSync:
+            return
+        world = self._world()
+        self._istep += world
+        if (self._istep // world) % self.opts.syncStep == 0:
+            self.model.mergeModelFn(self.group, self._istep // self.opts.syncStep)
+
     def _after_train_step(self, istep_global: int):
+        if self.opts.headSync:
+            return
         self._since_sync += 1
         if self.opts.overlapSync:
             if self._since_sync == 1:

@@ -253,17 +253,40 @@ class Word2Vec:
         return float(ret.item())
 
     # -- multi-GPU ------------------------------------------------------------
-    def mergeModelFn(self, group=None):
-        """Replaces Word2Vec.mergeModelFn (Word2Vec.scala:547-568), which averages a
-        frequency-ranked prefix of each matrix through host-driven peer copies:
-        here the whole model (both matrices, one buffer) is averaged over the
-        process group with one all-reduce (NCCL over NVLink when the group's
-        backend is nccl).  Blocks the compute stream until the average is in."""
+    @staticmethod
+    def mergeHeadLen(headlen: int, istep: int, vocab: int) -> int:
+        """Rows of each matrix that sync number ``istep`` of the reference
+        averages (Word2Vec.scala:548): all of them for ``istep == 0``, else the
+        first ``max(headlen, headlen << trailingZeros(istep))`` (Int arithmetic:
+        the shift count wraps at 32 and the product at 2^32), at most ``vocab``."""
+        if istep <= 0:
+            return vocab
+        tz = (istep & -istep).bit_length() - 1
+        shifted = (headlen << (tz & 31)) & 0xFFFFFFFF
+        if shifted >= 1 << 31:
+            shifted -= 1 << 32
+        return min(vocab, max(headlen, shifted))
+
+    def mergeModelFn(self, group=None, istep: int = 0):
+        """Word2Vec.mergeModelFn (Word2Vec.scala:547-568): every replica ends up
+        with the mean over the process group.  ``istep == 0`` (the default, and
+        what the benchmark uses) averages the whole model, both matrices in one
+        buffer, with one all-reduce (NCCL over NVLink when the group's backend is
+        nccl) instead of the reference's host-driven peer copies; ``istep > 0``
+        follows the reference's schedule and averages only the frequency-ranked
+        head of each matrix (``mergeHeadLen`` rows).  Blocks the compute stream
+        until the average is in."""
         import torch.distributed as dist
         if not dist.is_initialized() or dist.get_world_size(group) == 1:
             return
         self.finishMerge()
-        bufs = [self._flat] if getattr(self, "_flat", None) is not None else self.modelmats
+        flat = getattr(self, "_flat", None)
+        bufs = [flat] if flat is not None else self.modelmats
+        if istep > 0:
+            rows = self.mergeHeadLen(self.opts.headlen, istep, self.opts.vocabSize)
+            if rows < self.opts.vocabSize:
+                mats = flat if flat is not None else self.modelmats
+                bufs = [mats[j][:rows] for j in range(2)]   # the head of a matrix is contiguous
         avg = dist.ReduceOp.AVG if dist.get_backend(group) == "nccl" else None
         for m in bufs:
             if avg is not None:

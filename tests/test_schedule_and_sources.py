@@ -210,3 +210,72 @@ def test_parlearner_overlapped_exchange_order():
     # minibatches: train, eval, train, train, train, train, eval(last)
     assert m.log == ["train", "finish", "eval", "train", "start", "train", "finish", "train", "start",
                      "train", "finish", "eval", "finish"]
+
+
+def test_merge_head_length_follows_the_reference_formula():
+    """Word2Vec.scala:548: headlen = max(opts.headlen, opts.headlen << trailingZeros(istep)),
+    everything when istep == 0, never more than the vocabulary; Int arithmetic."""
+    from bidmach_b200.word2vec import Word2Vec
+    f = Word2Vec.mergeHeadLen
+    V = 1_000_000
+    assert f(10000, 0, V) == V
+    assert [f(10000, k, V) for k in (1, 2, 3, 4, 6, 8, 12, 64)] == [10000, 20000, 10000, 40000, 20000, 80000,
+                                                                   40000, 640000]
+    assert f(10000, 128, V) == V and f(10000, 1 << 10, V) == V
+    assert f(10000, 8, 50_000) == 50_000
+    # 10000 << 18 overflows Int to a negative number, so max() falls back to headlen;
+    # a shift count of 32 wraps to 0
+    assert f(10000, 1 << 18, 1 << 40) == 10000
+    assert f(10000, 1 << 32, 1 << 40) == 10000
+    assert f(10000, 1 << 17, 1 << 40) == 10000 << 17
+
+
+def _head_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from bidmach_b200.word2vec import Opts, Word2Vec
+    m = Word2Vec.__new__(Word2Vec)
+    m.opts = Opts(vocabSize=12, dim=4, headlen=2)
+    m.modelmats = [torch.full((12, 4), float(rank + 1)), torch.full((12, 4), 10.0 * (rank + 1))]
+    m.mergeModelFn(None, istep=2)        # head = 2 << 1 = 4 rows
+    q.put((rank, m.modelmats[0].clone(), m.modelmats[1].clone()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_merge_model_with_istep_averages_only_the_head_rows():
+    world, port = 2, 30011 + os.getpid() % 500
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_head_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted((q.get(timeout=120) for _ in range(world)), key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, m0, m1 in got:
+        assert torch.allclose(m0[:4], torch.full((4, 4), 1.5)) and torch.allclose(m1[:4], torch.full((4, 4), 15.0))
+        assert torch.equal(m0[4:], torch.full((8, 4), float(rank + 1)))       # the tail stays local
+        assert torch.equal(m1[4:], torch.full((8, 4), 10.0 * (rank + 1)))
+
+
+def test_parlearner_head_sync_counts_every_round_like_the_reference():
+    """headSync: ParLearner's istep grows by the number of replicas per round
+    (scoring rounds included) and sync k is handed istep / syncStep
+    (Learner.scala:654-655)."""
+    from bidmach_b200.learner import LearnerOpts, MatSource, ParLearner
+
+    class M(_FakeModel):
+        def __init__(self):
+            super().__init__()
+            self.isteps = []
+
+        def mergeModelFn(self, group=None, istep=0):
+            self.isteps.append(istep)
+
+    m = M()
+    toks = np.zeros((900, 2), np.int32)
+    ParLearner(MatSource(toks, 100), m, LearnerOpts(npasses=1, syncStep=2, headSync=True)).train()
+    # one replica: istep = 1..9, syncs when istep % 2 == 0 with istep / 2
+    assert m.isteps == [1, 2, 3, 4]

@@ -244,7 +244,8 @@ def run_ours(args):
     sampler.start()
 
     o = Opts(dim=w["dim"], vocabSize=w["vocab"], nskip=w["nskip"], nneg=w["nneg"], nreuse=w["nreuse"],
-             lrate=w["lrate"], texp=w["texp"], vexp=w["vexp"], wsample=w["wsample"], seed=17 + rank)
+             lrate=w["lrate"], texp=w["texp"], vexp=w["vexp"], wsample=w["wsample"], seed=17 + rank,
+             sortPermute=args.sort_permute)
     model = Word2Vec(o, device=torch.device("cuda", local)).init(N)
     # configs[1]: both matrices random
     g = torch.Generator(device="cuda")
@@ -417,6 +418,9 @@ def main():
     ap.add_argument("--vocab", type=int, default=None, help="override the workload's vocabulary (profiling)")
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per minibatch (profiling)")
     ap.add_argument("--nneg", type=int, default=None, help="override the number of negatives (configs[4] uses 10)")
+    ap.add_argument("--sort-permute", action="store_true",
+                    help="shuffle the pair list by sorting random keys (the reference's GPU branch) "
+                         "instead of the keyed bijection")
     args = ap.parse_args()
     if args.vocab:
         WORKLOAD["vocab"] = args.vocab

@@ -20,7 +20,7 @@ class W2VOpts(C.Structure):
     """``w2v_opts`` of include/bidmach_b200.h."""
     _fields_ = [("dim", _I), ("nskip", _I), ("nneg", _I), ("nreuse", _I), ("vocabSize", _I),
                 ("wexpt", _F), ("wsample", _F), ("lrate", _F), ("texp", _F), ("vexp", _F),
-                ("iflip", _I), ("eqPosNeg", _I), ("seed", C.c_uint64)]
+                ("iflip", _I), ("eqPosNeg", _I), ("permute", _I), ("seed", C.c_uint64)]
 
 
 class W2VUniforms(C.Structure):

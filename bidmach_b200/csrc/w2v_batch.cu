@@ -21,6 +21,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <algorithm>
+
 #include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_scan.cuh>
 
@@ -61,6 +63,36 @@ enum : uint32_t { kStreamSampleWindow = 1, kStreamPermute = 2, kStreamNegs = 3, 
 struct Rng {
   uint32_t k0, k1, batch;
 };
+
+// ---------------------------------------------------------------------------
+// Keyed permutation of [0, n) without a sort.  f(x) = four rounds of
+// x = (x * a + c) mod 2^b;  x ^= x >> ceil(b / 2)  is a bijection of [0, 2^b)
+// (an odd multiplier and a right xor-shift are both invertible), b being the
+// bit length of n - 1; following f from i until the value drops below n
+// ("cycle walking") restricts it to a bijection of [0, n).  2^b < 2n, so a walk
+// takes under two steps on average.  The eight constants come from one Philox
+// block pair per minibatch.
+// ---------------------------------------------------------------------------
+struct PermKeys {
+  uint32_t a[4], c[4];
+};
+
+__host__ __device__ inline uint32_t permute_index(uint32_t i, uint32_t n, const PermKeys &k) {
+  if (n < 2) return 0;
+  int b = 0;
+  while (b < 32 && ((n - 1) >> b) != 0) b++;
+  const uint32_t mask = (b >= 32) ? 0xFFFFFFFFu : ((1u << b) - 1u);
+  const int sh = (b + 1) >> 1;
+  uint32_t x = i;
+  do {
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+      x = (x * k.a[r] + k.c[r]) & mask;
+      x ^= x >> sh;
+    }
+  } while (x >= n);
+  return x;
+}
 
 // ---------------------------------------------------------------------------
 // Preprocessing kernels
@@ -148,26 +180,42 @@ __global__ void fill_pairs_kernel(int ncols, int nskip, const int *__restrict__ 
     const int w = words[i + j];
     if (w < 0) continue;
     const int row = (j < 0) ? j + nskip : j + nskip - 1;
-    float u;
-    if (upermute) {
-      u = upermute[(int64_t)i * (2 * nskip) + row];
-    } else {
-      if ((row >> 2) != have) {
-        have = row >> 2;
-        r = philox4x32_10((uint32_t)i, (uint32_t)have, kStreamPermute, rng.batch, rng.k0, rng.k1);
-      }
-      u = u01(r.v[row & 3]);
-    }
-    const float key = __fadd_rn(__fadd_rn(u, 1.0f), -1.0f);
     ctx[at] = w;
-    keys[at] = (uint32_t)__fmul_rn(key, 8388608.0f);
+    if (keys) {
+      float u;
+      if (upermute) {
+        u = upermute[(int64_t)i * (2 * nskip) + row];
+      } else {
+        if ((row >> 2) != have) {
+          have = row >> 2;
+          r = philox4x32_10((uint32_t)i, (uint32_t)have, kStreamPermute, rng.batch, rng.k0, rng.k1);
+        }
+        u = u01(r.v[row & 3]);
+      }
+      const float key = __fadd_rn(__fadd_rn(u, 1.0f), -1.0f);
+      keys[at] = (uint32_t)__fmul_rn(key, 8388608.0f);
+    }
     at++;
   }
 }
 
-__global__ void negative_ids_kernel(int64_t n, const float *__restrict__ unegs, Rng rng, int vocab,
+// out[i] = ctx[perm(i)] for the first groups * nreuse places of the keyed
+// permutation of the counts[0] pairs (counts as totals_kernel leaves them).
+__global__ void shuffle_contexts_kernel(const int *__restrict__ counts, int nreuse, PermKeys keys,
+                                        const int *__restrict__ ctx, int *__restrict__ out) {
+  const uint32_t n = (uint32_t)counts[0];
+  const uint32_t m = (uint32_t)counts[1] * (uint32_t)nreuse;
+  const uint32_t stride = gridDim.x * blockDim.x;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < m; i += stride)
+    out[i] = ctx[permute_index(i, n, keys)];
+}
+
+// n draws, or counts[1] * nneg of them when the count is only known on the device
+__global__ void negative_ids_kernel(int64_t n, const int *__restrict__ counts, int nneg,
+                                    const float *__restrict__ unegs, Rng rng, int vocab,
                                     float expt, int *__restrict__ out) {
   const int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (counts) n = (int64_t)counts[1] * nneg;
   if (q >= n) return;
   float u;
   if (unegs) {
@@ -232,19 +280,27 @@ struct w2v_ctx {
   void *cub_tmp;
   size_t cub_tmp_bytes;
   // pinned host
-  int *counts_host;
+  int *counts_host;     // [kRing][2]: pairs, groups of the batch that used the slot
   float *retvals_host;
-  // results of the latest wordmats
+  // results of the latest wordmats: on the device in counts[0..1], on the host
+  // once settle_counts has waited for their copy
   int64_t npairs;
   int ngroups;
-  // phase timers (off by default): events at the phase boundaries of the batch
-  // in flight, harvested once the stream is known to have passed them
+  int counts_pending;
+  cudaEvent_t ev_counts;
+  // Batches rotate through kRing slots, so that the host can run ahead of the
+  // device by several minibatches.  Phase timers (off by default): events at
+  // the phase boundaries of a slot's batch, harvested before the slot is used
+  // again or when the timers are read.
+  uint64_t nbatch;
+  int slot;
   int timing_on;
-  cudaEvent_t ev[5];
-  int ev_pending;       // 0 none, 1 train batch, 2 eval batch
+  cudaEvent_t ev[4][5];
+  int ev_state[4];      // 0 none, 1 train batch, 2 eval batch
   cudaStream_t ev_stream;
   w2v_timing acc;
 };
+constexpr int kRing = 4;
 
 #define W2V_CHECK(call)                    \
   do {                                     \
@@ -261,53 +317,75 @@ static w2v::Rng make_rng(const w2v_opts &o, uint64_t batch_id) {
 }
 
 static void mark(w2v_ctx *c, int k, cudaStream_t stream) {
-  if (c->timing_on) cudaEventRecord(c->ev[k], stream);
+  if (c->timing_on) cudaEventRecord(c->ev[c->slot][k], stream);
 }
 
-// Adds the phase durations of the batch whose events are pending.  Only called
-// when the stream has already been synchronised past ev[4].
-static void harvest(w2v_ctx *c) {
-  if (!c->ev_pending) return;
+// Waits for the pair and group counts of the latest wordmats to reach the host.
+static int settle_counts(w2v_ctx *c) {
+  if (!c->counts_pending) return 0;
+  cudaError_t e = cudaEventSynchronize(c->ev_counts);
+  if (e != cudaSuccess) return (int)e;
+  c->npairs = c->counts_host[2 * c->slot];
+  c->ngroups = c->counts_host[2 * c->slot + 1];
+  c->counts_pending = 0;
+  return 0;
+}
+
+// Adds the phase durations and counts of the batch that used `slot`; waits for
+// that batch to finish if it has not yet.
+static void harvest(w2v_ctx *c, int slot) {
+  const int kind = c->ev_state[slot];
+  if (!kind) return;
+  c->ev_state[slot] = 0;
+  if (cudaEventSynchronize(c->ev[slot][4]) != cudaSuccess) {
+    cudaGetLastError();
+    return;
+  }
   float ms[4] = {0, 0, 0, 0};
   bool ok = true;
-  for (int k = 0; k < 4; k++) ok = ok && cudaEventElapsedTime(&ms[k], c->ev[k], c->ev[k + 1]) == cudaSuccess;
-  if (ok) {
-    c->acc.prep_ms += ms[0];
-    c->acc.permute_ms += ms[1];
-    if (c->ev_pending == 1) {
-      c->acc.pos_ms += ms[2];
-      c->acc.neg_ms += ms[3];
-      c->acc.train_batches += 1;
-    } else {
-      c->acc.evalpos_ms += ms[2];
-      c->acc.evalneg_ms += ms[3];
-      c->acc.eval_batches += 1;
-    }
-  } else {
+  for (int k = 0; k < 4; k++)
+    ok = ok && cudaEventElapsedTime(&ms[k], c->ev[slot][k], c->ev[slot][k + 1]) == cudaSuccess;
+  if (!ok) {
     cudaGetLastError();
+    return;
   }
-  c->ev_pending = 0;
+  const int64_t pairs = c->counts_host[2 * slot], groups = c->counts_host[2 * slot + 1];
+  c->acc.prep_ms += ms[0];
+  c->acc.permute_ms += ms[1];
+  if (kind == 1) {
+    c->acc.pos_ms += ms[2];
+    c->acc.neg_ms += ms[3];
+    c->acc.train_batches += 1;
+    c->acc.pairs += pairs;
+    c->acc.groups += groups;
+  } else {
+    c->acc.evalpos_ms += ms[2];
+    c->acc.evalneg_ms += ms[3];
+    c->acc.eval_batches += 1;
+    c->acc.eval_pairs += pairs;
+    c->acc.eval_groups += groups;
+  }
 }
 
 extern "C" {
 
 int w2v_set_timing(w2v_ctx *c, int on) {
   if (!c) return 1;
-  if (on && !c->ev[0]) {
-    for (int k = 0; k < 5; k++) W2V_CHECK(cudaEventCreate(&c->ev[k]));
+  if (on && !c->ev[0][0]) {
+    for (int r = 0; r < kRing; r++)
+      for (int k = 0; k < 5; k++) W2V_CHECK(cudaEventCreate(&c->ev[r][k]));
   }
+  if (c->timing_on)
+    for (int r = 0; r < kRing; r++) harvest(c, r);  // nothing of the old run leaks into the new one
   c->timing_on = on ? 1 : 0;
-  c->ev_pending = 0;
+  for (int r = 0; r < kRing; r++) c->ev_state[r] = 0;
   memset(&c->acc, 0, sizeof(c->acc));
   return 0;
 }
 
 int w2v_get_timing(w2v_ctx *c, w2v_timing *out) {
   if (!c || !out) return 1;
-  if (c->ev_pending) {
-    W2V_CHECK(cudaStreamSynchronize(c->ev_stream));
-    harvest(c);
-  }
+  for (int r = 0; r < kRing; r++) harvest(c, r);
   *out = c->acc;
   return 0;
 }
@@ -326,6 +404,7 @@ void w2v_default_opts(w2v_opts *o) {
   o->vexp = 0.5f;
   o->iflip = 0;
   o->eqPosNeg = 0;
+  o->permute = 0;
   o->seed = 0;
 }
 
@@ -339,7 +418,9 @@ void w2v_destroy(w2v_ctx *c) {
   cudaFree(c->wa); cudaFree(c->key_in); cudaFree(c->key_out); cudaFree(c->retvals);
   cudaFree(c->cub_tmp); cudaFree(c->hot_buf);
   cudaFreeHost(c->counts_host); cudaFreeHost(c->retvals_host);
-  for (int k = 0; k < 5; k++) if (c->ev[k]) cudaEventDestroy(c->ev[k]);
+  for (int r = 0; r < kRing; r++)
+    for (int k = 0; k < 5; k++) if (c->ev[r][k]) cudaEventDestroy(c->ev[r][k]);
+  if (c->ev_counts) cudaEventDestroy(c->ev_counts);
   cudaSetDevice(prev);
   delete c;
 }
@@ -385,6 +466,7 @@ int w2v_create(const w2v_opts *opts, int ncols, w2v_ctx **out) {
   }
   c->hot = w2v::hot_rows_at(c->hot_buf, w2v::hot_levels_default());
   if (e == cudaSuccess) e = cudaMallocHost(&c->counts_host, 256);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_counts, cudaEventDisableTiming);
   if (e == cudaSuccess) e = cudaMallocHost(&c->retvals_host, 256);
   if (e == cudaSuccess)
     e = cub::DeviceScan::ExclusiveSum(nullptr, scan_bytes, c->cnt, c->off, ncols);
@@ -426,6 +508,18 @@ int w2v_init_model(const w2v_opts *o, float *A, float *B, void *stream_) {
   return (int)cudaGetLastError();
 }
 
+static w2v::PermKeys make_perm_keys(const w2v_opts &o, uint64_t batch_id) {
+  const w2v::Rng rng = make_rng(o, batch_id);
+  const w2v::PhiloxOut x = w2v::philox4x32_10(0u, 0u, w2v::kStreamPermute, rng.batch, rng.k0, rng.k1);
+  const w2v::PhiloxOut y = w2v::philox4x32_10(1u, 0u, w2v::kStreamPermute, rng.batch, rng.k0, rng.k1);
+  w2v::PermKeys k;
+  for (int r = 0; r < 4; r++) {
+    k.a[r] = x.v[r] | 1u;
+    k.c[r] = y.v[r];
+  }
+  return k;
+}
+
 int w2v_wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64_t batch_id,
                  void *stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
@@ -435,13 +529,15 @@ int w2v_wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64_t 
   const w2v::Rng rng = make_rng(o, batch_id);
   const float *us = u ? u->sample : nullptr, *uw = u ? u->window : nullptr;
   const float *up = u ? u->permute : nullptr, *un = u ? u->negs : nullptr;
+  // permutation keys given by the caller can only be honoured by the sort
+  const bool by_sort = (o.permute != 0) || (up != nullptr);
 
-  // the events of the previous batch are about to be re-recorded: read them
-  // first (waits for that batch to finish; only in timing mode)
-  if (c->timing_on && c->ev_pending) {
-    if (cudaEventSynchronize(c->ev[4]) == cudaSuccess) harvest(c);
-    c->ev_pending = 0;
-  }
+  c->slot = (int)(c->nbatch++ % kRing);
+  c->ev_stream = stream;
+  // the slot's events and counts are about to be overwritten: read them first
+  // (waits for the batch that used the slot, kRing batches ago)
+  if (c->timing_on) harvest(c, c->slot);
+  c->ev_state[c->slot] = 0;
   mark(c, 0, stream);
   w2v::words_bounds_kernel<<<blocks, threads, 0, stream>>>(
       n, tokens, o.iflip ? 1 : 0, o.vocabSize, o.nskip, c->salpha, us, uw, rng, c->words, c->lb, c->ub);
@@ -449,31 +545,48 @@ int w2v_wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64_t 
   size_t tmp = c->cub_tmp_bytes;
   W2V_CHECK(cub::DeviceScan::ExclusiveSum(c->cub_tmp, tmp, c->cnt, c->off, n, stream));
   w2v::totals_kernel<<<1, 32, 0, stream>>>(n, c->cnt, c->off, o.nreuse, c->counts);
-  W2V_CHECK(cudaMemcpyAsync(c->counts_host, c->counts, 2 * sizeof(int), cudaMemcpyDeviceToHost, stream));
+  W2V_CHECK(cudaMemcpyAsync(c->counts_host + 2 * c->slot, c->counts, 2 * sizeof(int),
+                            cudaMemcpyDeviceToHost, stream));
+  W2V_CHECK(cudaEventRecord(c->ev_counts, stream));
+  c->counts_pending = 1;
   w2v::fill_pairs_kernel<<<blocks, threads, 0, stream>>>(n, o.nskip, c->words, c->lb, c->ub, c->off,
-                                                        up, rng, c->ctx_in, c->key_in);
+                                                        up, rng, c->ctx_in,
+                                                        by_sort ? c->key_in : nullptr);
   w2v::count_launch(4);
   W2V_CHECK(cudaGetLastError());
   mark(c, 1, stream);
-  W2V_CHECK(cudaStreamSynchronize(stream));
-  {
-    // everything enqueued by earlier calls has finished: did a staged kernel give up?
-    const int fault = w2v::take_stage_fault();
-    if (fault) return fault;
-  }
-  c->npairs = c->counts_host[0];
-  c->ngroups = c->counts_host[1];
-  if (c->npairs > 0) {
-    tmp = c->cub_tmp_bytes;
-    W2V_CHECK(cub::DeviceRadixSort::SortPairsDescending(c->cub_tmp, tmp, c->key_in, c->key_out,
-                                                        c->ctx_in, c->ctx_out, (int)c->npairs, 0,
-                                                        24, stream));
-  }
-  const int64_t nn = (int64_t)c->ngroups * o.nneg;
-  if (nn > 0) {
-    w2v::negative_ids_kernel<<<(unsigned)((nn + threads - 1) / threads), threads, 0, stream>>>(
-        nn, un, rng, o.vocabSize, c->expt, c->wa);
-    w2v::count_launch(1);
+  if (by_sort) {
+    // the sort needs the pair count on the host
+    int err = settle_counts(c);
+    if (err) return err;
+    if (c->npairs > 0) {
+      tmp = c->cub_tmp_bytes;
+      W2V_CHECK(cub::DeviceRadixSort::SortPairsDescending(c->cub_tmp, tmp, c->key_in, c->key_out,
+                                                          c->ctx_in, c->ctx_out, (int)c->npairs, 0,
+                                                          24, stream));
+    }
+    const int64_t nn = (int64_t)c->ngroups * o.nneg;
+    if (nn > 0) {
+      w2v::negative_ids_kernel<<<(unsigned)((nn + threads - 1) / threads), threads, 0, stream>>>(
+          nn, nullptr, o.nneg, un, rng, o.vocabSize, c->expt, c->wa);
+      w2v::count_launch(1);
+    }
+  } else {
+    // everything downstream reads the counts on the device: nothing waits for the host
+    const int64_t max_groups = c->max_pairs / o.nreuse;
+    const int64_t max_negs = max_groups * o.nneg;
+    if (c->max_pairs > 0) {
+      const int shuffle_blocks = (int)std::min<int64_t>((c->max_pairs + threads - 1) / threads,
+                                                       (int64_t)w2v::device_sm_count() * 16);
+      w2v::shuffle_contexts_kernel<<<shuffle_blocks, threads, 0, stream>>>(
+          c->counts, o.nreuse, make_perm_keys(o, batch_id), c->ctx_in, c->ctx_out);
+      w2v::count_launch(1);
+    }
+    if (max_negs > 0) {
+      w2v::negative_ids_kernel<<<(unsigned)((max_negs + threads - 1) / threads), threads, 0, stream>>>(
+          max_negs, c->counts, o.nneg, un, rng, o.vocabSize, c->expt, c->wa);
+      w2v::count_launch(1);
+    }
   }
   mark(c, 2, stream);
   return (int)cudaGetLastError();
@@ -481,6 +594,8 @@ int w2v_wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64_t 
 
 int w2v_buffers(w2v_ctx *c, w2v_buffers_t *out) {
   if (!c || !out) return 1;
+  int err = settle_counts(c);
+  if (err) return err;
   out->words = c->words; out->lb = c->lb; out->ub = c->ub;
   out->contexts = c->ctx_in;
   out->WB = c->ctx_out;
@@ -488,6 +603,18 @@ int w2v_buffers(w2v_ctx *c, w2v_buffers_t *out) {
   out->npairs = c->npairs;
   out->ngroups = c->ngroups;
   return 0;
+}
+
+// Column count of the negative kernels: known on the host after a sort, else
+// an upper bound for the grid plus the device-side count.
+static void group_count(const w2v_ctx *c, int *ncols, const int **ncols_dev) {
+  if (c->counts_pending) {
+    *ncols = (int)(c->max_pairs / c->o.nreuse);
+    *ncols_dev = c->counts + 1;
+  } else {
+    *ncols = c->ngroups;
+    *ncols_dev = nullptr;
+  }
 }
 
 int w2v_dobatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, float *A, float *B,
@@ -505,15 +632,13 @@ int w2v_dobatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, float *A, 
                               lrpos, o.vexp, c->hot, stream);
   if (err) return err;
   mark(c, 3, stream);
-  err = w2v::neg_update_async(o.dim, c->ngroups, nullptr, 0x7fffffff, o.nneg, o.nreuse, c->wa,
+  int groups = 0;
+  const int *groups_dev = nullptr;
+  group_count(c, &groups, &groups_dev);
+  err = w2v::neg_update_async(o.dim, groups, groups_dev, 0x7fffffff, o.nneg, o.nreuse, c->wa,
                               c->ctx_out, A, B, lrneg, o.vexp, c->hot, stream);
   mark(c, 4, stream);
-  if (c->timing_on) {
-    c->ev_pending = 1;
-    c->ev_stream = stream;
-    c->acc.pairs += c->npairs;
-    c->acc.groups += c->ngroups;
-  }
+  if (c->timing_on) c->ev_state[c->slot] = 1;
   return err;
 }
 
@@ -528,18 +653,20 @@ int w2v_evalbatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, const fl
                             c->retvals, stream);
   if (err) return err;
   mark(c, 3, stream);
-  err = w2v::neg_eval_async(o.dim, c->ngroups, nullptr, o.nneg, o.nreuse, c->wa, c->ctx_out, A, B,
+  int groups = 0;
+  const int *groups_dev = nullptr;
+  group_count(c, &groups, &groups_dev);
+  err = w2v::neg_eval_async(o.dim, groups, groups_dev, o.nneg, o.nreuse, c->wa, c->ctx_out, A, B,
                             c->retvals + 1, stream);
   if (err) return err;
   mark(c, 4, stream);
-  if (c->timing_on) {
-    c->ev_pending = 2;
-    c->ev_stream = stream;
-    c->acc.eval_pairs += c->npairs;
-    c->acc.eval_groups += c->ngroups;
-  }
+  if (c->timing_on) c->ev_state[c->slot] = 2;
   W2V_CHECK(cudaMemcpyAsync(c->retvals_host, c->retvals, 2 * sizeof(float), cudaMemcpyDeviceToHost, stream));
   W2V_CHECK(cudaStreamSynchronize(stream));
+  err = settle_counts(c);
+  if (err) return err;
+  err = w2v::take_stage_fault();
+  if (err) return err;
   const double epos = c->retvals_host[0], eneg = c->retvals_host[1];
   const double denom = (double)c->ngroups * o.nreuse;
   // (epos + eneg / nneg) / goodwords.length  (Word2Vec.scala:209)
@@ -555,6 +682,8 @@ int w2v_dobatch_host(w2v_ctx *c, const int *tokens_host, float *A, float *B, int
   int err = w2v_dobatch(c, c->tokens, nullptr, A, B, pos, batch_id, stream);
   if (err) return err;
   W2V_CHECK(cudaStreamSynchronize(stream));
+  err = settle_counts(c);
+  if (err) return err;
   if (npairs_host) *npairs_host = c->npairs;
   W2V_CHECK(cudaGetLastError());
   return w2v::take_stage_fault();

@@ -48,11 +48,12 @@ class Opts:
     vexp: float = 0.5
     useGPU: bool = True
     seed: int = 0
+    sortPermute: bool = False   # True: shuffle the pair list by sorting random keys (the reference's GPU branch)
 
     def to_c(self) -> _lib.W2VOpts:
         return _lib.W2VOpts(self.dim, self.nskip, self.nneg, self.nreuse, self.vocabSize,
                             self.wexpt, self.wsample, self.lrate, self.texp, self.vexp,
-                            int(self.iflip), int(self.eqPosNeg), self.seed)
+                            int(self.iflip), int(self.eqPosNeg), int(self.sortPermute), self.seed)
 
 
 class _DevView:

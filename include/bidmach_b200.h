@@ -136,6 +136,10 @@ typedef struct w2v_opts {
   float vexp;       /* 0.5   */
   int iflip;        /* 0: row 0 of the minibatch is the word id, row 1 the sentence id */
   int eqPosNeg;     /* 0: negatives use lrate / nneg */
+  int permute;      /* how the pair list is shuffled (Word2Vec.scala:254-259 sorts it by random keys):
+                       0: keyed bijection of the pair indices, no sort and no host synchronisation;
+                       1: sort by random keys as the reference's GPU branch.  Keys given in
+                       w2v_uniforms.permute always select the sort. */
   uint64_t seed;    /* seed of the built-in counter-based generator */
 } w2v_opts;
 
@@ -170,8 +174,9 @@ int w2v_init_model(const w2v_opts *opts, float *A, float *B, void *stream);
 /* Word2Vec.wordMats (Word2Vec.scala:214-278): subsampling, window bounds,
  * ordered context list, random permutation, negative ids.  `tokens` is the
  * 2 x ncols int32 minibatch, column-major.  Results stay in the context and
- * are read with w2v_buffers.  Synchronises `stream` once (the pair count
- * crosses to the host). */
+ * are read with w2v_buffers.  With the sorted permutation the call
+ * synchronises `stream` once (the sort needs the pair count on the host); with
+ * the keyed bijection it only enqueues work. */
 int w2v_wordmats(w2v_ctx *ctx, const int *tokens, const w2v_uniforms *u, uint64_t batch_id,
                  void *stream);
 
@@ -183,6 +188,7 @@ typedef struct w2v_buffers_t {
   int64_t npairs;
   int ngroups;
 } w2v_buffers_t;
+/* Waits until the counts of the latest wordmats have reached the host. */
 int w2v_buffers(w2v_ctx *ctx, w2v_buffers_t *out);
 
 /* Word2Vec.dobatch (Word2Vec.scala:167-190): learning rate

@@ -263,17 +263,24 @@ def permute_by_keys(ctx, u_keys):
     return np.asarray(ctx)[order]
 
 
-def wordmats_gpu_branch(tokens, opts, u_sample, u_window, u_permute, u_negs):
+def wordmats_gpu_branch(tokens, opts, u_sample, u_window, u_permute, u_negs, perm=None):
     """Whole wordMats with the GPU branch's permutation.  u_permute is the
-    [ncols, 2*nskip] table of draws.  Returns words, lb, ub, contexts (ordered),
-    WB [ngroups, nreuse], WA [ngroups, nneg]."""
+    [ncols, 2*nskip] table of draws; when it is None, ``perm`` (an index array,
+    see library_permutation) shuffles the ordered list instead.  Returns words,
+    lb, ub, contexts (ordered), WB [ngroups, nreuse], WA [ngroups, nneg].
+    ``perm`` may also be a function of the pair count."""
     V, nskip = opts["vocabSize"], opts["nskip"]
     words, lb, ub = wordmats_bounds(tokens, V, nskip, salpha_of(opts["wsample"], V), u_sample,
                                     u_window, opts.get("iflip", False))
     ctx = ordered_contexts(words, lb, ub)
-    rows, centres = context_rows(words, lb, ub, nskip)
-    keys = np.asarray(u_permute, np.float32).reshape(len(words), 2 * nskip)[centres, rows]
-    perm = permute_by_keys(ctx, keys)
+    if u_permute is None:
+        if callable(perm):
+            perm = perm(len(ctx))
+        perm = np.asarray(ctx)[np.asarray(perm, np.int64)]
+    else:
+        rows, centres = context_rows(words, lb, ub, nskip)
+        keys = np.asarray(u_permute, np.float32).reshape(len(words), 2 * nskip)[centres, rows]
+        perm = permute_by_keys(ctx, keys)
     ngroups = len(ctx) // opts["nreuse"]
     WB = perm[: ngroups * opts["nreuse"]].reshape(ngroups, opts["nreuse"])
     WA = negative_ids(np.asarray(u_negs, np.float32).ravel()[: ngroups * opts["nneg"]],
@@ -332,6 +339,43 @@ def library_uniforms(seed, batch_id, ncols, nskip, n_negs):
                       (blk >> np.uint64(32)).astype(np.uint32), STREAM_NEGS, b, k0, k1)
     negs = np.stack([u01(x) for x in r], axis=1).ravel()[:n_negs]
     return sample, window, perm, negs
+
+
+def keyed_permutation(n, a, c):
+    """Keyed bijection of [0, n) the CUDA library shuffles pair indices with
+    when it sorts nothing: four rounds of x = (x*a[r] + c[r]) mod 2^b,
+    x ^= x >> ceil(b/2) (b = bit length of n-1, a[r] odd), applied again while
+    the value is >= n (cycle walking).  Returns perm with perm[i] = image of i."""
+    n = int(n)
+    if n < 2:
+        return np.zeros(n, np.int64)
+    b = int(n - 1).bit_length()
+    mask, sh = np.uint64((1 << b) - 1), np.uint64((b + 1) >> 1)
+    x = np.arange(n, dtype=np.uint64)
+    out = np.empty(n, np.int64)
+    todo = np.arange(n)
+    while todo.size:
+        v = x[todo]
+        for r in range(4):
+            v = (v * np.uint64(a[r]) + np.uint64(c[r])) & mask
+            v ^= v >> sh
+        x[todo] = v
+        done = v < np.uint64(n)
+        out[todo[done]] = v[done].astype(np.int64)
+        todo = todo[~done]
+    return out
+
+
+def library_permutation(seed, batch_id, n):
+    """keyed_permutation with the constants the CUDA library derives for one
+    minibatch: two Philox blocks of the permutation stream, multipliers made odd."""
+    k0, k1 = seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF
+    b = np.uint32(batch_id & 0xFFFFFFFF)
+    x = philox4x32_10(np.uint32(0), 0, STREAM_PERMUTE, b, k0, k1)
+    y = philox4x32_10(np.uint32(1), 0, STREAM_PERMUTE, b, k0, k1)
+    a = [int(np.asarray(v).ravel()[0]) | 1 for v in x]
+    c = [int(np.asarray(v).ravel()[0]) for v in y]
+    return keyed_permutation(n, a, c)
 
 
 def library_init_model(seed, dim, vocab):

@@ -55,22 +55,31 @@ def test_wordmats_bit_exact_with_supplied_uniforms(oracle, n, nskip, nneg, nreus
     assert (o_words >= 0).any() and (o_words < 0).any() and len(o_ctx) > 0
 
 
-def test_wordmats_builtin_generator_matches_its_cpu_restatement(oracle):
+@pytest.mark.parametrize("sort_permute", [False, True])
+def test_wordmats_builtin_generator_matches_its_cpu_restatement(oracle, sort_permute):
+    """No draws supplied: the library generates them (Philox), and shuffles the
+    pair list either with its keyed bijection (default, nothing is sorted and
+    nothing waits for the host) or by sorting random keys as the reference."""
     from bidmach_b200 import Word2Vec
     n = 3000
-    o = _opts(seed=0x1234_5678_9ABC_DEF0)
+    o = _opts(seed=0x1234_5678_9ABC_DEF0, sortPermute=sort_permute)
     toks = _tokens(n, o.vocabSize, 9)
     model = Word2Vec(o).init(n)
     batch_id = 7
     words, lb, ub, wa, wb = model.wordMats([dev(toks)], batch_id=batch_id)
     torch.cuda.synchronize()
     us, uw, up, un = oracle.library_uniforms(o.seed, batch_id, n, o.nskip, 2 * o.nskip * n)
+    perm = None
+    if not sort_permute:
+        up, perm = None, (lambda npairs: oracle.library_permutation(o.seed, batch_id, npairs))
     o_words, o_lb, o_ub, o_ctx, o_wb, o_wa = oracle.wordmats_gpu_branch(
         toks, dict(vocabSize=o.vocabSize, nskip=o.nskip, nneg=o.nneg, nreuse=o.nreuse,
-                   wsample=o.wsample, wexpt=o.wexpt), us, uw, up, un)
+                   wsample=o.wsample, wexpt=o.wexpt), us, uw, up, un, perm)
     assert np.array_equal(words.cpu().numpy(), o_words)
     assert np.array_equal(lb.cpu().numpy(), o_lb) and np.array_equal(ub.cpu().numpy(), o_ub)
+    assert np.array_equal(model.last_contexts.cpu().numpy(), o_ctx)
     assert np.array_equal(wb.cpu().numpy(), o_wb) and np.array_equal(wa.cpu().numpy(), o_wa)
+    assert wb.numel() == (len(o_ctx) // o.nreuse) * o.nreuse
 
 
 def test_iflip_and_oov_and_single_sentence(oracle):

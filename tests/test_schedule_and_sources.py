@@ -279,3 +279,14 @@ def test_parlearner_head_sync_counts_every_round_like_the_reference():
     ParLearner(MatSource(toks, 100), m, LearnerOpts(npasses=1, syncStep=2, headSync=True)).train()
     # one replica: istep = 1..9, syncs when istep % 2 == 0 with istep / 2
     assert m.isteps == [1, 2, 3, 4]
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 17, 1000, 65536, 65537, 1_000_003])
+def test_keyed_permutation_is_a_bijection(oracle, n):
+    """CPU restatement only (the GPU side is compared with it above): every index once."""
+    p = oracle.library_permutation(99, 4, n)
+    assert p.shape == (n,) and np.array_equal(np.sort(p), np.arange(n))
+    if n >= 1000:
+        assert abs(np.corrcoef(np.arange(n), p)[0, 1]) < 0.05     # no trace of the input order
+        assert (p == np.arange(n)).mean() < 0.01
+        assert not np.array_equal(p, oracle.library_permutation(99, 5, n))   # another minibatch, another shuffle

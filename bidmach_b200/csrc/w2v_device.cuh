@@ -9,6 +9,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 namespace w2v {
 
 constexpr unsigned kFullMask = 0xffffffffu;
@@ -179,6 +181,29 @@ __host__ __device__ constexpr unsigned spread_valid_mask(int q) {
   for (int idx = 0; idx < M; idx++)
     if (Spread<M>::slot_of(idx) == q) m |= 1u << Spread<M>::lane_of(idx);
   return m;
+}
+
+// Calls f(integral_constant<q>) on every lane that holds a real total in slot
+// q after Spread<M>::reduce.  The masks are constant expressions: left to the
+// optimiser, the loops of lane_of / slot_of were seen to survive into the kernel.
+template <int M, int Q = 0, class F>
+__device__ __forceinline__ void for_valid_totals(int lane, F &&f) {
+  if constexpr (Q < Spread<M>::FIN) {
+    constexpr unsigned valid = spread_valid_mask<M>(Q);
+    if ((valid >> lane) & 1u) f(std::integral_constant<int, Q>());
+    for_valid_totals<M, Q + 1>(lane, f);
+  }
+}
+
+// g[idx] = total idx of a Spread<M>::reduce, on every lane; source lane and
+// slot are constant expressions.
+template <int M, int I = 0>
+__device__ __forceinline__ void broadcast_totals(const float (&p)[M], float (&g)[M]) {
+  if constexpr (I < M) {
+    constexpr int src_lane = Spread<M>::lane_of(I), slot = Spread<M>::slot_of(I);
+    g[I] = __shfl_sync(kFullMask, p[slot], src_lane);
+    broadcast_totals<M, I + 1>(p, g);
+  }
 }
 
 // Lane l < NWA carries A-word l of the column, lanes NWA..NWA+NWB-1 the

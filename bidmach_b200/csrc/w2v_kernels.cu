@@ -442,7 +442,7 @@ __global__ void __launch_bounds__(kPosThreads)
       for (int c = 0; c < CH; c++) p[c] = prow_dot_partial(own, rows[c]);
       Spread<CH>::reduce(p, lane);
       // the lane that holds a pair's dot product scores it (networks/Word2Vec.scala:995)
-      if ((spread_valid_mask<CH>(0) >> lane) & 1u) acc += pair_score(sigmoid_guard(p[0]));
+      for_valid_totals<CH>(lane, [&](auto q) { acc += pair_score(sigmoid_guard(p[decltype(q)::value])); });
     };
     int cnt = __popc(todo);
     while (cnt > 0) {
@@ -591,9 +591,7 @@ __global__ void __launch_bounds__(kNegThreads)
 
     // every lane needs every pair's coefficient: fetch each from its owner
     float g[NWA * NWB];
-#pragma unroll
-    for (int idx = NWA * NWB - 1; idx >= 0; idx--)
-      g[idx] = __shfl_sync(kFullMask, p[S::slot_of(idx)], S::lane_of(idx));
+    broadcast_totals<NWA * NWB>(p, g);
 
 #pragma unroll
     for (int j = 0; j < NWA; j++) {
@@ -772,17 +770,13 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
       }
       S::reduce(p, lane);
       if constexpr (EVAL) {
-#pragma unroll
-        for (int q = 0; q < S::FIN; q++)
-          if ((spread_valid_mask<NWA * NWB>(q) >> lane) & 1u)
-            acc += pair_score(1.0f - sigmoid_guard(p[q]));
+        for_valid_totals<NWA * NWB>(
+            lane, [&](auto q) { acc += pair_score(1.0f - sigmoid_guard(p[decltype(q)::value])); });
       } else {
 #pragma unroll
         for (int q = 0; q < S::FIN; q++) p[q] = -lrate * sigmoid_guard(p[q]);
         float g[NWA * NWB];
-#pragma unroll
-        for (int idx = NWA * NWB - 1; idx >= 0; idx--)
-          g[idx] = __shfl_sync(kFullMask, p[S::slot_of(idx)], S::lane_of(idx));
+        broadcast_totals<NWA * NWB>(p, g);
         // rows of the streamed side: their deltas need the held rows only
 #pragma unroll
         for (int y = 0; y < NY; y++) {
@@ -891,11 +885,8 @@ __global__ void __launch_bounds__(kNegThreads, (NegEvalShape<NWA, NWB, NR>::bloc
         p[HOLD_B ? (y * NWB + x) : (x * NWB + y)] = prow_dot_partial(X[x], Y);
     }
     S::reduce(p, lane);
-#pragma unroll
-    for (int q = 0; q < S::FIN; q++) {
-      const unsigned valid = spread_valid_mask<NWA * NWB>(q);
-      if ((valid >> lane) & 1u) acc += pair_score(1.0f - sigmoid_guard(p[q]));
-    }
+    for_valid_totals<NWA * NWB>(
+        lane, [&](auto q) { acc += pair_score(1.0f - sigmoid_guard(p[decltype(q)::value])); });
   }
   finish_eval_sum(acc, scratch, retval);
 }
@@ -939,19 +930,13 @@ __global__ void __launch_bounds__(kGenericThreads)
     S::reduce(p, lane);
 
     if constexpr (EVAL) {
-#pragma unroll
-      for (int q = 0; q < S::FIN; q++) {
-        const unsigned valid = spread_valid_mask<NWA * NWB>(q);
-        if ((valid >> lane) & 1u)
-          acc += pair_score(1.0f - sigmoid_guard(p[q]));
-      }
+      for_valid_totals<NWA * NWB>(
+          lane, [&](auto q) { acc += pair_score(1.0f - sigmoid_guard(p[decltype(q)::value])); });
     } else {
 #pragma unroll
     for (int q = 0; q < S::FIN; q++) p[q] = -lrate * sigmoid_guard(p[q]);
     float g[NWA * NWB];
-#pragma unroll
-    for (int idx = NWA * NWB - 1; idx >= 0; idx--)
-      g[idx] = __shfl_sync(kFullMask, p[S::slot_of(idx)], S::lane_of(idx));
+    broadcast_totals<NWA * NWB>(p, g);
     float sa[NWA], sb[NWB];
 #pragma unroll
     for (int j = 0; j < NWA; j++) sa[j] = __shfl_sync(kFullMask, mysc, j);

@@ -91,11 +91,8 @@ __global__ void __launch_bounds__(kThreads)
         for (int k = 0; k < NWB; k++) p[j * NWB + k] = fmaf(av[j], bv[k], p[j * NWB + k]);
     }
     S::reduce(p, lane);
-#pragma unroll
-    for (int q = 0; q < S::FIN; q++) {
-      const unsigned valid = spread_valid_mask<NWA * NWB>(q);
-      if ((valid >> lane) & 1u) acc += pair_score(1.0f - sigmoid_guard(p[q]));
-    }
+    for_valid_totals<NWA * NWB>(
+        lane, [&](auto q) { acc += pair_score(1.0f - sigmoid_guard(p[decltype(q)::value])); });
   }
 
   acc = warp_sum(acc);

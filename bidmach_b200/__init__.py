@@ -5,7 +5,11 @@ negative-sampling minibatch path behind the reference's CUMACH interface.
 ``Word2Vec``   host-side mirror of BIDMach.networks.Word2Vec (options, dobatch,
                evalbatch) above the C-ABI library
 ``Learner`` / ``ParLearner``  the minibatch schedule that drives it
+``MatSource`` / ``FileSource``  minibatches from memory or from corpus files
+``matio`` / ``modelio``  BIDMat matrix files, checkpoints, Google word2vec files
 """
 from .cumach import CUMACH, cuda_error_string  # noqa: F401
 from .word2vec import Word2Vec  # noqa: F401
 from .learner import Learner, ParLearner, MatSource  # noqa: F401
+from .filesource import FileSource, FileSourceOpts  # noqa: F401
+from . import matio, modelio  # noqa: F401

@@ -50,6 +50,10 @@ SIGNATURES = {
     "word2vecEvalPos": (_I, [_I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "word2vecEvalNeg": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "word2vecEvalNegNoAlloc": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "bidmach_xxh32": (C.c_uint32, [_P, C.c_int64, C.c_uint32]),
+    "bidmach_lz4_compress_bound": (C.c_int64, [C.c_int64]),
+    "bidmach_lz4_compress": (C.c_int64, [_P, C.c_int64, _P, C.c_int64]),
+    "bidmach_lz4_decompress": (C.c_int64, [_P, C.c_int64, _P, C.c_int64]),
     "JNI_OnLoad": (_I, [_P, _P]),
     "Java_edu_berkeley_bid_CUMACH_word2vecPos": (_I, [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _F, _F]),
     "Java_edu_berkeley_bid_CUMACH_word2vecNeg": (_I, [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _F, _F]),

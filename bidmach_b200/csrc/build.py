@@ -21,7 +21,7 @@ LIB_NAME = "libbidmachcuda-linux-x86_64.so"
 LIB_PATH = os.path.join(PKG, LIB_NAME)
 OBJ_DIR = os.path.join(HERE, "build")
 
-SOURCES = ["w2v_kernels.cu", "w2v_batch.cu", "w2v_noalloc.cu", "jni_shim.cpp"]
+SOURCES = ["w2v_kernels.cu", "w2v_batch.cu", "w2v_noalloc.cu", "jni_shim.cpp", "matio_codec.cpp"]
 HEADERS = ["w2v_device.cuh", "w2v_internal.h", "jni_min.h",
            os.path.join("..", "..", "include", "bidmach_b200.h")]
 

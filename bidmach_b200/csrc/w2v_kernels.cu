@@ -714,9 +714,9 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
 
   for (int i = 0; i < mycols; i++) {
     const int st = i % NST;
-    if (!mbar_wait_bounded(&bars[st], (unsigned)(i / NST) & 1u, kWaitPolls)) {
+    if (!__all_sync(kFullMask, mbar_wait_bounded(&bars[st], (unsigned)(i / NST) & 1u, kWaitPolls))) {
       // the copies never completed within the limit (this warp has no other
-      // copy in flight): report and stop
+      // copy in flight): report and stop, the whole warp together
       if (lane == 0) atomicExch(&g_stage_fault, 1);
       break;
     }

@@ -96,3 +96,46 @@ def readGoogleW2V(fname, dict_index, n: int, binary: bool = False) -> np.ndarray
         if 0 <= icol < n:
             model[icol] = vec
     return model
+
+
+# ---------------------------------------------------------------------------
+# BIDMach checkpoint directory, Model.save / Model.load
+# (src/main/scala/BIDMach/models/Model.scala:245-315): ``<fname>options.json``
+# and one ``<fname>modelmat%02d.lz4`` per model matrix (BIDMat matrix file,
+# dim x vocab column-major, which is the [vocab, dim] row-major buffer of this
+# package).  ``fname`` normally ends in "/" (a directory, created if needed);
+# otherwise it is a prefix, as in the reference.  The reference also writes
+# ``options.ser`` (Java serialisation of the options object), which has no
+# meaning outside a JVM: it is not written, and ``load`` is the reference's
+# ``load(fname, useJson = true)``.
+# ---------------------------------------------------------------------------
+def saveModel(fname: str, opts: dict, mats) -> None:
+    import json
+    import os
+
+    from . import matio
+    parent = os.path.dirname(fname + "options.json")
+    if parent:
+        os.makedirs(parent, exist_ok=True)
+    with open(fname + "options.json", "w") as f:
+        json.dump(opts, f, indent=1, sort_keys=True)
+    for i, m in enumerate(mats):
+        if hasattr(m, "detach"):
+            m = m.detach().cpu().numpy()
+        matio.saveMat(fname + "modelmat%02d.lz4" % i, np.asarray(m).T)
+
+
+def loadModel(fname: str):
+    """Returns ``(opts dict, [matrix, ...])``; each matrix comes back as
+    ``[vocab, dim]`` (a view of the file's bytes, read-only)."""
+    import json
+    import os
+
+    from . import matio
+    with open(fname + "options.json") as f:
+        opts = json.load(f)
+    mats, n = [], 0
+    while os.path.exists(fname + "modelmat%02d.lz4" % n):
+        mats.append(matio.loadMat(fname + "modelmat%02d.lz4" % n).T)
+        n += 1
+    return opts, mats

@@ -365,6 +365,29 @@ class Word2Vec:
         opts.seed = opts.seed + 7919 * rank   # every replica draws its own samples
         return ParLearner(MatSource(tokens, batchSize, rank, world), Word2Vec(opts), lopts, group), opts
 
+    def save(self, fname: str):
+        """Model.save (models/Model.scala:245-263): ``options.json`` and
+        ``modelmat00.lz4`` / ``modelmat01.lz4`` under ``fname``."""
+        modelio.saveModel(fname, dataclasses.asdict(self.opts), self.modelmats)
+
+    def load(self, fname: str):
+        """Model.load(fname, useJson = true) (models/Model.scala:282-315): the
+        options of the checkpoint replace this model's, the matrices are copied
+        onto the device."""
+        o, mats = modelio.loadModel(fname)
+        known = {f.name for f in dataclasses.fields(Opts)}
+        for k, v in o.items():
+            if k in known:
+                setattr(self.opts, k, v)
+        if len(mats) != 2 or mats[0].shape != (self.opts.vocabSize, self.opts.dim):
+            raise ValueError("checkpoint holds %s, options say %d x %d" %
+                             ([m.shape for m in mats], self.opts.vocabSize, self.opts.dim))
+        if not getattr(self, "modelmats", None) or tuple(self.modelmats[0].shape) != mats[0].shape:
+            self.init(getattr(self, "ncols", 0) or 1)
+        for dst, src in zip(self.modelmats, mats):
+            dst.copy_(torch.from_numpy(np.array(src, dtype=np.float32, order="C")))
+        return self
+
     @staticmethod
     def predictor(model: "Word2Vec", tokens, batchSize: int | None = None):
         """Word2Vec.predictor (Word2Vec.scala:1282-1307): scores of a trained model on

@@ -239,6 +239,21 @@ int w2v_get_timing(w2v_ctx *ctx, w2v_timing *out); /* synchronises the last stre
 /* Number of kernels this library has launched in this process (all threads). */
 long long w2v_launch_count(void);
 
+/* -------------------------------------------------------------------------
+ * Part 4.  Byte codecs of BIDMat's compressed matrix files (host code).  The
+ * reference reads corpora ("*.imat.lz4", scripts/getw2vdata.ssc:44) and writes
+ * checkpoints ("modelmat%02d.lz4", models/Model.scala:259) through BIDMat's
+ * loadMat / saveMat over lz4-java's block stream; these are the LZ4 block codec
+ * and the XXH32 checksum that container needs.  The container itself and the
+ * matrix header are handled by the host-side reader (bidmach_b200/matio.py).
+ * ---------------------------------------------------------------------- */
+uint32_t bidmach_xxh32(const void *data, int64_t len, uint32_t seed);
+int64_t bidmach_lz4_compress_bound(int64_t n);
+/* Both return the number of bytes written to dst, or -1 (dst too small;
+ * malformed input).  Neither touches memory outside the given ranges. */
+int64_t bidmach_lz4_compress(const void *src, int64_t n, void *dst, int64_t cap);
+int64_t bidmach_lz4_decompress(const void *src, int64_t n, void *dst, int64_t cap);
+
 #ifdef __cplusplus
 }
 #endif

@@ -67,3 +67,26 @@ def test_accepts_torch_tensors(tmp_path):
     saveGoogleW2V(["a", "b", "c", "d"], mod, f, binary=True)
     back = readGoogleW2V(f, {"a": 0, "b": 1, "c": 2}, 3, binary=True)
     assert np.array_equal(back, mod.numpy())
+
+
+def test_checkpoint_directory_layout_and_round_trip(tmp_path):
+    """Model.save (models/Model.scala:245-263): options.json + modelmat%02d.lz4, each a
+    dim x vocab column-major float matrix."""
+    import json
+    import struct
+
+    from bidmach_b200 import matio, modelio
+    rng = np.random.default_rng(0)
+    m0 = rng.standard_normal((50, 8)).astype(np.float32)      # [vocab, dim]
+    m1 = rng.standard_normal((50, 8)).astype(np.float32)
+    d = str(tmp_path / "ckpt") + "/"
+    modelio.saveModel(d, {"dim": 8, "vocabSize": 50, "nskip": 5}, [m0, m1])
+    assert sorted(p.name for p in (tmp_path / "ckpt").iterdir()) == ["modelmat00.lz4", "modelmat01.lz4",
+                                                                    "options.json"]
+    assert json.load(open(d + "options.json"))["vocabSize"] == 50
+    raw = matio.lz4_stream_decompress(open(d + "modelmat00.lz4", "rb").read())
+    assert struct.unpack_from("<iiii", raw, 0) == (130, 8, 50, 0)     # FMat, dim rows, vocab columns
+    assert raw[16:] == m0.tobytes()                                    # word w = column w = 8 contiguous floats
+    opts, mats = modelio.loadModel(d)
+    assert opts["dim"] == 8 and len(mats) == 2
+    assert np.array_equal(mats[0], m0) and np.array_equal(mats[1], m1)

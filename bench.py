@@ -312,11 +312,34 @@ def run_ours(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()), lib.w2v_launch_count() - launches0, clocks, pos
 
+    def probe_bounds(reps=8):
+        """The memory side of the negative kernels alone, on the workload's own columns:
+        the update kernel's atomic row reductions with zeros (nothing else), and the
+        scoring kernel's row reads (nothing else).  ms per launch, CUDA events."""
+        out = []
+        for mode in (0, 1):
+            tot = 0.0
+            for r in range(reps + 2):
+                model.wordMats([devt[r % POOL]], batch_id=1000 + r)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                err = lib.w2v_probe_rows(model._ctx, model.modelmats[1].data_ptr(), model.modelmats[0].data_ptr(),
+                                         mode, model._stream())
+                b.record(stream)
+                torch.cuda.synchronize()
+                if err:
+                    return None
+                if r >= 2:
+                    tot += a.elapsed_time(b)
+            out.append(tot / reps)
+        return out
+
     pos = 0
     ms_dev, launches, clocks, pos = timed(False, pos)
     tm = _lib.W2VTiming()
     lib.w2v_get_timing(model._ctx, tm)
     ms_e2e, _, clocks_e2e, pos = timed(True, pos)
+    bounds = probe_bounds() if (rank == 0 and world == 1) else None
     sampler.stop()
 
     if rank != 0:
@@ -341,6 +364,8 @@ def run_ours(args):
                            "evalpos_ms": tm.evalpos_ms / nb, "evalneg_ms": tm.evalneg_ms / nb,
                            "evalneg_algorithmic_gbs": eg * (w["nneg"] + w["nreuse"]) * row / (tm.evalneg_ms / nb) / 1e6,
                            "evalpos_algorithmic_gbs": (N + ep) * row / (tm.evalpos_ms / nb) / 1e6},
+                # reading the negative columns' rows and nothing else, same columns (ms per launch)
+                "memory_bound": {"gather_only_ms": bounds[1]} if bounds else None,
                 "clocks": clocks}
         print(json.dumps(line), flush=True)
         if world > 1:
@@ -363,12 +388,18 @@ def run_ours(args):
     # changes the L2 hit rate, so no traffic figure is claimed for it
     default_shape = all(w[k] == DEFAULT_WORKLOAD[k] for k in ("vocab", "dim", "ntokens", "nneg", "nreuse", "nskip"))
     traffic = NEG_DRAM_TRAFFIC_BYTES if default_shape else None
-    roofline = {"bound": "hbm", "kernel": "neg_update_staged_kernel<5,5,3,false>", "achieved": achieved, "peak": peak,
+    roofline = {"bound": "hbm", "kernel": "neg_update_staged_kernel<%d,%d,%d,false>" % (
+                    w["nneg"], w["nreuse"], (w["dim"] // 4 + 31) // 32), "achieved": achieved, "peak": peak,
                 "peak_kind": peak_kind, "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
                 "traffic": traffic, "algorithmic_bytes_per_launch": neg_bytes,
                 "avg_launch_ms": neg_s * 1e3,
                 # the same fraction from the measured DRAM bytes instead of the algorithmic ones
-                "dram_frac": (traffic / neg_s / 1e9 / peak) if (traffic and neg_s > 0) else None}
+                "dram_frac": (traffic / neg_s / 1e9 / peak) if (traffic and neg_s > 0) else None,
+                # what the kernel's atomic row reductions take with nothing else in the kernel
+                # (zeros added to the same rows), and what reading those rows takes: ms per launch
+                "memory_bound": ({"scatter_only_ms": bounds[0], "gather_only_ms": bounds[1],
+                                  "atomic_payload_gbs": neg_bytes / 2 / (bounds[0] * 1e-3) / 1e9,
+                                  "kernel_over_scatter_only": neg_s * 1e3 / bounds[0]} if bounds else None)}
     phases = {"prep_ms": tm.prep_ms / nb, "permute_ms": tm.permute_ms / nb, "pos_ms": tm.pos_ms / nb,
               "neg_ms": tm.neg_ms / nb, "pairs_per_step": pairs, "groups_per_step": groups,
               "pos_algorithmic_gbs": pos_bytes / pos_s / 1e9 if pos_s > 0 else None,

@@ -50,6 +50,7 @@ SIGNATURES = {
     "word2vecEvalPos": (_I, [_I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "word2vecEvalNeg": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "word2vecEvalNegNoAlloc": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "w2v_probe_rows": (_I, [_P, _P, _P, _I, _P]),
     "bidmach_xxh32": (C.c_uint32, [_P, C.c_int64, C.c_uint32]),
     "bidmach_lz4_compress_bound": (C.c_int64, [C.c_int64]),
     "bidmach_lz4_compress": (C.c_int64, [_P, C.c_int64, _P, C.c_int64]),

@@ -12,9 +12,12 @@
 //     last match starting at least 12 bytes before the end);
 //   * XXH32, the 32-bit xxHash;
 // and, in matio.py, lz4-java's block-stream container around them.
-// No fixture of either exists in the reference: parity unpinned for ".lz4"
-// files (the uncompressed and ".gz" layouts are pinned by the reference's own
-// C writers, src/main/C/newparse/utils.cpp:350-362).
+// Pinning: the uncompressed and ".gz" layouts by the reference's own C writers
+// (src/main/C/newparse/utils.cpp:350-362); the container and the checksum by
+// the one ".lz4" matrix file in the BIDMach checkout
+// (scripts/networks/modelmat_test.fmat.lz4, raw blocks only); XXH32 by its
+// published test values; the block codec by interoperation with another LZ4
+// implementation in the tests.
 #include <stdint.h>
 #include <string.h>
 

@@ -674,6 +674,16 @@ int w2v_evalbatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, const fl
   return 0;
 }
 
+int w2v_probe_rows(w2v_ctx *c, float *A, float *B, int mode, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!c) return 1;
+  int groups = 0;
+  const int *groups_dev = nullptr;
+  group_count(c, &groups, &groups_dev);
+  return w2v::row_probe_async(c->o.dim, groups, groups_dev, c->o.nneg, c->o.nreuse, c->wa, c->ctx_out,
+                              A, B, c->hot, mode, c->retvals + 2, stream);
+}
+
 int w2v_dobatch_host(w2v_ctx *c, const int *tokens_host, float *A, float *B, int64_t pos,
                      uint64_t batch_id, int64_t *npairs_host, void *stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;

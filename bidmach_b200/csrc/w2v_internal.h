@@ -51,5 +51,10 @@ int neg_update_async(int dim, int ncols, const int *ncols_dev, int nwords, int n
 int neg_eval_async(int dim, int ncols, const int *ncols_dev, int nwa, int nwb, const int *WA,
                    const int *WB, const float *A, const float *B, float *retval,
                    cudaStream_t stream);
+// Memory side only of the negative kernels on the same columns: mode 0 adds zeros to
+// every row with the update kernel's reductions, mode 1 reads every row.
+int row_probe_async(int dim, int ncols, const int *ncols_dev, int nwa, int nwb, const int *WA,
+                    const int *WB, float *A, float *B, const HotRows &hot, int mode, float *sink,
+                    cudaStream_t stream);
 
 }  // namespace w2v

@@ -1352,6 +1352,69 @@ int neg_eval_async(int dim, int ncols, const int *ncols_dev, int nwa, int nwb, c
                  const_cast<float *>(B), 0.f, 0.f, retval, hot_rows_at(nullptr, 0), stream);
 }
 
+// ---------------------------------------------------------------------------
+// Row-traffic probe: the memory side of the negative update or scoring with
+// the arithmetic left out, on the same columns.  MODE 0 adds a row of zeros to
+// every row of every column with the update kernel's atomic reductions (the
+// model is left as it was); MODE 1 reads every row.  The time of a launch is
+// what the memory system needs for the kernel's scatter or gather alone.
+// ---------------------------------------------------------------------------
+template <int NR, int MODE>
+__global__ void __launch_bounds__(512) row_probe_kernel(int dim, int ncols,
+                                                        const int *__restrict__ ncols_dev, int nwa,
+                                                        int nwb, const int *__restrict__ WA,
+                                                        const int *__restrict__ WB, float *A, float *B,
+                                                        HotRows hot, float *sink) {
+  const int lane = threadIdx.x & 31;
+  const int nvec = dim >> 2;
+  const bool tail = lane + 32 * (NR - 1) < nvec;
+  const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  if (ncols_dev) ncols = *ncols_dev;
+  PRow<NR> zero;
+  prow_zero(zero);
+  float seen = 0.f;
+  for (int col = gwarp; col < ncols; col += nwarps) {
+    int myw = 0;
+    if (lane < nwa)
+      myw = WA[(int64_t)col * nwa + lane];
+    else if (lane < nwa + nwb)
+      myw = WB[(int64_t)col * nwb + (lane - nwa)];
+    for (int r = 0; r < nwa + nwb; r++) {
+      const int w = __shfl_sync(kFullMask, myw, r);
+      if (MODE == 0) {
+        float *dst = (r < nwa) ? update_target(A, hot.shadowA, hot, w, dim, gwarp)
+                               : update_target(B, hot.shadowB, hot, w, dim, gwarp);
+        prow_red_lane(dst + 4 * lane, tail, zero);
+      } else {
+        PRow<NR> row;
+        prow_load_lane(row, reinterpret_cast<const ulonglong2 *>((r < nwa ? A : B) + (int64_t)w * dim) + lane, tail);
+        seen += prow_dot_partial(row, row);
+      }
+    }
+  }
+  if (MODE == 1 && seen == -1.0f) *sink = seen;  // keeps the loads alive; never true
+}
+
+int row_probe_async(int dim, int ncols, const int *ncols_dev, int nwa, int nwb, const int *WA,
+                    const int *WB, float *A, float *B, const HotRows &hot, int mode, float *sink,
+                    cudaStream_t stream) {
+  if (ncols <= 0) return 0;
+  if (!vector_ok(dim, A, B) || nwa + nwb > 32 || mode < 0 || mode > 1) return 1;
+  const int nr = (dim / 4 + 31) / 32;
+  if (nr > 10) return 1;
+  const int grid = device_sm_count() * 4;
+  if (mode == 0) {
+    W2V_NR_SWITCH(nr, (row_probe_kernel<NR, 0><<<grid, 512, 0, stream>>>(dim, ncols, ncols_dev, nwa, nwb, WA,
+                                                                       WB, A, B, hot, sink)));
+  } else {
+    W2V_NR_SWITCH(nr, (row_probe_kernel<NR, 1><<<grid, 512, 0, stream>>>(dim, ncols, ncols_dev, nwa, nwb, WA,
+                                                                       WB, A, B, hot, sink)));
+  }
+  count_launch(1);
+  return (int)cudaGetLastError();
+}
+
 bool neg_shape_supported(int nwa, int nwb) {
   const int which = nwa * 10000 + nwb;
   return which == 50001 || which == 50005 || which == 100005 || which == 50010;

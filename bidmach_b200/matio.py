@@ -13,8 +13,11 @@ file layout is pinned by the reference's own C writers
 ``type`` 110 = int32, 120 = int64, 130 = float32, 140 = float64.  The extension
 selects the compression of the whole stream: none, ``.gz`` (gzip, as
 utils.cpp:300-341), or ``.lz4``: lz4-java's block stream.  That container is
-restated from the library's published format (no copy of it ships with the
-reference, so this layer's parity is unpinned): per block the 8 bytes
+restated from the library's published format and pinned by the one such file
+in the BIDMach checkout (scripts/networks/modelmat_test.fmat.lz4, whose blocks
+are stored raw: framing, checksum and end mark are pinned by it, the
+LZ4-compressed block method by interoperation with another LZ4 implementation
+in the tests): per block the 8 bytes
 ``LZ4Block``, a token byte (method 0x10 raw / 0x20 LZ4, or'ed with
 ``log2(blocksize) - 10``), int32 compressed length, int32 original length, int32
 XXH32 checksum of the original bytes (seed 0x9747b28c, low 28 bits), then the

@@ -236,6 +236,14 @@ typedef struct w2v_timing {
 int w2v_set_timing(w2v_ctx *ctx, int on);
 int w2v_get_timing(w2v_ctx *ctx, w2v_timing *out); /* synchronises the last stream used */
 
+/* Diagnostic: the memory side of the negative kernels alone, on the columns of
+ * the latest w2v_wordmats.  mode 0: a row of zeros is added to every row of
+ * every column with the update kernel's atomic reductions (A and B keep their
+ * values); mode 1: every row is read.  The duration of the call's kernel is
+ * what the memory system needs for the scatter (the gather) of one negative
+ * update (scoring) launch: the bound bench.py --mode bound reports. */
+int w2v_probe_rows(w2v_ctx *ctx, float *A, float *B, int mode, void *stream);
+
 /* Number of kernels this library has launched in this process (all threads). */
 long long w2v_launch_count(void);
 

@@ -197,3 +197,32 @@ def test_filesource_without_files_raises(tmp_path):
     from bidmach_b200.filesource import FileSource, FileSourceOpts, simpleEnum
     with pytest.raises(RuntimeError):
         FileSource(FileSourceOpts(fnames=simpleEnum(str(tmp_path / "none%05d.imat"))))
+
+
+def test_lz4_stream_reader_against_a_file_bidmat_wrote():
+    """Golden vector: the tail (last data block + end mark) of the one matrix file in the
+    BIDMach checkout that BIDMat wrote through lz4-java, with the header fields of all its
+    blocks (tests/golden/make_lz4_golden.py).  Pins the container: magic, token, the two
+    lengths, the 28-bit XXH32 checksum with lz4-java's seed, the end mark."""
+    import json
+    import os
+
+    from bidmach_b200 import matio
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    meta = json.load(open(os.path.join(here, "lz4block_meta.json")))
+    tail = open(os.path.join(here, "lz4block_tail.bin"), "rb").read()
+    last, end = meta["blocks"][-2], meta["blocks"][-1]
+    assert tail[:8] == b"LZ4Block" and struct.unpack_from("<BiiI", tail, 8) == (
+        last["token"], last["compressed"], last["original"], last["checksum"])
+    assert last["token"] == 0x16 and end == {"offset": end["offset"], "token": 0x16, "compressed": 0,
+                                             "original": 0, "checksum": 0}
+    chunk = matio.lz4_stream_decompress(tail)                 # verifies the stored checksum
+    assert len(chunk) == last["original"]
+    assert matio.xxh32(chunk, 0x9747B28C) & 0x0FFFFFFF == last["checksum"]
+    # this build's writer frames the same bytes identically (the block is incompressible: raw)
+    assert matio.lz4_stream_compress(chunk) == tail
+    src = os.path.join("/root/reference", meta["source"])
+    if os.path.exists(src):                                  # the whole file, where the checkout is at hand
+        payload = matio.lz4_stream_decompress(open(src, "rb").read())
+        assert len(payload) == meta["payload_bytes"] and matio.xxh32(payload, 0) == meta["payload_xxh32_seed0"]
+        assert list(struct.unpack_from("<6i", payload, 0)) == meta["matrix_header_ints"]

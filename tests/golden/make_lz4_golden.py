@@ -6,8 +6,9 @@ scripts/networks/modelmat_test.fmat.lz4.  Writes
   lz4block_meta.json   the header fields of every block, the matrix header ints and
                        the XXH32 (seed 0) of the whole decompressed payload
 
-Run from the repository root with the BIDMach checkout at the given path:
-    python tests/golden/make_lz4_golden.py /root/reference
+Run from the repository root, giving the path of the BIDMach checkout (or set
+BIDMACH_REFERENCE, as oracle/build.py reads it):
+    python tests/golden/make_lz4_golden.py <BIDMach checkout>
 """
 import json
 import os
@@ -41,4 +42,5 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    from oracle.build import REF_ROOT  # noqa: E402  (BIDMACH_REFERENCE or its default)
+    main(sys.argv[1] if len(sys.argv) > 1 else REF_ROOT)

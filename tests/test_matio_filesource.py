@@ -221,7 +221,8 @@ def test_lz4_stream_reader_against_a_file_bidmat_wrote():
     assert matio.xxh32(chunk, 0x9747B28C) & 0x0FFFFFFF == last["checksum"]
     # this build's writer frames the same bytes identically (the block is incompressible: raw)
     assert matio.lz4_stream_compress(chunk) == tail
-    src = os.path.join("/root/reference", meta["source"])
+    from oracle.build import REF_ROOT
+    src = os.path.join(REF_ROOT, meta["source"])
     if os.path.exists(src):                                  # the whole file, where the checkout is at hand
         payload = matio.lz4_stream_decompress(open(src, "rb").read())
         assert len(payload) == meta["payload_bytes"] and matio.xxh32(payload, 0) == meta["payload_xxh32_seed0"]

@@ -123,8 +123,13 @@ class ClockSampler:
 
 
 def make_pool(rank: int, n: int):
-    from bidmach_b200.corpus import zipf_cdf, zipf_corpus
+    from bidmach_b200.corpus import TopicCorpus, zipf_cdf, zipf_corpus
     w = WORKLOAD
+    if w.get("topics"):
+        # configs[3]/[4]: documents of a seeded topic model, 1000 tokens each
+        tc = TopicCorpus(w["vocab"], w["topics"], w["zipf_s"], 0.1, w["doc_len"], seed=11)
+        ndocs = w["ntokens"] // w["doc_len"]
+        return [tc.tokens((rank * n + k) * ndocs, ndocs) for k in range(n)]
     cdf = zipf_cdf(w["vocab"], w["zipf_s"])
     return [zipf_corpus(w["vocab"], w["ntokens"], w["zipf_s"], seed=1000 * rank + k,
                         doc_len=w["doc_len"], cdf=cdf, first_doc=k * 1000) for k in range(n)]
@@ -213,6 +218,14 @@ def config_dict(args, extra=None):
                         + (" (overlapped with the next minibatch)" if args.overlap_sync else " (blocking)")
                         if args.gpus > 1 else "single GPU",
          "l2_policy": "inputs larger than L2: 2.4 GB of embedding rows gathered per Zipf draw; no flush"}
+    if w.get("topics"):
+        c["workload"] = ("configs[3]/[4] shape: minibatches of %d-token documents from a seeded topic model "
+                         "(%d topics, Zipf(%.2f) per topic, Dirichlet(0.1) mixtures), ids ranked by frequency"
+                         % (w["doc_len"], w["topics"], w["zipf_s"]))
+        c["topics"] = w["topics"]
+    elif w["wsample"] != DEFAULT_WORKLOAD["wsample"] or w["vocab"] != DEFAULT_WORKLOAD["vocab"] \
+            or w["nneg"] != DEFAULT_WORKLOAD["nneg"] or w["ntokens"] != DEFAULT_WORKLOAD["ntokens"]:
+        c["workload"] = "configs[1] with overrides (see the fields below)"
     if extra:
         c.update(extra)
     return c
@@ -449,6 +462,11 @@ def main():
     ap.add_argument("--vocab", type=int, default=None, help="override the workload's vocabulary (profiling)")
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per minibatch (profiling)")
     ap.add_argument("--nneg", type=int, default=None, help="override the number of negatives (configs[4] uses 10)")
+    ap.add_argument("--wsample", type=float, default=None,
+                    help="frequent-word subsampling (configs[3] and [4] use 1e-4; default: none)")
+    ap.add_argument("--topics", type=int, default=None,
+                    help="draw the minibatches from a topic-model corpus with this many topics "
+                         "(configs[3]: 1000, configs[4]: 3000) instead of i.i.d. Zipf text")
     ap.add_argument("--sort-permute", action="store_true",
                     help="shuffle the pair list by sorting random keys (the reference's GPU branch) "
                          "instead of the keyed bijection")
@@ -459,6 +477,10 @@ def main():
         WORKLOAD["ntokens"] = args.tokens
     if args.nneg:
         WORKLOAD["nneg"] = args.nneg
+    if args.wsample is not None:
+        WORKLOAD["wsample"] = args.wsample
+    if args.topics:
+        WORKLOAD["topics"] = args.topics
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -1184,6 +1184,10 @@ int pos_eval_async(int dim, int ncols, const int *ncols_dev, int skip, const int
   return (int)cudaGetLastError();
 }
 
+// blocks per SM the negative scoring grid is cut into (four are resident at a time;
+// more and shorter blocks even out the tail: measured 1.78 / 1.74 / 1.71 ms at 4 / 8 / 16)
+constexpr int kNegEvalGridBlocks = 16;
+
 static bool neg_staged_enabled() {
   static bool on = [] {
     const char *e = getenv("W2V_NEG_IMPL");
@@ -1266,7 +1270,7 @@ static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int
   if constexpr (NWA + NWB == 15) {
     // scoring a 10+5 column = scoring its two 5+5 halves, which the register-resident kernel holds
     if (eval && vector_ok(dim, A, B) && nr >= 3 && nr <= 4) {
-      const int grid = grid_for(ncols, kNegThreads, 8);
+      const int grid = grid_for(ncols, kNegThreads, kNegEvalGridBlocks);
       for (int half = 0; half < 2; half++) {
         const int *wa = WA + (NWA == 10 ? 5 * half : 0), *wb = WB + (NWB == 10 ? 5 * half : 0);
         if (nr == 3)
@@ -1293,7 +1297,7 @@ static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int
     if (e != cudaSuccess) return (int)e;
     if (!eval) fold_hot_rows(dim, hot, A, B, stream);
   } else if (vector_ok(dim, A, B) && nr <= kMaxNr) {
-    const int grid = grid_for(ncols, kNegThreads, 8);
+    const int grid = grid_for(ncols, kNegThreads, eval ? kNegEvalGridBlocks : 8);
     if (eval) {
       switch (nr) {
         case 1: neg_eval_kernel<NWA, NWB, 1><<<grid, kNegThreads, 0, stream>>>(dim, ncols, ncols_dev, WA, WB, A, B, scratch, retval, NWA, NWB); break;

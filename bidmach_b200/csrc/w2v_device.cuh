@@ -108,18 +108,6 @@ __device__ __forceinline__ void row_axpy(Row<NR> &acc, float c, const Row<NR> &x
   }
 }
 
-// M[w] += r   (atomic, 128 bits at a time)
-template <int NR>
-__device__ __forceinline__ void row_red(float *M, int64_t w, int dim, int nvec, int lane,
-                                        const Row<NR> &r) {
-  float *p = M + w * (int64_t)dim;
-#pragma unroll
-  for (int q = 0; q < NR; q++) {
-    int idx = lane + 32 * q;
-    if (idx < nvec) red_add_v4(p + 4 * idx, r.v[q]);
-  }
-}
-
 // ---------------------------------------------------------------------------
 // Many-value warp reduction.  Each lane brings M partial sums; five exchange
 // steps later the M totals are spread over the lanes (FIN per lane) instead of
@@ -268,19 +256,6 @@ __device__ __forceinline__ void prow_zero(PRow<NR> &r) {
   for (int q = 0; q < NR; q++) r.v[q][0] = r.v[q][1] = 0ull;
 }
 
-// Row from a 16-byte aligned base (global or shared); nvec = dim / 4.
-template <int NR>
-__device__ __forceinline__ void prow_load(PRow<NR> &r, const void *base, int nvec, int lane) {
-  const ulonglong2 *p = reinterpret_cast<const ulonglong2 *>(base);
-#pragma unroll
-  for (int q = 0; q < NR; q++) {
-    const int idx = lane + 32 * q;
-    const ulonglong2 t = (idx < nvec) ? p[idx] : make_ulonglong2(0ull, 0ull);
-    r.v[q][0] = t.x;
-    r.v[q][1] = t.y;
-  }
-}
-
 template <int NR>
 __device__ __forceinline__ float prow_dot_partial(const PRow<NR> &a, const PRow<NR> &b) {
   // one packed accumulator: many dot products are always in flight, so the
@@ -316,21 +291,6 @@ __device__ __forceinline__ void prow_axpy(PRow<NR> &acc, float c, const PRow<NR>
   for (int q = 0; q < NR; q++) {
     acc.v[q][0] = fma2(cc, x.v[q][0], acc.v[q][0]);
     acc.v[q][1] = fma2(cc, x.v[q][1], acc.v[q][1]);
-  }
-}
-
-// dst[0..dim) += r   (atomic, 128 bits at a time)
-template <int NR>
-__device__ __forceinline__ void prow_red_to(float *dst, int nvec, int lane, const PRow<NR> &r) {
-#pragma unroll
-  for (int q = 0; q < NR; q++) {
-    const int idx = lane + 32 * q;
-    if (idx < nvec) {
-      float4 v;
-      unpack2(r.v[q][0], v.x, v.y);
-      unpack2(r.v[q][1], v.z, v.w);
-      red_add_v4(dst + 4 * idx, v);
-    }
   }
 }
 

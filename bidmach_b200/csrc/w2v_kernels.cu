@@ -28,9 +28,12 @@
 // inputs where no row is shared between units the result equals the sequential
 // CPU result up to fp32 summation order.
 //
-// Work decomposition: one warp per token position (Pos) or per column (Neg);
-// the rows of the unit live in registers as 128-bit vectors; dot products are
-// reduced with warp shuffles; grids are sized to fill every SM.
+// Work decomposition: a warp per stretch of token positions (Pos) or per column
+// (Neg); a row is dim/4 16-byte vectors of which lane l owns l, l+32, ...; dot
+// products are reduced with warp shuffles so that each total ends on one lane;
+// grids are sized to fill every SM.  Neg stages a column's rows in shared memory
+// with bulk asynchronous copies and is bound by the L2's atomic throughput; the
+// scoring kernels read rows straight from global memory.
 //
 // Pos walks the minibatch in order: every warp owns a contiguous stretch of
 // positions and visits its centres one after the other.  The delta of a

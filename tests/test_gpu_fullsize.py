@@ -87,12 +87,32 @@ def test_full_minibatch_preprocessing_properties(oracle):
     full = np.bincount(ctx, minlength=V)
     assert (have <= full).all() and full.sum() - have.sum() == len(ctx) - g * o.nreuse
     assert np.array_equal(wa.cpu().numpy().ravel(), oracle.negative_ids(un, oracle.expt_of(o.wexpt), V))
+    # and the shuffle is exactly the keyed bijection of the pair indices
+    perm = oracle.library_permutation(o.seed, 5, len(ctx))
+    assert np.array_equal(wb.cpu().numpy().ravel(), ctx[perm[: g * o.nreuse]])
     # windows never cross a sentence boundary
     i = np.arange(N)
     assert (toks[np.clip(i + lb, 0, N - 1), 1] == toks[:, 1]).all()
     assert (toks[np.clip(i + ub, 0, N - 1), 1] == toks[:, 1]).all()
     # heavy subsampling of the most frequent words, none of the rare ones
     assert (words[toks[:, 0] == 0] >= 0).mean() < 0.1 and (words[toks[:, 0] > 1000] >= 0).all()
+
+
+def test_dense_minibatch_shuffle_is_the_keyed_bijection(oracle):
+    """No subsampling: 6M pairs, the size the benchmark shuffles every minibatch."""
+    from bidmach_b200 import Word2Vec
+    from bidmach_b200.corpus import zipf_corpus
+    from bidmach_b200.word2vec import Opts
+    o = Opts(dim=D, vocabSize=V, wsample=1.0, seed=21)
+    toks = zipf_corpus(V, N, 1.07, seed=8, doc_len=1000)
+    model = Word2Vec(o).init(N)
+    _, _, _, wa, wb = model.wordMats([dev(toks)], batch_id=2)
+    ctx = model.last_contexts.cpu().numpy()
+    assert len(ctx) > 5_900_000
+    perm = oracle.library_permutation(o.seed, 2, len(ctx))
+    assert np.array_equal(np.sort(perm), np.arange(len(ctx)))
+    assert np.array_equal(wb.cpu().numpy().ravel(), ctx[perm[: wb.numel()]])
+    assert wa.shape[0] == wb.shape[0] == len(ctx) // o.nreuse
 
 
 def test_full_minibatch_scores_match_oracle_and_zero_lrate_is_identity(oracle, big_model):

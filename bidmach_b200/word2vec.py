@@ -347,23 +347,36 @@ class Word2Vec:
     # -- constructors and file formats of the companion object -----------------
     @staticmethod
     def learner(tokens, opts: "Opts | None" = None, batchSize: int = 1_000_000, lopts=None):
-        """Word2Vec.learner (Word2Vec.scala:1222-1245): a single-GPU learner over an
-        in-memory token matrix (int32 ``[ntokens, 2]``).  Returns (learner, opts)."""
-        from .learner import Learner, MatSource
+        """Word2Vec.learner (Word2Vec.scala:1222-1254): a single-GPU learner over an
+        in-memory token matrix (int32 ``[ntokens, 2]``, the reference's
+        ``learner(mat0)``) or, when ``tokens`` is a file-name pattern such as
+        ``"data/train%05d.imat.lz4"``, over those files (``learner(fn1)``).
+        Returns (learner, opts)."""
+        from .learner import Learner
         opts = opts or Opts()
-        return Learner(MatSource(tokens, batchSize), Word2Vec(opts), lopts), opts
+        return Learner(Word2Vec._source(tokens, batchSize, 0, 1), Word2Vec(opts), lopts), opts
+
+    @staticmethod
+    def _source(tokens, batchSize, rank, world):
+        from .learner import MatSource
+        if isinstance(tokens, str):
+            from .filesource import FileSource, FileSourceOpts, simpleEnum
+            return FileSource(FileSourceOpts(fnames=simpleEnum(tokens), batchSize=batchSize), rank, world)
+        return MatSource(tokens, batchSize, rank, world)
 
     @staticmethod
     def learnPar(tokens, opts: "Opts | None" = None, batchSize: int = 1_000_000, lopts=None, group=None):
         """Word2Vec.learnPar (Word2Vec.scala:1312-1328): the data-parallel learner of
-        this rank (one process per GPU, ``torch.distributed`` initialised)."""
+        this rank (one process per GPU, ``torch.distributed`` initialised) over a
+        token matrix or a file-name pattern; the minibatches are dealt to the
+        replicas in turn."""
         import torch.distributed as dist
-        from .learner import MatSource, ParLearner
+        from .learner import ParLearner
         opts = opts or Opts()
         rank = dist.get_rank(group) if dist.is_initialized() else 0
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         opts.seed = opts.seed + 7919 * rank   # every replica draws its own samples
-        return ParLearner(MatSource(tokens, batchSize, rank, world), Word2Vec(opts), lopts, group), opts
+        return ParLearner(Word2Vec._source(tokens, batchSize, rank, world), Word2Vec(opts), lopts, group), opts
 
     def save(self, fname: str):
         """Model.save (models/Model.scala:245-263): ``options.json`` and

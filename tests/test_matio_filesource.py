@@ -227,3 +227,20 @@ def test_lz4_stream_reader_against_a_file_bidmat_wrote():
         payload = matio.lz4_stream_decompress(open(src, "rb").read())
         assert len(payload) == meta["payload_bytes"] and matio.xxh32(payload, 0) == meta["payload_xxh32_seed0"]
         assert list(struct.unpack_from("<6i", payload, 0)) == meta["matrix_header_ints"]
+
+
+def test_learner_constructors_take_a_file_pattern(tmp_path):
+    """Word2Vec.learner(fn1) / learnPar(fn1) (Word2Vec.scala:1240-1254, 1315): a file-name
+    pattern selects a FileSource; replica r of n gets minibatches r, r + n, ..."""
+    from bidmach_b200.filesource import FileSource
+    from bidmach_b200.learner import MatSource
+    from bidmach_b200.word2vec import Word2Vec
+    pat, total = _write_corpus(tmp_path, [100, 100], ext=".imat.gz")
+    src = Word2Vec._source(pat, 50, 1, 2)
+    assert isinstance(src, FileSource)
+    got = []
+    while src.hasNext():
+        got.append(int(src.next()[0][0, 0]))
+    src.close()
+    assert got == [50, 150]
+    assert isinstance(Word2Vec._source(np.zeros((10, 2), np.int32), 5, 0, 1), MatSource)

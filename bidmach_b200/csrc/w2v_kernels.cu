@@ -178,12 +178,29 @@ template <int NR>
 struct ChunkOf {
   static constexpr int value = NR <= 4 ? 5 : (NR <= 6 ? 3 : 2);
 };
+// The scoring kernel holds no deltas, so it can take more rows at a time.
+template <int NR>
+struct EvalChunkOf {
+  static constexpr int value = NR <= 3 ? 10 : ChunkOf<NR>::value;
+};
 // Resident blocks per SM the positive update is compiled for (its ring of
 // row-sized slots in shared memory allows no more for wide rows anyway).
 template <int NR>
 struct PosBlocksOf {
   static constexpr int value = NR <= 3 ? 4 : (NR <= 5 ? 2 : 1);
 };
+
+// Calls take(integral_constant<n>) for a run-time n in [LO, HI]: one
+// instantiation of the chunk body per size, exactly one of them taken.
+template <int LO, int HI, class F>
+__device__ __forceinline__ void take_n(int n, F &take) {
+  if constexpr (LO <= HI) {
+    if (n == LO)
+      take(std::integral_constant<int, LO>());
+    else
+      take_n<LO + 1, HI>(n, take);
+  }
+}
 
 // What lane `lane` sees at offset lane - skip from position t: the word there
 // and whether t, as a centre, pairs with it.
@@ -353,11 +370,7 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
         while (cnt > 0) {
           const int n = cnt > kChunk ? min(kChunk, (cnt + 1) >> 1) : cnt;
           cnt -= n;
-          if (n == 1) take(std::integral_constant<int, 1>());
-          if constexpr (kChunk >= 2) { if (n == 2) take(std::integral_constant<int, 2>()); }
-          if constexpr (kChunk >= 3) { if (n == 3) take(std::integral_constant<int, 3>()); }
-          if constexpr (kChunk >= 4) { if (n == 4) take(std::integral_constant<int, 4>()); }
-          if constexpr (kChunk >= 5) { if (n == 5) take(std::integral_constant<int, 5>()); }
+          take_n<1, kChunk>(n, take);
         }
         prow_red_lane(update_target(A, hot.shadowA, hot, wt, dim, gwarp) + 4 * lane, tail, da);
       }
@@ -409,7 +422,7 @@ __global__ void __launch_bounds__(kPosThreads)
                     const int *__restrict__ W, const int *__restrict__ LB,
                     const int *__restrict__ UB, const float *__restrict__ A,
                     const float *__restrict__ B, EvalScratch *scratch, float *retval) {
-  constexpr int kChunk = ChunkOf<NR>::value;
+  constexpr int kChunk = EvalChunkOf<NR>::value;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = dim >> 2;
   const bool tail = lane + 32 * (NR - 1) < nvec;
@@ -451,11 +464,7 @@ __global__ void __launch_bounds__(kPosThreads)
     while (cnt > 0) {
       const int n = cnt > kChunk ? min(kChunk, (cnt + 1) >> 1) : cnt;
       cnt -= n;
-      if (n == 1) take(std::integral_constant<int, 1>());
-      if constexpr (kChunk >= 2) { if (n == 2) take(std::integral_constant<int, 2>()); }
-      if constexpr (kChunk >= 3) { if (n == 3) take(std::integral_constant<int, 3>()); }
-      if constexpr (kChunk >= 4) { if (n == 4) take(std::integral_constant<int, 4>()); }
-      if constexpr (kChunk >= 5) { if (n == 5) take(std::integral_constant<int, 5>()); }
+      take_n<1, kChunk>(n, take);
     }
   }
   finish_eval_sum(acc, scratch, retval);

@@ -95,3 +95,23 @@ def test_unsupported_options_are_refused():
         Word2Vec(Opts(nSlices=2))
     with pytest.raises(RuntimeError):
         Word2Vec(Opts(useGPU=False))
+
+
+def test_row_probe_leaves_the_model_unchanged():
+    """w2v_probe_rows: the memory side of the negative kernels alone (zeros added with
+    the update kernel's reductions, or rows read); a diagnostic, so the model must come
+    out bit for bit as it went in."""
+    from bidmach_b200 import _lib
+    n = 3000
+    m = _model(n, dim=300)
+    toks = torch.from_numpy(_toks(n, 500, seed=4, doc=37)).cuda()
+    m.dobatch([toks], 0, n)                      # non-trivial matrices, replicas used
+    m.wordMats([toks], batch_id=9)
+    before = [x.clone() for x in m.modelmats]
+    lib = _lib.load()
+    for mode in (0, 1):
+        assert lib.w2v_probe_rows(m._ctx, m.modelmats[1].data_ptr(), m.modelmats[0].data_ptr(), mode,
+                                  m._stream()) == 0
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, b) for a, b in zip(before, m.modelmats))
+    assert lib.w2v_probe_rows(m._ctx, m.modelmats[1].data_ptr(), m.modelmats[0].data_ptr(), 7, m._stream()) == 1

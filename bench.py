@@ -215,7 +215,8 @@ def config_dict(args, extra=None):
          "vexp": w["vexp"], "minibatch_pool": POOL,
          "parallelism": f"dp{args.gpus}: replicas, own minibatches, all-reduce(avg) of both matrices "
                         f"every {args.sync_every} minibatches"
-                        + (" (overlapped with the next minibatch)" if args.overlap_sync else " (blocking)")
+                        + (" (overlapped with the next minibatch)" if args.overlap_sync else
+                           " (head rows only, the reference's schedule)" if args.head_sync else " (blocking)")
                         if args.gpus > 1 else "single GPU",
          "l2_policy": "inputs larger than L2: 2.4 GB of embedding rows gathered per Zipf draw; no flush"}
     if w.get("topics"):
@@ -294,7 +295,12 @@ def run_ours(args):
             else:
                 model.dobatch([devt[s % POOL]], 0, pos)
             if world > 1:
-                if not args.overlap_sync:
+                if args.head_sync:
+                    # the reference's schedule (Learner.scala:654-655, Word2Vec.scala:548): sync k
+                    # averages the first headlen << trailingZeros(k * world) rows of each matrix
+                    if (s + 1) % args.sync_every == 0:
+                        model.mergeModelFn(None, (s + 1) * world // args.sync_every)
+                elif not args.overlap_sync:
                     if (s + 1) % args.sync_every == 0:
                         model.mergeModelFn()
                 else:   # the exchange runs beside the next minibatch and is folded in after it
@@ -456,6 +462,9 @@ def main():
     ap.add_argument("--overlap-sync", action="store_true",
                     help="multi-GPU: run the averaging all-reduce beside the next minibatch (snapshot + "
                          "delayed correction) instead of blocking on it")
+    ap.add_argument("--head-sync", action="store_true",
+                    help="average only the growing head of the vocabulary at each sync, as the reference's "
+                         "mergeModelFn does, instead of the whole model")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--mode", default="train", choices=["train", "eval"],
                     help="eval: time the scoring path (evalbatch) instead of the update path")

@@ -290,3 +290,12 @@ def test_keyed_permutation_is_a_bijection(oracle, n):
         assert abs(np.corrcoef(np.arange(n), p)[0, 1]) < 0.05     # no trace of the input order
         assert (p == np.arange(n)).mean() < 0.01
         assert not np.array_equal(p, oracle.library_permutation(99, 5, n))   # another minibatch, another shuffle
+
+
+def test_keyed_permutation_known_answers(oracle):
+    """Frozen values: the shuffle is part of the library's reproducible behaviour
+    (seed, minibatch number -> permutation), so a change of the algorithm must show."""
+    assert oracle.library_permutation(99, 4, 1000)[:12].tolist() == [901, 489, 480, 393, 865, 397, 859, 141,
+                                                                   978, 308, 64, 102]
+    assert oracle.library_permutation(0x123456789ABCDEF0, 7, 5_985_887)[:8].tolist() == [
+        5068001, 3494612, 1389536, 5787168, 2465857, 5956610, 135992, 4957205]

@@ -272,6 +272,13 @@ struct w2v_ctx {
   int64_t first_pos;
   // device
   int *tokens, *words, *lb, *ub, *cnt, *off, *counts;
+  // host-minibatch entry points: two token buffers filled on a copy stream, so that
+  // the upload of the next minibatch runs beside the kernels of the current one
+  int *tokens_in[2];
+  cudaStream_t copy_stream;
+  cudaEvent_t ev_copied[2], ev_read[2];   // upload done / the preprocessing has read the buffer
+  int read_recorded[2];
+  uint64_t host_calls;
   int *ctx_in, *ctx_out, *wa;
   uint32_t *key_in, *key_out;
   float *retvals;  // [0] positive, [1] negative
@@ -413,6 +420,12 @@ void w2v_destroy(w2v_ctx *c) {
   int prev = 0;
   cudaGetDevice(&prev);
   cudaSetDevice(c->device);
+  cudaFree(c->tokens_in[1]);
+  if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
+  for (int k = 0; k < 2; k++) {
+    if (c->ev_copied[k]) cudaEventDestroy(c->ev_copied[k]);
+    if (c->ev_read[k]) cudaEventDestroy(c->ev_read[k]);
+  }
   cudaFree(c->tokens); cudaFree(c->words); cudaFree(c->lb); cudaFree(c->ub); cudaFree(c->cnt);
   cudaFree(c->off); cudaFree(c->counts); cudaFree(c->ctx_in); cudaFree(c->ctx_out);
   cudaFree(c->wa); cudaFree(c->key_in); cudaFree(c->key_out); cudaFree(c->retvals);
@@ -448,6 +461,13 @@ int w2v_create(const w2v_opts *opts, int ncols, w2v_ctx **out) {
   const int64_t max_groups = c->max_pairs / o.nreuse;
   size_t scan_bytes = 0, sort_bytes = 0;
   if (e == cudaSuccess) e = cudaMalloc(&c->tokens, 2 * n4);
+  if (e == cudaSuccess) e = cudaMalloc(&c->tokens_in[1], 2 * n4);
+  c->tokens_in[0] = c->tokens;
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking);
+  for (int k = 0; k < 2 && e == cudaSuccess; k++) {
+    e = cudaEventCreateWithFlags(&c->ev_copied[k], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_read[k], cudaEventDisableTiming);
+  }
   if (e == cudaSuccess) e = cudaMalloc(&c->words, n4);
   if (e == cudaSuccess) e = cudaMalloc(&c->lb, n4);
   if (e == cudaSuccess) e = cudaMalloc(&c->ub, n4);
@@ -684,27 +704,54 @@ int w2v_probe_rows(w2v_ctx *c, float *A, float *B, int mode, void *stream_) {
                               A, B, c->hot, mode, c->retvals + 2, stream);
 }
 
+// Uploads a host minibatch into the token buffer whose turn it is, on the copy
+// stream, and makes `stream` wait for it.  The buffer was last read by the
+// preprocessing of the call before the previous one.
+static int upload_tokens(w2v_ctx *c, const int *tokens_host, cudaStream_t stream, int **dev, int *which) {
+  const int k = (int)(c->host_calls++ & 1);
+  *which = k;
+  if (c->read_recorded[k]) W2V_CHECK(cudaStreamWaitEvent(c->copy_stream, c->ev_read[k], 0));
+  W2V_CHECK(cudaMemcpyAsync(c->tokens_in[k], tokens_host, 2 * sizeof(int) * (size_t)c->ncols,
+                            cudaMemcpyHostToDevice, c->copy_stream));
+  W2V_CHECK(cudaEventRecord(c->ev_copied[k], c->copy_stream));
+  W2V_CHECK(cudaStreamWaitEvent(stream, c->ev_copied[k], 0));
+  *dev = c->tokens_in[k];
+  return 0;
+}
+
 int w2v_dobatch_host(w2v_ctx *c, const int *tokens_host, float *A, float *B, int64_t pos,
                      uint64_t batch_id, int64_t *npairs_host, void *stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
-  W2V_CHECK(cudaMemcpyAsync(c->tokens, tokens_host, 2 * sizeof(int) * (size_t)c->ncols,
-                            cudaMemcpyHostToDevice, stream));
-  int err = w2v_dobatch(c, c->tokens, nullptr, A, B, pos, batch_id, stream);
+  int *dev = nullptr;
+  int k = 0;
+  int err = upload_tokens(c, tokens_host, stream, &dev, &k);
   if (err) return err;
-  W2V_CHECK(cudaStreamSynchronize(stream));
+  err = w2v_dobatch(c, dev, nullptr, A, B, pos, batch_id, stream);
+  if (err) return err;
+  // only the preprocessing reads the tokens; it is enqueued ahead of the update kernels,
+  // but an event recorded here completes after them: good enough two calls later
+  W2V_CHECK(cudaEventRecord(c->ev_read[k], stream));
+  c->read_recorded[k] = 1;
+  // the pair count is this call's result: wait for it (and thereby for the upload, so the
+  // caller may reuse its host buffer), not for the update kernels, which finish in stream order
   err = settle_counts(c);
   if (err) return err;
   if (npairs_host) *npairs_host = c->npairs;
-  W2V_CHECK(cudaGetLastError());
-  return w2v::take_stage_fault();
+  return (int)cudaGetLastError();
 }
 
 int w2v_evalbatch_host(w2v_ctx *c, const int *tokens_host, const float *A, const float *B,
                        uint64_t batch_id, double *score_host, void *stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
-  W2V_CHECK(cudaMemcpyAsync(c->tokens, tokens_host, 2 * sizeof(int) * (size_t)c->ncols,
-                            cudaMemcpyHostToDevice, stream));
-  return w2v_evalbatch(c, c->tokens, nullptr, A, B, batch_id, score_host, stream);
+  int *dev = nullptr;
+  int k = 0;
+  int err = upload_tokens(c, tokens_host, stream, &dev, &k);
+  if (err) return err;
+  err = w2v_evalbatch(c, dev, nullptr, A, B, batch_id, score_host, stream);  // synchronises
+  if (err) return err;
+  W2V_CHECK(cudaEventRecord(c->ev_read[k], stream));
+  c->read_recorded[k] = 1;
+  return 0;
 }
 
 }  // extern "C"

@@ -205,9 +205,15 @@ int w2v_evalbatch(w2v_ctx *ctx, const int *tokens, const w2v_uniforms *u, const 
                   const float *B, uint64_t batch_id, double *score_host, void *stream);
 
 /* Model.dobatchg / evalbatchg (models/Model.scala:350-365): the same two calls
- * for a minibatch that still lives in host memory.  The tokens are copied to
- * the device inside the call; dobatch_host returns after the update finished
- * and reports the number of positive pairs it trained on. */
+ * for a minibatch that still lives in host memory (pinned, for the copy to be
+ * asynchronous).  The tokens are uploaded inside the call, on a copy stream of
+ * the context and into one of two buffers, so the upload of one minibatch runs
+ * beside the kernels of the one before.  dobatch_host returns when the number
+ * of positive pairs of this minibatch is known (by then the upload is complete
+ * and the host buffer may be reused); the update kernels finish in stream
+ * order, as after w2v_dobatch.  evalbatch_host returns the score and
+ * therefore synchronises.  A staged kernel that gave up waiting for its copies
+ * is reported by the next w2v_evalbatch / w2v_evalbatch_host. */
 int w2v_dobatch_host(w2v_ctx *ctx, const int *tokens_host, float *A, float *B, int64_t pos,
                      uint64_t batch_id, int64_t *npairs_host, void *stream);
 int w2v_evalbatch_host(w2v_ctx *ctx, const int *tokens_host, const float *A, const float *B,

@@ -292,10 +292,10 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
   int wslot = 0;
   // B[W[u]] += the given slot (which belongs to position u), if it holds
   // anything; the slot is left zeroed for the position that takes it next
-  auto retire = [&](int u, int slot) {
+  auto retire = [&](int wu, int slot) {  // wu = the word at the slot's position
     if ((dirty >> slot) & 1u) {
       dirty &= ~(1u << slot);
-      float *dst = update_target(B, hot.shadowB, hot, W[u], dim, gwarp) + 4 * lane;
+      float *dst = update_target(B, hot.shadowB, hot, wu, dim, gwarp) + 4 * lane;
       ulonglong2 *sp = ring + slot * nvec;
 #pragma unroll
       for (int q = 0; q < NR; q++) {
@@ -309,11 +309,33 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
   int until_fold = 2 * hot.fold_every;
   unsigned fold_turn = gwarp * 3u;
 
+  // The index data of a position (its window of words, lane l holding offset l - skip, and
+  // its bounds) is fetched one position ahead, so that the row loads of a position do not
+  // wait for a chain of dependent index loads first.
+  auto fetch = [&](int t, int &wraw, int &lbt, int &ubt) {
+    const int u = t + lane - skip;
+    const bool in = t < last;
+    wraw = (in && lane <= 2 * skip && u >= 0 && u < ncols) ? W[u] : -1;
+    lbt = in ? max(LB[t], -skip) : 0;
+    ubt = in ? min(UB[t], skip) : 0;
+  };
+  int wraw, lbt, ubt;
+  fetch(first, wraw, lbt, ubt);
+
   for (int t = first; t < last; t++) {
-    const int wt = W[t];
+    int wraw_next, lb_next, ub_next;
+    fetch(t + 1, wraw_next, lb_next, ub_next);
+    const int wt = __shfl_sync(kFullMask, wraw, skip);
+    const int w_oldest = __shfl_sync(kFullMask, wraw, 0);  // the word at position t - skip
     if (wt >= 0) {
-      const int lbt = max(LB[t], -skip), ubt = min(UB[t], skip);
-      const Neighbour nb = look_at_neighbour(W, t, lbt, ubt, skip, ncols, lane);
+      Neighbour nb = {-1, false};
+      {
+        const int j = lane - skip;
+        if (j != 0 && j >= lbt && j <= ubt && wraw >= 0) {
+          nb.word = wraw;
+          nb.t_is_centre = true;
+        }
+      }
       unsigned todo = __ballot_sync(kFullMask, nb.t_is_centre);
       if (todo) {
         // lane 31 never carries a neighbour (at most 31 offsets), so it
@@ -376,15 +398,20 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
       }
     }
     // no later centre of this warp reaches position t - skip
-    if (dirty) retire(t - skip, wslot);
+    if (dirty) retire(w_oldest, wslot);
     wslot = (wslot + 1 == slots) ? 0 : wslot + 1;
     if (hot.fold_every > 0 && --until_fold == 0) {
       until_fold = 2 * hot.fold_every;
       fold_one_replica<NR>(hot, A, B, dim, nvec, lane, fold_turn++);
     }
+    wraw = wraw_next;
+    lbt = lb_next;
+    ubt = ub_next;
   }
   for (int k = 0; k < slots && dirty; k++) {  // positions last - skip ... last + skip
-    retire(last - skip + k, wslot);
+    const int u = last - skip + k;
+    // a dirty slot belongs to a position inside the minibatch that holds a word
+    retire((u >= 0 && u < ncols) ? W[u] : 0, wslot);
     wslot = (wslot + 1 == slots) ? 0 : wslot + 1;
   }
 }

@@ -245,3 +245,47 @@ def test_apply_average_adds_the_difference():
     torch.cuda.synchronize()
     assert torch.allclose(theta, want, rtol=0, atol=1e-6)
     assert lib.w2v_apply_average(theta.data_ptr(), base.data_ptr(), avg.data_ptr(), 7, stream) == 1
+
+
+@pytest.mark.parametrize("dim,drop", [(300, 0.0), (300, 0.3), (100, 0.15), (64, 0.0)])
+def test_pos_adjacent_centres_match_a_jacobi_reference(dim, drop):
+    """Every position a centre with its own window, all words distinct: every gradient is
+    then a function of the initial rows only (an A row is written by its own centre after it
+    was read; a B row when the window has passed), so the result must equal the sums below up
+    to fp32 order.  This is the input on which neighbouring centres share their context rows
+    (the two-centres-at-a-time path).  Positions near the seams between the four warps'
+    stretches are left out of the comparison: there a row may be read after the neighbouring
+    warp has already added its delta."""
+    from bidmach_b200 import CUMACH
+    n, V, skip, lr, vexp = 400, 1000, 5, 0.05, 0.5
+    rng = np.random.default_rng(int(dim + 100 * drop))
+    W = rng.permutation(V)[:n].astype(np.int32)
+    W[rng.random(n) < drop] = -1
+    ub = rng.integers(1, skip + 1, n).astype(np.int32)
+    LB, UB = (-ub).astype(np.int32), ub.copy()
+    A0, B0 = random_model(V, dim, 7, scale=0.5)
+    dA, dB = np.zeros((V, dim)), np.zeros((V, dim))
+    A64, B64 = A0.astype(np.float64), B0.astype(np.float64)
+    for t in range(n):
+        if W[t] < 0:
+            continue
+        for j in range(LB[t], UB[t] + 1):
+            u = t + j
+            if j == 0 or u < 0 or u >= n or W[u] < 0:
+                continue
+            d = float(np.float32(A64[W[t]] @ B64[W[u]]))
+            g = lr * (1.0 - (1.0 if d > 16 else 0.0 if d < -16 else np.exp(d) / (1 + np.exp(d))))
+            dA[W[t]] += (1.0 + W[t]) ** vexp * g * B64[W[u]]
+            dB[W[u]] += (1.0 + W[u]) ** vexp * g * A64[W[t]]
+    gA, gB = dev(A0), dev(B0)
+    assert CUMACH.word2vecPos(dim, n, skip, dev(W), dev(LB), dev(UB), gA, gB, lr, vexp) == 0
+    gotA, gotB = gA.cpu().numpy().astype(np.float64) - A64, gB.cpu().numpy().astype(np.float64) - B64
+    seams = [100, 200, 300]                       # one block of four warps: stretches of 100 positions
+    inner = np.array([t for t in range(n) if W[t] >= 0 and all(abs(t - s) > 2 * skip + 2 for s in seams)])
+    assert len(inner) > 150
+    rows = W[inner]
+    assert rel_err(gotA[rows], dA[rows]) <= 1e-5
+    assert rel_err(gotB[rows], dB[rows]) <= 1e-5
+    # nothing outside the minibatch's words moved
+    untouched = np.setdiff1d(np.arange(V), W[W >= 0])
+    assert not gotA[untouched].any() and not gotB[untouched].any()

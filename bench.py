@@ -225,7 +225,8 @@ def config_dict(args, extra=None):
                          % (w["doc_len"], w["topics"], w["zipf_s"]))
         c["topics"] = w["topics"]
     elif w["wsample"] != DEFAULT_WORKLOAD["wsample"] or w["vocab"] != DEFAULT_WORKLOAD["vocab"] \
-            or w["nneg"] != DEFAULT_WORKLOAD["nneg"] or w["ntokens"] != DEFAULT_WORKLOAD["ntokens"]:
+            or w["nneg"] != DEFAULT_WORKLOAD["nneg"] or w["ntokens"] != DEFAULT_WORKLOAD["ntokens"] \
+            or w["dim"] != DEFAULT_WORKLOAD["dim"]:
         c["workload"] = "configs[1] with overrides (see the fields below)"
     if extra:
         c.update(extra)
@@ -471,6 +472,7 @@ def main():
     ap.add_argument("--vocab", type=int, default=None, help="override the workload's vocabulary (profiling)")
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per minibatch (profiling)")
     ap.add_argument("--nneg", type=int, default=None, help="override the number of negatives (configs[4] uses 10)")
+    ap.add_argument("--dim", type=int, default=None, help="override the embedding dimension (a multiple of 4)")
     ap.add_argument("--wsample", type=float, default=None,
                     help="frequent-word subsampling (configs[3] and [4] use 1e-4; default: none)")
     ap.add_argument("--topics", type=int, default=None,
@@ -486,6 +488,8 @@ def main():
         WORKLOAD["ntokens"] = args.tokens
     if args.nneg:
         WORKLOAD["nneg"] = args.nneg
+    if args.dim:
+        WORKLOAD["dim"] = args.dim
     if args.wsample is not None:
         WORKLOAD["wsample"] = args.wsample
     if args.topics:

@@ -61,6 +61,13 @@ SIGNATURES = {
     "Java_edu_berkeley_bid_CUMACH_word2vecNegFilt": (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _F, _F]),
     "Java_edu_berkeley_bid_CUMACH_word2vecEvalPos": (_I, [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "Java_edu_berkeley_bid_CUMACH_word2vecEvalNeg": (_I, [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "Java_edu_berkeley_bid_CUMACH_w2vCreate": (C.c_int64, [_P, _P, _I, _I, _I, _I, _I, _F, _F, _F, _F, _F, _I, _I, _I,
+                                                           C.c_int64, _I]),
+    "Java_edu_berkeley_bid_CUMACH_w2vDestroy": (None, [_P, _P, C.c_int64]),
+    "Java_edu_berkeley_bid_CUMACH_w2vInitModel": (_I, [_P, _P, C.c_int64, _P, _P]),
+    "Java_edu_berkeley_bid_CUMACH_w2vDobatch": (_I, [_P, _P, C.c_int64, _P, _P, _P, C.c_int64, C.c_int64]),
+    "Java_edu_berkeley_bid_CUMACH_w2vEvalbatch": (C.c_double, [_P, _P, C.c_int64, _P, _P, _P, C.c_int64]),
+    "Java_edu_berkeley_bid_CUMACH_w2vLastError": (_I, [_P, _P, C.c_int64]),
     "w2v_default_opts": (None, [C.POINTER(W2VOpts)]),
     "w2v_create": (_I, [C.POINTER(W2VOpts), _I, C.POINTER(_P)]),
     "w2v_destroy": (None, [_P]),

@@ -11,6 +11,7 @@
 typedef int32_t jint;
 typedef int64_t jlong;
 typedef float jfloat;
+typedef double jdouble;
 typedef void *jobject;
 typedef jobject jclass;
 typedef void *jfieldID;

@@ -17,6 +17,8 @@
 #include "jni_min.h"
 #endif
 
+#include <cuda_runtime_api.h>
+
 #define BIDMACH_B200_NO_JNI_DECLS
 #include "../../include/bidmach_b200.h"
 
@@ -118,6 +120,114 @@ JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMACH_word2vecEvalNeg(
   return word2vecEvalNeg(nrows, ncols, nwa, nwb, (int *)device_address(env, jWA),
                          (int *)device_address(env, jWB), (float *)device_address(env, jA),
                          (float *)device_address(env, jB), (float *)device_address(env, jRetval));
+}
+
+// ---------------------------------------------------------------------------
+// Binders for the whole-minibatch extension (part 3 of the header), so that a
+// JVM host needs nothing but the matching `native` declarations in
+// edu.berkeley.bid.CUMACH:
+//
+//   public static native long   w2vCreate(int dim, int nskip, int nneg, int nreuse, int vocabSize,
+//                                         float wexpt, float wsample, float lrate, float texp, float vexp,
+//                                         int iflip, int eqPosNeg, int permute, long seed, int ncols);
+//   public static native void   w2vDestroy(long ctx);
+//   public static native int    w2vInitModel(long ctx, Pointer A, Pointer B);
+//   public static native int    w2vDobatch(long ctx, Pointer tokens, Pointer A, Pointer B, long pos, long batchId);
+//   public static native double w2vEvalbatch(long ctx, Pointer tokens, Pointer A, Pointer B, long batchId);
+//   public static native int    w2vLastError(long ctx);
+//
+// The context handle travels as a long.  Work goes to the calling thread's
+// default stream, as the five reference binders; w2vDobatch only enqueues,
+// w2vEvalbatch returns the score (NaN after an error, whose code w2vLastError
+// then reports).
+// ---------------------------------------------------------------------------
+namespace {
+struct JniCtx {
+  w2v_ctx *ctx;
+  w2v_opts opts;
+  int last_error;
+};
+void *const kPerThreadStream = (void *)cudaStreamPerThread;
+}  // namespace
+
+JNIEXPORT jlong JNICALL Java_edu_berkeley_bid_CUMACH_w2vCreate(
+    JNIEnv *env, jobject obj, jint dim, jint nskip, jint nneg, jint nreuse, jint vocabSize, jfloat wexpt,
+    jfloat wsample, jfloat lrate, jfloat texp, jfloat vexp, jint iflip, jint eqPosNeg, jint permute,
+    jlong seed, jint ncols) {
+  (void)env;
+  (void)obj;
+  JniCtx *h = new JniCtx();
+  w2v_default_opts(&h->opts);
+  h->opts.dim = dim;
+  h->opts.nskip = nskip;
+  h->opts.nneg = nneg;
+  h->opts.nreuse = nreuse;
+  h->opts.vocabSize = vocabSize;
+  h->opts.wexpt = wexpt;
+  h->opts.wsample = wsample;
+  h->opts.lrate = lrate;
+  h->opts.texp = texp;
+  h->opts.vexp = vexp;
+  h->opts.iflip = iflip;
+  h->opts.eqPosNeg = eqPosNeg;
+  h->opts.permute = permute;
+  h->opts.seed = (uint64_t)seed;
+  h->last_error = w2v_create(&h->opts, ncols, &h->ctx);
+  if (h->last_error) {
+    delete h;
+    return 0;
+  }
+  return (jlong)(intptr_t)h;
+}
+
+JNIEXPORT void JNICALL Java_edu_berkeley_bid_CUMACH_w2vDestroy(JNIEnv *env, jobject obj, jlong handle) {
+  (void)env;
+  (void)obj;
+  JniCtx *h = (JniCtx *)(intptr_t)handle;
+  if (!h) return;
+  w2v_destroy(h->ctx);
+  delete h;
+}
+
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMACH_w2vInitModel(JNIEnv *env, jobject obj, jlong handle,
+                                                                 jobject jA, jobject jB) {
+  (void)obj;
+  JniCtx *h = (JniCtx *)(intptr_t)handle;
+  if (!h) return 1;
+  return h->last_error = w2v_init_model(&h->opts, (float *)device_address(env, jA),
+                                        (float *)device_address(env, jB), kPerThreadStream);
+}
+
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMACH_w2vDobatch(JNIEnv *env, jobject obj, jlong handle,
+                                                               jobject jTokens, jobject jA, jobject jB,
+                                                               jlong pos, jlong batchId) {
+  (void)obj;
+  JniCtx *h = (JniCtx *)(intptr_t)handle;
+  if (!h) return 1;
+  return h->last_error = w2v_dobatch(h->ctx, (const int *)device_address(env, jTokens), nullptr,
+                                     (float *)device_address(env, jA), (float *)device_address(env, jB),
+                                     pos, (uint64_t)batchId, kPerThreadStream);
+}
+
+JNIEXPORT jdouble JNICALL Java_edu_berkeley_bid_CUMACH_w2vEvalbatch(JNIEnv *env, jobject obj, jlong handle,
+                                                                    jobject jTokens, jobject jA, jobject jB,
+                                                                    jlong batchId) {
+  (void)obj;
+  JniCtx *h = (JniCtx *)(intptr_t)handle;
+  double score = 0.0;
+  const double nan = __builtin_nan("");
+  if (!h) return nan;
+  h->last_error = w2v_evalbatch(h->ctx, (const int *)device_address(env, jTokens), nullptr,
+                                (const float *)device_address(env, jA), (const float *)device_address(env, jB),
+                                (uint64_t)batchId, &score, kPerThreadStream);
+  return h->last_error ? nan : score;
+}
+
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMACH_w2vLastError(JNIEnv *env, jobject obj, jlong handle) {
+  (void)env;
+  (void)obj;
+  JniCtx *h = (JniCtx *)(intptr_t)handle;
+  return h ? h->last_error : 1;
 }
 
 }  // extern "C"

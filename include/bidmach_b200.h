@@ -111,6 +111,29 @@ int Java_edu_berkeley_bid_CUMACH_word2vecEvalPos(BidmachJNIEnv *env, void *obj, 
 int Java_edu_berkeley_bid_CUMACH_word2vecEvalNeg(BidmachJNIEnv *env, void *obj, int nrows,
                                                  int ncols, int nwa, int nwb, void *jWA, void *jWB,
                                                  void *jA, void *jB, void *jRetval);
+
+/* Binders of the whole-minibatch extension (part 3), for a CUMACH that declares
+ *   native long w2vCreate(int dim, int nskip, int nneg, int nreuse, int vocabSize, float wexpt,
+ *                         float wsample, float lrate, float texp, float vexp, int iflip, int eqPosNeg,
+ *                         int permute, long seed, int ncols);            // 0 = refused
+ *   native void w2vDestroy(long ctx);
+ *   native int w2vInitModel(long ctx, Pointer A, Pointer B);
+ *   native int w2vDobatch(long ctx, Pointer tokens, Pointer A, Pointer B, long pos, long batchId);
+ *   native double w2vEvalbatch(long ctx, Pointer tokens, Pointer A, Pointer B, long batchId);  // NaN = error
+ *   native int w2vLastError(long ctx);
+ * Work goes to the calling thread's default stream, as with the five binders above. */
+int64_t Java_edu_berkeley_bid_CUMACH_w2vCreate(BidmachJNIEnv *env, void *obj, int dim, int nskip, int nneg,
+                                               int nreuse, int vocabSize, float wexpt, float wsample,
+                                               float lrate, float texp, float vexp, int iflip,
+                                               int eqPosNeg, int permute, int64_t seed, int ncols);
+void Java_edu_berkeley_bid_CUMACH_w2vDestroy(BidmachJNIEnv *env, void *obj, int64_t ctx);
+int Java_edu_berkeley_bid_CUMACH_w2vInitModel(BidmachJNIEnv *env, void *obj, int64_t ctx, void *jA,
+                                              void *jB);
+int Java_edu_berkeley_bid_CUMACH_w2vDobatch(BidmachJNIEnv *env, void *obj, int64_t ctx, void *jTokens,
+                                            void *jA, void *jB, int64_t pos, int64_t batchId);
+double Java_edu_berkeley_bid_CUMACH_w2vEvalbatch(BidmachJNIEnv *env, void *obj, int64_t ctx,
+                                                 void *jTokens, void *jA, void *jB, int64_t batchId);
+int Java_edu_berkeley_bid_CUMACH_w2vLastError(BidmachJNIEnv *env, void *obj, int64_t ctx);
 #endif
 
 /* ------------------------------------------------------------------------

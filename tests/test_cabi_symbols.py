@@ -10,7 +10,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def _declared_functions():
     text = open(os.path.join(ROOT, "include", "bidmach_b200.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    names = re.findall(r"^\s*(?:int|void|long long|int64_t|uint32_t)\s+\**(\w+)\s*\(", text, flags=re.M)
+    names = re.findall(r"^\s*(?:int|void|long long|int64_t|uint32_t|double)\s+\**(\w+)\s*\(", text, flags=re.M)
     return sorted(set(names))
 
 

@@ -115,3 +115,37 @@ def test_row_probe_leaves_the_model_unchanged():
     torch.cuda.synchronize()
     assert all(torch.equal(a, b) for a, b in zip(before, m.modelmats))
     assert lib.w2v_probe_rows(m._ctx, m.modelmats[1].data_ptr(), m.modelmats[0].data_ptr(), 7, m._stream()) == 1
+
+
+def test_jni_binders_of_the_whole_minibatch_calls():
+    """Java_edu_berkeley_bid_CUMACH_w2v*: create, initialise, train and score one minibatch
+    through the symbols a JVM would bind (null jcuda.Pointer objects cannot carry an address,
+    so the pointers go through a mock JNIEnv as in tests/test_jni_shim.py)."""
+    import ctypes as C
+
+    from bidmach_b200 import _lib
+    from test_jni_shim import MockJVM
+    lib = _lib.load()
+    jvm = MockJVM()
+    assert lib.JNI_OnLoad(jvm.vm, None) == 0x00010004
+    n, V, D = 2000, 500, 100
+    h = lib.Java_edu_berkeley_bid_CUMACH_w2vCreate(jvm.env, None, D, 5, 5, 5, V, 0.75, 1.0, 0.01, 0.5, 0.5,
+                                                   0, 0, 0, 7, n)
+    assert h != 0
+    A = torch.empty(V, D, device="cuda")
+    B = torch.empty(V, D, device="cuda")
+    toks = torch.from_numpy(_toks(n, V, seed=2, doc=37)).cuda()
+    pA, pB, pT = (jvm.pointer(x.data_ptr() - 64, 64) for x in (A, B, toks))   # nativePointer + byteOffset
+    assert lib.Java_edu_berkeley_bid_CUMACH_w2vInitModel(jvm.env, None, h, pA, pB) == 0
+    torch.cuda.synchronize()
+    assert float(A.abs().sum()) == 0.0 and float(B.abs().max()) <= 0.5 / D
+    s0 = lib.Java_edu_berkeley_bid_CUMACH_w2vEvalbatch(jvm.env, None, h, pT, pA, pB, 1)
+    assert s0 == pytest.approx(2 * np.log(0.5), abs=2e-3)
+    for k in range(8):
+        assert lib.Java_edu_berkeley_bid_CUMACH_w2vDobatch(jvm.env, None, h, pT, pA, pB, n, 2 + k) == 0
+    s1 = lib.Java_edu_berkeley_bid_CUMACH_w2vEvalbatch(jvm.env, None, h, pT, pA, pB, 20)
+    assert s1 > s0 + 0.05 and lib.Java_edu_berkeley_bid_CUMACH_w2vLastError(jvm.env, None, h) == 0
+    lib.Java_edu_berkeley_bid_CUMACH_w2vDestroy(jvm.env, None, h)
+    # unsupported options are refused with a null handle
+    assert lib.Java_edu_berkeley_bid_CUMACH_w2vCreate(jvm.env, None, D, 5, 7, 3, V, 0.75, 1.0, 0.01, 0.5, 0.5,
+                                                      0, 0, 0, 7, n) == 0

@@ -18,8 +18,20 @@ scaling) and both matrices are averaged with an all-reduce every
 Prints ONE JSON line (rank 0).  `value` is measured with the minibatches
 already in device memory; `e2e` is the same loop through the host-buffer entry
 point (pinned host minibatch -> device copy -> update -> pair count back).
+`roofline` describes the negative-update kernel: algorithmic bytes over its
+measured duration against the measured HBM copy peak, the DRAM traffic of an
+ncu capture, and `memory_bound`: what the kernel's atomic row additions and
+its row reads take on their own, on the same columns (w2v_probe_rows).
 `--impl reference` times the reference's own CPU kernels (compiled from its C
 source into oracle/_ref) with all host cores on a bounded sample per step.
+
+Other switches: `--mode eval` times the scoring path (configs[2]);
+`--vocab / --tokens / --dim / --nneg / --wsample / --topics` change the
+workload (configs[3] and [4]: `--topics 1000 --wsample 1e-4`,
+`--topics 3000 --wsample 1e-4 --vocab 3000000 --nneg 10`); `--sort-permute`
+shuffles the pair list by sorting random keys as the reference's GPU branch;
+`--head-sync` / `--overlap-sync` select the reference's head-only averaging
+schedule or an exchange overlapped with the next minibatch.
 """
 from __future__ import annotations
 

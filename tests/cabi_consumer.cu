@@ -72,6 +72,47 @@ int main(int argc, char **argv) {
   fwrite(A.data(), 4, A.size(), g);
   fwrite(B.data(), 4, B.size(), g);
   fclose(g);
+
+  // the whole-minibatch calls from plain C++: a context, a model, a pinned host minibatch
+  // trained on eight times and scored before and after
+  {
+    w2v_opts o;
+    w2v_default_opts(&o);
+    o.dim = 100;
+    o.vocabSize = 500;
+    o.wsample = 1.0f;
+    o.lrate = 0.01f;
+    o.seed = 5;
+    const int n = 3000;
+    w2v_ctx *ctx = nullptr;
+    if (w2v_create(&o, n, &ctx) != 0) return 7;
+    float *mA, *mB;
+    CK(cudaMalloc(&mA, sizeof(float) * o.dim * o.vocabSize));
+    CK(cudaMalloc(&mB, sizeof(float) * o.dim * o.vocabSize));
+    if (w2v_init_model(&o, mA, mB, nullptr) != 0) return 8;
+    int *toks;
+    CK(cudaMallocHost(&toks, sizeof(int) * 2 * n));
+    unsigned x = 12345u;
+    for (int i = 0; i < n; i++) {
+      x = x * 1664525u + 1013904223u;
+      toks[2 * i] = (int)((x >> 8) % (unsigned)o.vocabSize);
+      toks[2 * i + 1] = i / 37;
+    }
+    double before = 0, after = 0;
+    if (w2v_evalbatch_host(ctx, toks, mA, mB, 1, &before, nullptr) != 0) return 9;
+    long long pairs = 0;
+    for (int k = 0; k < 8; k++) {
+      int64_t np = 0;
+      if (w2v_dobatch_host(ctx, toks, mA, mB, n, 2 + k, &np, nullptr) != 0) return 10;
+      pairs = np;
+    }
+    if (w2v_evalbatch_host(ctx, toks, mA, mB, 20, &after, nullptr) != 0) return 11;
+    printf("minibatch pairs=%lld score %.6f -> %.6f\n", pairs, before, after);
+    w2v_destroy(ctx);
+    CK(cudaFreeHost(toks));
+    CK(cudaFree(mA));
+    CK(cudaFree(mB));
+  }
   printf("ok launches=%lld\n", w2v_launch_count());
   return 0;
 }

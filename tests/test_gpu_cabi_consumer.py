@@ -38,7 +38,13 @@ def test_c_program_links_and_matches_oracle(oracle, tmp_path):
     res = subprocess.run([str(exe), str(inp), str(out)], capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stderr + res.stdout
     assert "word2vec unsupport size combination 3 3" in res.stdout      # the reference's message
-    assert res.stdout.strip().splitlines()[-1].startswith("ok launches=")
+    lines = res.stdout.strip().splitlines()
+    assert lines[-1].startswith("ok launches=")
+    # the whole-minibatch calls: training on a minibatch raises its own score from 2*log(1/2)
+    import re
+    m = re.match(r"minibatch pairs=(\d+) score (-?[\d.]+) -> (-?[\d.]+)", lines[-2])
+    assert m and int(m.group(1)) > 10000
+    assert abs(float(m.group(2)) - 2 * np.log(0.5)) < 2e-3 and float(m.group(3)) > float(m.group(2)) + 0.05
     raw = np.fromfile(out, np.float32)
     scores, gA, gB = raw[:2], raw[2:2 + vocab * dim].reshape(vocab, dim), raw[2 + vocab * dim:].reshape(vocab, dim)
     want = oracle.word2vecEvalNeg(dim, ncols, nwa, nwb, WA, WB, A, B)

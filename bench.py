@@ -218,6 +218,30 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# dram__bytes_read.sum per launch of the negative scoring kernel on the default workload
+# (one-pass ncu capture; see profiles/scoring_kernels_zipf_vocab1M_dim300.md)
+EVALNEG_DRAM_TRAFFIC_BYTES = 7.07e9
+
+
+def eval_roofline(w, groups, row, evalneg_ms, bounds):
+    """The negative scoring kernel against the HBM copy peak: rows read (algorithmic bytes)
+    over its measured duration, the DRAM bytes of the ncu capture, and what reading the same
+    rows and nothing else takes (ms per launch)."""
+    peak, peak_kind = measured_peak_gbs()
+    nbytes = groups * (w["nneg"] + w["nreuse"]) * row
+    achieved = nbytes / (evalneg_ms * 1e-3) / 1e9 if evalneg_ms > 0 else None
+    default_shape = all(w[k] == DEFAULT_WORKLOAD[k] for k in ("vocab", "dim", "ntokens", "nneg", "nreuse", "nskip"))
+    traffic = EVALNEG_DRAM_TRAFFIC_BYTES if default_shape else None
+    return {"bound": "hbm", "kernel": "neg_update_staged_kernel<%d,%d,%d,true>" % (
+                w["nneg"], w["nreuse"], (w["dim"] // 4 + 31) // 32),
+            "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+            "frac": (achieved / peak) if achieved else None, "traffic": traffic,
+            "algorithmic_bytes_per_launch": nbytes, "avg_launch_ms": evalneg_ms,
+            "dram_frac": (traffic / (evalneg_ms * 1e-3) / 1e9 / peak) if (traffic and evalneg_ms > 0) else None,
+            "memory_bound": ({"gather_only_ms": bounds[1],
+                              "kernel_over_gather_only": evalneg_ms / bounds[1]} if bounds else None)}
+
+
 def config_dict(args, extra=None):
     w = WORKLOAD
     c = {"workload": "configs[1]: single-minibatch SGNS update, vocab 1M, dim 300, 1M-token "
@@ -396,8 +420,7 @@ def run_ours(args):
                            "evalpos_ms": tm.evalpos_ms / nb, "evalneg_ms": tm.evalneg_ms / nb,
                            "evalneg_algorithmic_gbs": eg * (w["nneg"] + w["nreuse"]) * row / (tm.evalneg_ms / nb) / 1e6,
                            "evalpos_algorithmic_gbs": (N + ep) * row / (tm.evalpos_ms / nb) / 1e6},
-                # reading the negative columns' rows and nothing else, same columns (ms per launch)
-                "memory_bound": {"gather_only_ms": bounds[1]} if bounds else None,
+                "roofline": eval_roofline(w, eg, row, tm.evalneg_ms / nb, bounds),
                 "clocks": clocks}
         print(json.dumps(line), flush=True)
         if world > 1:

@@ -1432,7 +1432,9 @@ int row_probe_async(int dim, int ncols, const int *ncols_dev, int nwa, int nwb, 
   if (!vector_ok(dim, A, B) || nwa + nwb > 32 || mode < 0 || mode > 1) return 1;
   const int nr = (dim / 4 + 31) / 32;
   if (nr > 10) return 1;
-  const int grid = device_sm_count() * 4;
+  // the scatter takes the same time with 16 to 128 warps per SM (4.02 - 4.16 ms on the benchmark
+  // workload); the gather needs the many warps
+  const int grid = device_sm_count() * 8;
   if (mode == 0) {
     W2V_NR_SWITCH(nr, (row_probe_kernel<NR, 0><<<grid, 512, 0, stream>>>(dim, ncols, ncols_dev, nwa, nwb, WA,
                                                                        WB, A, B, hot, sink)));

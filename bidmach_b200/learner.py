@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import dataclasses
 import math
+import time
 
 import numpy as np
 
@@ -61,23 +62,35 @@ class LearnerOpts:
     syncStep: int = 2
     overlapSync: bool = False   # not in the reference: exchange beside the next minibatch
     headSync: bool = False      # the reference's schedule: syncs average a growing head of the vocabulary
+    pstep: float = 0.01         # progress between two log lines (Learner.Opts.pstep)
+    verbose: bool = False       # print the reference's progress lines
 
 
 def _scala_mod(a: int, b: int) -> int:
     return int(math.fmod(a, b))
 
 
+def _summary(scores, start: int) -> float:
+    """Learner.scoreSummary without cumScore: the mean of the scores since ``start``."""
+    part = scores[start:]
+    return float(np.mean(part)) if part else float("nan")
+
+
 class Learner:
     """Single-GPU loop, ``Learner.nextPass`` (Learner.scala:173-252): minibatch
     ``istep`` only scores when ``(istep - 1) % evalStep == 0`` or it is the last
-    one of the pass (and not the first); every other minibatch trains.  ``here``
-    advances by batchSize per minibatch and drives the learning-rate decay."""
+    one of the pass (and not the first); every other minibatch trains, and the
+    one with ``(istep - 1) % evalStep == 1`` is scored after it was trained on
+    (the training score, ``trainlist``).  ``here`` advances by batchSize per
+    minibatch and drives the learning-rate decay."""
 
     def __init__(self, datasource: MatSource, model: Word2Vec, opts: LearnerOpts | None = None):
         self.datasource, self.model = datasource, model
         self.opts = opts or LearnerOpts()
         self.reslist: list[float] = []
         self.samplist: list[int] = []
+        self.trainlist: list[float] = []
+        self.trainsamplist: list[int] = []
         self.here = 0
         self.ipass = 0
         self.nsamps = 0
@@ -96,6 +109,8 @@ class Learner:
             self.init()
         self.here, self.ipass, self.nsamps = 0, 0, 0
         self.reslist, self.samplist = [], []
+        self.trainlist, self.trainsamplist = [], []
+        self._t0 = time.time()
         while self.ipass < self.opts.npasses:
             self.nextPass()
         return self
@@ -104,10 +119,14 @@ class Learner:
         ds, o = self.datasource, self.opts
         ds.reset()
         istep = 0
+        lastp, lasti, lastti = 0.0, len(self.reslist), len(self.trainlist)
+        if o.verbose:
+            print("pass=%2d" % self.ipass)
         while ds.hasNext():
             mats = ds.next()
             self.nsamps += mats[0].shape[0]
             self.here += ds.batchSize
+            dsp = ds.progress()
             if _scala_mod(istep - 1, o.evalStep) == 0 or (istep > 0 and not ds.hasNext()):
                 if o.updateAll:
                     self.model.dobatchg(mats, self.ipass, self.here)
@@ -117,8 +136,19 @@ class Learner:
             else:
                 self.model.dobatchg(mats, self.ipass, self.here)
                 self._after_train_step(istep)
+                if _scala_mod(istep - 1, o.evalStep) == 1:      # Learner.scala:217-222
+                    self.trainlist.append(self.model.evalbatchg(mats, self.ipass, self.here))
+                    self.trainsamplist.append(self.here)
             self._after_minibatch()
             istep += 1
+            if o.verbose and ((dsp > lastp + o.pstep and len(self.reslist) > lasti) or not ds.hasNext()):
+                # the reference's line (Learner.scala:228-239) without its flop and memory columns
+                lastp = (dsp - math.fmod(dsp, o.pstep)) if ds.hasNext() else 1.0
+                secs = max(1e-9, time.time() - self._t0)
+                print("%6.2f%%, train=%6.5f, val=%6.5f, sec=%2.0f, sam/s=%2.0f" % (
+                    100.0 * lastp, _summary(self.trainlist, lastti), _summary(self.reslist, lasti), secs,
+                    self.nsamps / secs))
+                lasti, lastti = len(self.reslist), len(self.trainlist)
         self.ipass += 1
 
     def predict(self, datasource: MatSource) -> list[float]:

@@ -64,11 +64,13 @@ def test_learner_replays_the_reference_schedule():
     m = _FakeModel()
     Learner(MatSource(toks, 100), m, LearnerOpts(npasses=2, evalStep=11)).train()
     kinds = [c[0] for c in m.calls]
-    one_pass = ["train", "eval"] + ["train"] * 10 + ["eval"] + ["train"] + ["eval"]
+    # istep 0 trains, 1 scores, 2 trains and is scored afterwards (the training score,
+    # (istep - 1) % evalStep == 1), 3..11 train, 12 scores, 13 trains + training score, 14 (last) scores
+    one_pass = ["train", "eval", "train", "eval"] + ["train"] * 9 + ["eval", "train", "eval", "eval"]
     assert kinds == one_pass * 2
-    assert [c[1] for c in m.calls][:3] == [100, 200, 300]          # `here` advances by batchSize
-    assert m.calls[14][2] == 50                                      # the short last batch still arrives
-    assert [c[1] for c in m.calls][15] == 1600                       # and `here` keeps counting in pass 2
+    assert [c[1] for c in m.calls][:4] == [100, 200, 300, 300]      # `here` advances by batchSize
+    assert m.calls[16][2] == 50                                      # the short last batch still arrives
+    assert [c[1] for c in m.calls][17] == 1600                       # and `here` keeps counting in pass 2
 
 
 def test_corpora_are_seeded_and_ranked():
@@ -175,8 +177,9 @@ def test_parlearner_syncs_every_syncstep_and_replicas_agree():
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    # 21 batches -> 20 usable, 10 per rank; istep 1 and the last are eval-only: 8 train steps, 4 syncs
-    assert got[0][1] == got[1][1] == 4 and got[0][2] == got[1][2] == 10
+    # 21 batches -> 20 usable, 10 per rank; istep 1 and the last are eval-only: 8 train steps, 4 syncs;
+    # istep 2 is also scored after training (the training score): 11 model calls
+    assert got[0][1] == got[1][1] == 4 and got[0][2] == got[1][2] == 11
     assert torch.equal(got[0][3], got[1][3])
 
 
@@ -207,8 +210,8 @@ def test_parlearner_overlapped_exchange_order():
     m = M()
     toks = np.zeros((700, 2), np.int32)
     ParLearner(MatSource(toks, 100), m, LearnerOpts(npasses=1, evalStep=11, syncStep=2, overlapSync=True)).train()
-    # minibatches: train, eval, train, train, train, train, eval(last)
-    assert m.log == ["train", "finish", "eval", "train", "start", "train", "finish", "train", "start",
+    # minibatches: train, eval, train (+ its training score), train, train, train, eval(last)
+    assert m.log == ["train", "finish", "eval", "train", "start", "eval", "train", "finish", "train", "start",
                      "train", "finish", "eval", "finish"]
 
 

@@ -62,6 +62,10 @@ class LearnerOpts:
     syncStep: int = 2
     overlapSync: bool = False   # not in the reference: exchange beside the next minibatch
     headSync: bool = False      # the reference's schedule: syncs average a growing head of the vocabulary
+    checkPointFile: str | None = None   # e.g. "ckpt/w2v%03d/": a checkpoint directory per number
+    checkPointInterval: float = 0.0     # in passes over the data (Learner.scala:1074-1077)
+    keepCheckPoints: int = 2
+    nextCheckPoint: int = 0
     pstep: float = 0.01         # progress between two log lines (Learner.Opts.pstep)
     verbose: bool = False       # print the reference's progress lines
 
@@ -111,9 +115,32 @@ class Learner:
         self.reslist, self.samplist = [], []
         self.trainlist, self.trainsamplist = [], []
         self._t0 = time.time()
+        self._next_ckpt = self.opts.nextCheckPoint
         while self.ipass < self.opts.npasses:
             self.nextPass()
+        if self.opts.checkPointFile is not None:        # Learner.wrapUp (Learner.scala:258-259)
+            self.model.save(self.opts.checkPointFile % self._next_ckpt)
         return self
+
+    def loadCheckPoint(self, checkPointNumber: int = -1):
+        """Learner.loadCheckPoint (Learner.scala:397-425): loads the given checkpoint, or
+        the last one of the consecutive run found on disk, and continues the numbering."""
+        import os
+        o = self.opts
+        lasti, found = -1, False
+        while lasti < 100000:
+            lasti += 1
+            if os.path.exists((o.checkPointFile % lasti) + "options.json"):
+                found = True
+            elif found:
+                break
+        lasti -= 1
+        if not found:
+            print("loadCheckPoint: didnt find any checkpoint files")
+            return False
+        self.model.load(o.checkPointFile % (checkPointNumber if checkPointNumber >= 0 else lasti))
+        o.nextCheckPoint = lasti + 1
+        return True
 
     def nextPass(self):
         ds, o = self.datasource, self.opts
@@ -149,6 +176,14 @@ class Learner:
                     100.0 * lastp, _summary(self.trainlist, lastti), _summary(self.reslist, lasti), secs,
                     self.nsamps / secs))
                 lasti, lastti = len(self.reslist), len(self.trainlist)
+            if o.checkPointFile is not None and \
+                    self.ipass + dsp > o.checkPointInterval * (1 + self._next_ckpt - o.nextCheckPoint):
+                # Learner.scala:242-249: save, then drop the checkpoint keepCheckPoints back
+                self.model.save(o.checkPointFile % self._next_ckpt)
+                old = self._next_ckpt - o.keepCheckPoints
+                self._next_ckpt += 1
+                if o.keepCheckPoints > 0 and old >= 0:
+                    self.model.delete(o.checkPointFile % old)
         self.ipass += 1
 
     def predict(self, datasource: MatSource) -> list[float]:

@@ -139,3 +139,20 @@ def loadModel(fname: str):
         mats.append(matio.loadMat(fname + "modelmat%02d.lz4" % n).T)
         n += 1
     return opts, mats
+
+
+def deleteModel(fname: str) -> None:
+    """Model.delete (models/Model.scala:266-280): the files ``saveModel`` wrote, then the
+    directory if that leaves it empty."""
+    import os
+    names = [fname + "options.json", fname + "options.ser"]
+    n = 0
+    while os.path.exists(fname + "modelmat%02d.lz4" % n):
+        names.append(fname + "modelmat%02d.lz4" % n)
+        n += 1
+    for f in names:
+        if os.path.exists(f):
+            os.remove(f)
+    parent = os.path.dirname(fname + "options.json")
+    if parent and os.path.isdir(parent) and not os.listdir(parent):
+        os.rmdir(parent)

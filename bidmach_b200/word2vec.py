@@ -383,6 +383,10 @@ class Word2Vec:
         ``modelmat00.lz4`` / ``modelmat01.lz4`` under ``fname``."""
         modelio.saveModel(fname, dataclasses.asdict(self.opts), self.modelmats)
 
+    def delete(self, fname: str):
+        """Model.delete (models/Model.scala:266-280): removes a checkpoint written by ``save``."""
+        modelio.deleteModel(fname)
+
     def load(self, fname: str):
         """Model.load(fname, useJson = true) (models/Model.scala:282-315): the
         options of the checkpoint replace this model's, the matrices are copied

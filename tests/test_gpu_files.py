@@ -64,3 +64,24 @@ def test_checkpoint_round_trip_keeps_the_score(tmp_path):
     m3.load(d)
     m3._batches = m._batches - 1                             # same draw counter as the call above
     assert m3.evalbatch([dt], 0, n) == pytest.approx(s1, rel=1e-6)
+
+
+def test_learner_checkpoints_and_resumes(tmp_path):
+    """checkPointFile / checkPointInterval / keepCheckPoints and loadCheckPoint
+    (Learner.scala:242-249, 258-259, 397-425) with real checkpoint directories."""
+    import os
+
+    from bidmach_b200 import Learner, MatSource, Word2Vec
+    from bidmach_b200.corpus import zipf_corpus
+    from bidmach_b200.learner import LearnerOpts
+    toks = zipf_corpus(2000, 16_000, 1.0, seed=9, doc_len=40)
+    pat = str(tmp_path / "w2v%03d") + "/"
+    lo = LearnerOpts(npasses=1, checkPointFile=pat, checkPointInterval=0.3, keepCheckPoints=1)
+    a = Learner(MatSource(toks, 2000), Word2Vec(_opts()), lo).train()
+    kept = sorted(p.name for p in tmp_path.iterdir())
+    assert kept == ["w2v002", "w2v003"]                       # 0 and 1 were dropped, 3 is the final one
+    assert sorted(os.listdir(tmp_path / "w2v003")) == ["modelmat00.lz4", "modelmat01.lz4", "options.json"]
+    b = Learner(MatSource(toks, 2000), Word2Vec(_opts()), LearnerOpts(npasses=1, checkPointFile=pat))
+    b.init()
+    assert b.loadCheckPoint() and b.opts.nextCheckPoint == 4
+    assert all(torch.equal(x, y) for x, y in zip(a.model.modelmats, b.model.modelmats))

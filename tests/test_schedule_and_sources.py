@@ -302,3 +302,38 @@ def test_keyed_permutation_known_answers(oracle):
                                                                    978, 308, 64, 102]
     assert oracle.library_permutation(0x123456789ABCDEF0, 7, 5_985_887)[:8].tolist() == [
         5068001, 3494612, 1389536, 5787168, 2465857, 5956610, 135992, 4957205]
+
+
+def test_learner_checkpoints_as_the_reference(tmp_path):
+    """Learner.scala:242-249, 258-259: a checkpoint whenever ipass + progress passes the next
+    multiple of checkPointInterval, the one keepCheckPoints back deleted, a last one at the end."""
+    from bidmach_b200.learner import Learner, LearnerOpts, MatSource
+
+    class M(_FakeModel):
+        def __init__(self):
+            super().__init__()
+            self.saved, self.deleted = [], []
+
+        def save(self, f):
+            self.saved.append(f)
+
+        def delete(self, f):
+            self.deleted.append(f)
+
+    m = M()
+    toks = np.zeros((1000, 2), np.int32)
+    pat = str(tmp_path / "ck%02d") + "/"
+    Learner(MatSource(toks, 100), m, LearnerOpts(npasses=1, checkPointFile=pat, checkPointInterval=0.25,
+                                                 keepCheckPoints=2)).train()
+    # progress 0.1, 0.2, ... 1.0: checkpoints when it passes 0.25, 0.5, 0.75, then the final one
+    assert m.saved == [pat % k for k in range(4)]
+    assert m.deleted == [pat % 0]
+
+
+def test_checkpoint_files_can_be_deleted(tmp_path):
+    from bidmach_b200 import modelio
+    d = str(tmp_path / "ck") + "/"
+    modelio.saveModel(d, {"dim": 4}, [np.zeros((3, 4), np.float32), np.ones((3, 4), np.float32)])
+    assert (tmp_path / "ck" / "modelmat01.lz4").exists()
+    modelio.deleteModel(d)
+    assert not (tmp_path / "ck").exists()

@@ -9,6 +9,14 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 
+def _free_port() -> int:
+    """A TCP port nobody listens on right now, for a gloo rendezvous on 127.0.0.1."""
+    import socket
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]
+
+
 def test_eval_schedule_matches_learner_nextpass(oracle):
     from bidmach_b200.learner import _scala_mod
     # (istep - 1) % evalStep == 0 with Scala's truncated remainder: 1, 12, 23, ...
@@ -122,7 +130,7 @@ def _avg_worker(rank, world, port, q):
 
 
 def test_merge_model_averages_both_matrices_over_a_gloo_group():
-    world, port = 2, 29511 + os.getpid() % 500
+    world, port = 2, _free_port()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_avg_worker, args=(r, world, port, q)) for r in range(world)]
@@ -167,7 +175,7 @@ def _par_worker(rank, world, port, q):
 
 
 def test_parlearner_syncs_every_syncstep_and_replicas_agree():
-    world, port = 2, 29011 + os.getpid() % 500
+    world, port = 2, _free_port()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_par_worker, args=(r, world, port, q)) for r in range(world)]
@@ -247,7 +255,7 @@ def _head_worker(rank, world, port, q):
 
 
 def test_merge_model_with_istep_averages_only_the_head_rows():
-    world, port = 2, 30011 + os.getpid() % 500
+    world, port = 2, _free_port()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_head_worker, args=(r, world, port, q)) for r in range(world)]

@@ -68,6 +68,7 @@ class LearnerOpts:
     nextCheckPoint: int = 0
     pstep: float = 0.01         # progress between two log lines (Learner.Opts.pstep)
     verbose: bool = False       # print the reference's progress lines
+    logFile: str | None = None  # append one JSON object per progress line (pct, train, val, sec, words_per_s)
 
 
 def _scala_mod(a: int, b: int) -> int:
@@ -168,13 +169,22 @@ class Learner:
                     self.trainsamplist.append(self.here)
             self._after_minibatch()
             istep += 1
-            if o.verbose and ((dsp > lastp + o.pstep and len(self.reslist) > lasti) or not ds.hasNext()):
+            if (o.verbose or o.logFile) and \
+                    ((dsp > lastp + o.pstep and len(self.reslist) > lasti) or not ds.hasNext()):
                 # the reference's line (Learner.scala:228-239) without its flop and memory columns
                 lastp = (dsp - math.fmod(dsp, o.pstep)) if ds.hasNext() else 1.0
                 secs = max(1e-9, time.time() - self._t0)
-                print("%6.2f%%, train=%6.5f, val=%6.5f, sec=%2.0f, sam/s=%2.0f" % (
-                    100.0 * lastp, _summary(self.trainlist, lastti), _summary(self.reslist, lasti), secs,
-                    self.nsamps / secs))
+                tr, va = _summary(self.trainlist, lastti), _summary(self.reslist, lasti)
+                if o.verbose:
+                    print("%6.2f%%, train=%6.5f, val=%6.5f, sec=%2.0f, sam/s=%2.0f" % (
+                        100.0 * lastp, tr, va, secs, self.nsamps / secs))
+                if o.logFile:
+                    import json
+                    with open(o.logFile, "a") as f:
+                        f.write(json.dumps({"pass": self.ipass, "pct": 100.0 * lastp,
+                                            "train": None if math.isnan(tr) else tr,
+                                            "val": None if math.isnan(va) else va, "sec": secs,
+                                            "words_per_s": self.nsamps / secs, "here": self.here}) + "\n")
                 lasti, lastti = len(self.reslist), len(self.trainlist)
             if o.checkPointFile is not None and \
                     self.ipass + dsp > o.checkPointInterval * (1 + self._next_ckpt - o.nextCheckPoint):

@@ -345,3 +345,16 @@ def test_checkpoint_files_can_be_deleted(tmp_path):
     assert (tmp_path / "ck" / "modelmat01.lz4").exists()
     modelio.deleteModel(d)
     assert not (tmp_path / "ck").exists()
+
+
+def test_learner_progress_log(tmp_path):
+    """One JSON object per progress line: the fields of the reference's log line."""
+    import json
+
+    from bidmach_b200.learner import Learner, LearnerOpts, MatSource
+    log = tmp_path / "progress.jsonl"
+    toks = np.zeros((3000, 2), np.int32)
+    Learner(MatSource(toks, 100), _FakeModel(), LearnerOpts(npasses=1, pstep=0.25, logFile=str(log))).train()
+    rows = [json.loads(l) for l in open(log)]
+    assert [round(r["pct"]) for r in rows] == [25, 50, 75, 100]
+    assert all(r["val"] == -1.0 and r["words_per_s"] > 0 and r["pass"] == 0 for r in rows)

@@ -508,6 +508,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per minibatch (profiling)")
     ap.add_argument("--nneg", type=int, default=None, help="override the number of negatives (configs[4] uses 10)")
     ap.add_argument("--dim", type=int, default=None, help="override the embedding dimension (a multiple of 4)")
+    ap.add_argument("--lrate", type=float, default=None, help="override the learning rate (default 1e-3)")
     ap.add_argument("--wsample", type=float, default=None,
                     help="frequent-word subsampling (configs[3] and [4] use 1e-4; default: none)")
     ap.add_argument("--topics", type=int, default=None,
@@ -525,6 +526,8 @@ def main():
         WORKLOAD["nneg"] = args.nneg
     if args.dim:
         WORKLOAD["dim"] = args.dim
+    if args.lrate is not None:
+        WORKLOAD["lrate"] = args.lrate
     if args.wsample is not None:
         WORKLOAD["wsample"] = args.wsample
     if args.topics:

@@ -106,34 +106,44 @@ __global__ void words_bounds_kernel(int ncols, const int *__restrict__ tokens, i
                                     int nskip, float salpha, const float *__restrict__ usample,
                                     const float *__restrict__ uwindow, Rng rng,
                                     int *__restrict__ words, int *__restrict__ lb,
-                                    int *__restrict__ ub) {
+                                    int *__restrict__ ub, int *__restrict__ stats) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= ncols) return;
-  const int srow = 1 - wrow;
-  const int id = tokens[2 * i + wrow];
-  const int sid = tokens[2 * i + srow];
-  float u1, u2;
-  if (usample == nullptr || uwindow == nullptr) {
-    PhiloxOut r = philox4x32_10((uint32_t)i, 0u, kStreamSampleWindow, rng.batch, rng.k0, rng.k1);
-    u1 = u01(r.v[0]);
-    u2 = u01(r.v[1]);
+  bool good = false;
+  int id = -1;
+  if (i < ncols) {
+    const int srow = 1 - wrow;
+    id = tokens[2 * i + wrow];
+    const int sid = tokens[2 * i + srow];
+    float u1, u2;
+    if (usample == nullptr || uwindow == nullptr) {
+      PhiloxOut r = philox4x32_10((uint32_t)i, 0u, kStreamSampleWindow, rng.batch, rng.k0, rng.k1);
+      u1 = u01(r.v[0]);
+      u2 = u01(r.v[1]);
+    }
+    if (usample) u1 = usample[i];
+    if (uwindow) u2 = uwindow[i];
+
+    const float x = __fmul_rn((float)(id + 1), salpha);
+    const float thr = __fadd_rn(__fsqrt_rn(x), x);
+    good = (id < vocab) && (u1 < thr);
+    words[i] = good ? id : -1;
+
+    int ubr = (int)__fmul_rn(u2, (float)nskip) + 1;
+    ubr = min(ubr, nskip);
+    int back = 0;
+    while (back < nskip && i - back - 1 >= 0 && tokens[2 * (i - back - 1) + srow] == sid) back++;
+    int fwd = 0;
+    while (fwd < nskip && i + fwd + 1 < ncols && tokens[2 * (i + fwd + 1) + srow] == sid) fwd++;
+    lb[i] = max(-ubr, -back);
+    ub[i] = min(ubr, fwd);
   }
-  if (usample) u1 = usample[i];
-  if (uwindow) u2 = uwindow[i];
-
-  const float x = __fmul_rn((float)(id + 1), salpha);
-  const float thr = __fadd_rn(__fsqrt_rn(x), x);
-  const bool good = (id < vocab) && (u1 < thr);
-  words[i] = good ? id : -1;
-
-  int ubr = (int)__fmul_rn(u2, (float)nskip) + 1;
-  ubr = min(ubr, nskip);
-  int back = 0;
-  while (back < nskip && i - back - 1 >= 0 && tokens[2 * (i - back - 1) + srow] == sid) back++;
-  int fwd = 0;
-  while (fwd < nskip && i + fwd + 1 < ncols && tokens[2 * (i + fwd + 1) + srow] == sid) fwd++;
-  lb[i] = max(-ubr, -back);
-  ub[i] = min(ubr, fwd);
+  // kept tokens, and kept tokens of the most frequent word (id 0): the update kernels
+  // derive their folding period from this share; one pair of atomics per block
+  const int k = __syncthreads_count(good), z = __syncthreads_count(good && id == 0);
+  if (threadIdx.x == 0) {
+    if (k) atomicAdd(&stats[0], k);
+    if (z) atomicAdd(&stats[1], z);
+  }
 }
 
 __global__ void count_pairs_kernel(int ncols, const int *__restrict__ words,
@@ -485,6 +495,7 @@ int w2v_create(const w2v_opts *opts, int ncols, w2v_ctx **out) {
     if (e == cudaSuccess) e = cudaMemset(c->hot_buf, 0, w2v::hot_rows_bytes());
   }
   c->hot = w2v::hot_rows_at(c->hot_buf, w2v::hot_levels_default());
+  c->hot.stats = nullptr;   // set once the counts buffer exists
   if (e == cudaSuccess) e = cudaMallocHost(&c->counts_host, 256);
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_counts, cudaEventDisableTiming);
   if (e == cudaSuccess) e = cudaMallocHost(&c->retvals_host, 256);
@@ -499,6 +510,7 @@ int w2v_create(const w2v_opts *opts, int ncols, w2v_ctx **out) {
     w2v_destroy(c);
     return (int)e;
   }
+  c->hot.stats = c->counts + 8;
   *out = c;
   return 0;
 }
@@ -559,8 +571,10 @@ int w2v_wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64_t 
   if (c->timing_on) harvest(c, c->slot);
   c->ev_state[c->slot] = 0;
   mark(c, 0, stream);
+  W2V_CHECK(cudaMemsetAsync(c->counts + 8, 0, 2 * sizeof(int), stream));   // the hot-word statistics
   w2v::words_bounds_kernel<<<blocks, threads, 0, stream>>>(
-      n, tokens, o.iflip ? 1 : 0, o.vocabSize, o.nskip, c->salpha, us, uw, rng, c->words, c->lb, c->ub);
+      n, tokens, o.iflip ? 1 : 0, o.vocabSize, o.nskip, c->salpha, us, uw, rng, c->words, c->lb, c->ub,
+      c->counts + 8);
   w2v::count_pairs_kernel<<<blocks, threads, 0, stream>>>(n, c->words, c->lb, c->ub, c->cnt);
   size_t tmp = c->cub_tmp_bytes;
   W2V_CHECK(cub::DeviceScan::ExclusiveSum(c->cub_tmp, tmp, c->cnt, c->off, n, stream));

@@ -22,6 +22,10 @@ struct HotRows {
   int limit;
   int rmax;        // replicas of id 0 (a power of two); level L ids have rmax >> L
   int fold_every;  // in-kernel folding period (0 = only the fold kernel folds)
+  // Optional: {kept tokens, kept tokens of word 0} of the minibatch, on the device.  With
+  // them the kernels shorten the folding period when the text is dense and the rate high
+  // (see fold_period in w2v_kernels.cu); null = fold_every as it stands.
+  const int *stats;
 };
 size_t hot_rows_bytes();
 int hot_levels_default();

@@ -100,6 +100,28 @@ __device__ __forceinline__ float *update_target(float *M, float *shadow, const H
   return M + (int64_t)w * dim;
 }
 
+// Folding period for this launch.  Updates to a hot row sit in its replicas until
+// the next fold, and everything computed meanwhile uses the row without them.  If the
+// most frequent word takes a share p0 of the text, `per_unit` updates of it arrive per
+// unit of work (column / position), the replica rows are folded round robin (`cycled` of
+// them) and each update moves the row by about `rate`, then fold_every units between a
+// warp's folds leave per_unit * p0 * cycled * fold_every * rate worth of updates unseen.
+// Measured on unsubsampled Zipf(1.07) text: training is as stable as with plain atomics
+// while that product stays near 0.1 and diverges from about 0.4; at the reference's
+// default subsampling (p0 about 0.01) the configured period already satisfies it.
+__device__ __forceinline__ int fold_period(const HotRows &hot, float rate, float per_unit) {
+  int fe = hot.fold_every;
+  if (fe > 0 && hot.stats != nullptr) {
+    const float kept = (float)max(1, hot.stats[0]);
+    const float p0 = (float)hot.stats[1] / kept;
+    const int levels = 31 - __clz(hot.limit);
+    const float cycled = 2.0f * (float)(hot.rmax * levels);
+    const float unseen_per_fold = per_unit * p0 * cycled * fabsf(rate);
+    if (unseen_per_fold * (float)fe > 0.1f) fe = max(4, (int)(0.1f / unseen_per_fold));
+  }
+  return fe;
+}
+
 template <int NR>
 __device__ __forceinline__ void row_red_to(float *p, int nvec, int lane, const Row<NR> &r) {
 #pragma unroll
@@ -306,7 +328,9 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
       }
     }
   };
-  int until_fold = 2 * hot.fold_every;
+  // about six pairs per position; the rate of the positive update is five times the negative one's
+  const int fold_every = 2 * fold_period(hot, lrate, 6.0f);
+  int until_fold = fold_every;
   unsigned fold_turn = gwarp * 3u;
 
   // The index data of a position (its window of words, lane l holding offset l - skip, and
@@ -400,8 +424,8 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
     // no later centre of this warp reaches position t - skip
     if (dirty) retire(w_oldest, wslot);
     wslot = (wslot + 1 == slots) ? 0 : wslot + 1;
-    if (hot.fold_every > 0 && --until_fold == 0) {
-      until_fold = 2 * hot.fold_every;
+    if (fold_every > 0 && --until_fold == 0) {
+      until_fold = fold_every;
       fold_one_replica<NR>(hot, A, B, dim, nvec, lane, fold_turn++);
     }
     wraw = wraw_next;
@@ -728,7 +752,8 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
   const int mycols = (gwarp < ncols) ? (ncols - gwarp + nwarps - 1) / nwarps : 0;
   double acc = 0.0;  // EVAL: this lane's share of the score
   const bool tail = lane + 32 * (NR - 1) < nvec;
-  int until_fold = hot.fold_every;
+  const int fold_every = fold_period(hot, lrate, (float)NWB);
+  int until_fold = fold_every;
   unsigned fold_turn = (unsigned)gwarp * 5u;
 
   // Starts the copies of a column (word ids in `w`, one per lane) into stage `st`.
@@ -863,8 +888,8 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
       __syncwarp();  // every lane is done with this stage: start the copies of the next column
       refill();
     }
-    if (!EVAL && hot.fold_every > 0 && --until_fold == 0) {
-      until_fold = hot.fold_every;
+    if (!EVAL && fold_every > 0 && --until_fold == 0) {
+      until_fold = fold_every;
       fold_one_replica<NR>(hot, A, B, dim, nvec, lane, fold_turn++);
     }
   }
@@ -1092,6 +1117,7 @@ HotRows hot_rows_at(float *buffer, int levels) {
     return e ? atoi(e) : 64;
   }();
   h.fold_every = h.limit > 1 ? every : 0;
+  h.stats = nullptr;
   return h;
 }
 

@@ -193,3 +193,26 @@ def test_heldout_score_matches_cpu_reference_at_benchmark_scale(oracle):
     cpu = cpu_model.evalbatch(held, *oracle._draws(rng, N, 5, 5, 5))
     assert cpu > 2 * np.log(0.5) + 2e-3            # the CPU run learnt something
     assert abs(gpu - cpu) <= 0.01 * abs(cpu), (gpu, cpu)
+
+
+def test_dense_text_at_the_script_rate_stays_bounded():
+    """Unsubsampled Zipf text at lrate 1e-3 is the hard case for the hot-row replicas: the most
+    frequent word takes a tenth of all contexts, and with a fixed folding period the model
+    reached 1e19 within twenty minibatches (plain atomics stay near 3).  The folding period
+    now follows the word's share and the rate; the model must stay bounded."""
+    from bidmach_b200 import Word2Vec
+    from bidmach_b200.corpus import zipf_cdf, zipf_corpus
+    from bidmach_b200.word2vec import Opts
+    cdf = zipf_cdf(V, 1.07)
+    pool = [dev(zipf_corpus(V, N, 1.07, seed=40 + k, doc_len=1000, cdf=cdf)) for k in range(3)]
+    m = Word2Vec(Opts(dim=D, vocabSize=V, wsample=1.0, lrate=1e-3, seed=17)).init(N)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    m.modelmats[1].copy_((torch.rand(V, D, device="cuda", generator=g) - 0.5) / D)
+    pos = 0
+    for s in range(20):
+        pos += N
+        m.dobatch([pool[s % 3]], 0, pos)
+    assert torch.isfinite(m.modelmats[0]).all() and torch.isfinite(m.modelmats[1]).all()
+    assert float(m.modelmats[0].abs().max()) < 100 and float(m.modelmats[1].abs().max()) < 100
+    assert m.evalbatch([pool[0]], 0, N) > -10.0

@@ -341,5 +341,22 @@ __device__ __forceinline__ void bulk_load_row(void *smem_dst, const void *gsrc, 
 __device__ __forceinline__ void async_proxy_fence() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// Bulk reduction shared -> global: adds `bytes` / 4 floats at smem_src to those at gdst
+// (both 16-byte aligned, bytes a multiple of 16).  Completion through bulk groups.
+__device__ __forceinline__ void bulk_reduce_add_row(float *gdst, const void *smem_src, unsigned bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gdst),
+               "r"(smem_addr(smem_src)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_group_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
 
 }  // namespace w2v

@@ -1435,6 +1435,13 @@ __global__ void __launch_bounds__(512) row_probe_kernel(int dim, int ncols,
   PRow<NR> zero;
   prow_zero(zero);
   float seen = 0.f;
+  __shared__ __align__(16) float zero_row[MODE == 2 ? 32 * 4 * NR : 4];
+  if (MODE == 2) {
+    for (int k = threadIdx.x; k < 32 * 4 * NR; k += blockDim.x) zero_row[k] = 0.f;
+    async_proxy_fence();
+    __syncthreads();
+  }
+  int in_flight = 0;
   for (int col = gwarp; col < ncols; col += nwarps) {
     int myw = 0;
     if (lane < nwa)
@@ -1447,13 +1454,23 @@ __global__ void __launch_bounds__(512) row_probe_kernel(int dim, int ncols,
         float *dst = (r < nwa) ? update_target(A, hot.shadowA, hot, w, dim, gwarp)
                                : update_target(B, hot.shadowB, hot, w, dim, gwarp);
         prow_red_lane(dst + 4 * lane, tail, zero);
+      } else if (MODE == 2) {
+        // the same additions as one bulk reduction per row, issued by one lane
+        float *dst = (r < nwa) ? update_target(A, hot.shadowA, hot, w, dim, gwarp)
+                               : update_target(B, hot.shadowB, hot, w, dim, gwarp);
+        if (lane == 0) bulk_reduce_add_row(dst, zero_row, (unsigned)dim * 4u);
       } else {
         PRow<NR> row;
         prow_load_lane(row, reinterpret_cast<const ulonglong2 *>((r < nwa ? A : B) + (int64_t)w * dim) + lane, tail);
         seen += prow_dot_partial(row, row);
       }
     }
+    if (MODE == 2 && lane == 0) {
+      bulk_commit_group();
+      if (++in_flight > 4) bulk_wait_group_read<4>();
+    }
   }
+  if (MODE == 2 && lane == 0) bulk_wait_group_all();
   if (MODE == 1 && seen == -1.0f) *sink = seen;  // keeps the loads alive; never true
 }
 
@@ -1461,7 +1478,7 @@ int row_probe_async(int dim, int ncols, const int *ncols_dev, int nwa, int nwb, 
                     const int *WB, float *A, float *B, const HotRows &hot, int mode, float *sink,
                     cudaStream_t stream) {
   if (ncols <= 0) return 0;
-  if (!vector_ok(dim, A, B) || nwa + nwb > 32 || mode < 0 || mode > 1) return 1;
+  if (!vector_ok(dim, A, B) || nwa + nwb > 32 || mode < 0 || mode > 2) return 1;
   const int nr = (dim / 4 + 31) / 32;
   if (nr > 10) return 1;
   // the scatter takes the same time with 16 to 128 warps per SM (4.02 - 4.16 ms on the benchmark
@@ -1470,8 +1487,11 @@ int row_probe_async(int dim, int ncols, const int *ncols_dev, int nwa, int nwb, 
   if (mode == 0) {
     W2V_NR_SWITCH(nr, (row_probe_kernel<NR, 0><<<grid, 512, 0, stream>>>(dim, ncols, ncols_dev, nwa, nwb, WA,
                                                                        WB, A, B, hot, sink)));
-  } else {
+  } else if (mode == 1) {
     W2V_NR_SWITCH(nr, (row_probe_kernel<NR, 1><<<grid, 512, 0, stream>>>(dim, ncols, ncols_dev, nwa, nwb, WA,
+                                                                       WB, A, B, hot, sink)));
+  } else {
+    W2V_NR_SWITCH(nr, (row_probe_kernel<NR, 2><<<grid, 512, 0, stream>>>(dim, ncols, ncols_dev, nwa, nwb, WA,
                                                                        WB, A, B, hot, sink)));
   }
   count_launch(1);

@@ -268,7 +268,9 @@ int w2v_get_timing(w2v_ctx *ctx, w2v_timing *out); /* synchronises the last stre
 /* Diagnostic: the memory side of the negative kernels alone, on the columns of
  * the latest w2v_wordmats.  mode 0: a row of zeros is added to every row of
  * every column with the update kernel's atomic reductions (A and B keep their
- * values); mode 1: every row is read.  The duration of the call's kernel is
+ * values); mode 1: every row is read; mode 2: as mode 0 with one bulk
+ * reduction (shared -> global, add.f32) per row in place of the per-lane
+ * reductions.  The duration of the call's kernel is
  * what the memory system needs for the scatter (the gather) of one negative
  * update (scoring) launch: the bound bench.py --mode bound reports. */
 int w2v_probe_rows(w2v_ctx *ctx, float *A, float *B, int mode, void *stream);

@@ -99,7 +99,7 @@ def test_unsupported_options_are_refused():
 
 def test_row_probe_leaves_the_model_unchanged():
     """w2v_probe_rows: the memory side of the negative kernels alone (zeros added with
-    the update kernel's reductions, or rows read); a diagnostic, so the model must come
+    the update kernel's reductions or with bulk reductions, or rows read); a diagnostic, so the model must come
     out bit for bit as it went in."""
     from bidmach_b200 import _lib
     n = 3000
@@ -109,7 +109,7 @@ def test_row_probe_leaves_the_model_unchanged():
     m.wordMats([toks], batch_id=9)
     before = [x.clone() for x in m.modelmats]
     lib = _lib.load()
-    for mode in (0, 1):
+    for mode in (0, 1, 2):
         assert lib.w2v_probe_rows(m._ctx, m.modelmats[1].data_ptr(), m.modelmats[0].data_ptr(), mode,
                                   m._stream()) == 0
     torch.cuda.synchronize()

@@ -131,8 +131,8 @@ __device__ __forceinline__ void row_red_to(float *p, int nvec, int lane, const R
   }
 }
 
-// Continuous folding.  Every so often a warp takes one replica row (round
-// robin over all of them), atomically swaps its contents for zeros and adds
+// Continuous folding.  Every so often a warp takes one replica row (the next
+// of the schedule in fold_one_replica), atomically swaps its contents for zeros and adds
 // what it took to the model row the replica stands for.  Replicas therefore
 // hold only the last few microseconds of updates, and readers of a hot row see
 // its updates almost as soon as they would without replicas; what is left at

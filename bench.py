@@ -12,26 +12,35 @@ nreuse 5, both matrices U(-0.5,0.5)/dim; frequent-word subsampling is switched
 off (wsample=1 keeps every word), so every token yields pairs.
 
 With N > 1 every rank runs the same workload on its own minibatches (weak
-scaling) and both matrices are averaged with an all-reduce every
-``--sync-every`` (8) minibatches, inside the timed region.
+scaling) and both matrices are averaged over the replicas every
+``--sync-every`` (8) minibatches, inside the timed region: in place through the
+NVLink multicast mapping of the model buffer, beside the next minibatch, where
+the platform offers one, else with an NCCL all-reduce.
 
-Prints ONE JSON line (rank 0).  `value` is measured with the minibatches
-already in device memory; `e2e` is the same loop through the host-buffer entry
-point (pinned host minibatch -> device copy -> update -> pair count back).
-`roofline` describes the negative-update kernel: algorithmic bytes over its
-measured duration against the measured HBM copy peak, the DRAM traffic of an
-ncu capture, and `memory_bound`: what the kernel's atomic row additions and
-its row reads take on their own, on the same columns (w2v_probe_rows).
+Prints ONE JSON line (rank 0).  The timed region of `--steps` minibatches is
+repeated `--repeats` times and the median region reported (`repeats` holds all
+of them).  `value` is measured with the minibatches already in device memory;
+`e2e` is the same loop through the host-buffer entry point (pinned host
+minibatch -> device copy -> update -> pair count back).  `roofline` describes
+the negative-update kernel: algorithmic bytes over its measured duration
+against the measured HBM copy peak, the DRAM traffic of an ncu capture,
+`compulsory_bytes` (every distinct row the launch names read once and written
+once: a fraction that cannot exceed 1), and `memory_bound`: what the kernel's
+atomic row additions and its row reads take on their own, on the same columns
+(a probe library of its own, libw2vrowprobe.so).  `eval` is the scoring path
+(configs[2]) on fixed random matrices, a shorter stretch of the same run.
+With N > 1, `collective` describes the exchange: its kind, the bytes, what it
+takes alone (CUDA events, max over ranks) and how many fell into the region.
 `--impl reference` times the reference's own CPU kernels (compiled from its C
 source into oracle/_ref) with all host cores on a bounded sample per step.
 
-Other switches: `--mode eval` times the scoring path (configs[2]);
+Other switches: `--mode eval` times the scoring path alone;
 `--vocab / --tokens / --dim / --nneg / --wsample / --topics` change the
 workload (configs[3] and [4]: `--topics 1000 --wsample 1e-4`,
 `--topics 3000 --wsample 1e-4 --vocab 3000000 --nneg 10`); `--sort-permute`
 shuffles the pair list by sorting random keys as the reference's GPU branch;
-`--head-sync` / `--overlap-sync` select the reference's head-only averaging
-schedule or an exchange overlapped with the next minibatch.
+`--head-sync` selects the reference's head-only averaging schedule;
+`--exchange nccl|nvls` and `--sync-mode blocking|overlap` the kind of exchange.
 """
 from __future__ import annotations
 
@@ -57,9 +66,9 @@ DEFAULT_WORKLOAD = dict(WORKLOAD)   # --vocab / --tokens / --nneg change WORKLOA
 POOL = 4             # distinct minibatches per rank, cycled
 CPU_SAMPLE = 500_000  # tokens of one minibatch the CPU arms process per step
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the negative-update
-# kernel on this workload (6.48 GB read + 6.82 GB written), from a one-pass ncu
-# capture of the full-size workload; see profiles/update_kernels_zipf_vocab1M_dim300.md.
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the negative-update kernel on the
+# default workload at the default rate (6.48 GB read + 6.82 GB written), from a one-pass ncu
+# capture of the full-size workload.
 NEG_DRAM_TRAFFIC_BYTES = 13.30e9
 
 
@@ -191,11 +200,36 @@ def cpu_kind():
     return "reference" if orc.have_reference() else "port"
 
 
+def cpu_threads():
+    """Gives the CPU kernels every host core, whatever OMP_NUM_THREADS the launcher exported
+    (torch.distributed.run sets it to 1), and returns (threads asked for, threads an OpenMP
+    parallel region really runs with)."""
+    from oracle import oracle as orc
+    cores = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(cores)
+    return cores, orc.set_threads(cores)
+
+
+def cpu_baseline(tokens, reps, warm=1):
+    """The reference's CPU update kernels on a bounded sample of one minibatch: words/s."""
+    cores, team = cpu_threads()
+    kind = cpu_kind()
+    orc, state = cpu_arm_setup(tokens)
+    for _ in range(warm):
+        cpu_arm_step(orc, state, kind, cores)
+    t = [cpu_arm_step(orc, state, kind, cores) for _ in range(reps)]
+    return {"value": CPU_SAMPLE / min(t), "unit": UNIT, "cores": team, "kind": kind,
+            "sample_tokens": CPU_SAMPLE, "seconds_per_sample": t,
+            "sample": f"first {CPU_SAMPLE} tokens of one 1M-token minibatch; positive + negative update "
+                      f"kernels of the reference's BIDMach_CPUMACH.c split into {cores} chunks, run by an "
+                      f"OpenMP team of {team} threads; best of {reps}; preprocessing untimed"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cores = os.cpu_count() or 1
+    cores, team = cpu_threads()
     kind = cpu_kind()
     pool = make_pool(0, 1)
     orc, state = cpu_arm_setup(pool[0])
@@ -205,41 +239,24 @@ def run_reference(args):
     total = float(np.sum(t))
     value = CPU_SAMPLE * args.steps / total
     sample = (f"first {CPU_SAMPLE} tokens of one 1M-token minibatch per step; positive + negative "
-              f"update kernels of BIDMach_CPUMACH.c, {cores} OpenMP threads; preprocessing untimed")
+              f"update kernels of BIDMach_CPUMACH.c split into {cores} chunks, run by an OpenMP team of "
+              f"{team} threads; preprocessing untimed")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": config_dict(args, extra={"cpu_sample_tokens": CPU_SAMPLE}),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "data": "synthetic", "config": config_dict(args),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": team, "kind": kind, "sample": sample,
+                         "sample_tokens": CPU_SAMPLE},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
-# dram__bytes_read.sum per launch of the negative scoring kernel on the default workload
-# (one-pass ncu capture; see profiles/scoring_kernels_zipf_vocab1M_dim300.md)
+# dram__bytes_read.sum per launch of the negative scoring kernel on the default workload (one-pass
+# ncu capture of the full-size workload)
 EVALNEG_DRAM_TRAFFIC_BYTES = 7.07e9
-
-
-def eval_roofline(w, groups, row, evalneg_ms, bounds):
-    """The negative scoring kernel against the HBM copy peak: rows read (algorithmic bytes)
-    over its measured duration, the DRAM bytes of the ncu capture, and what reading the same
-    rows and nothing else takes (ms per launch)."""
-    peak, peak_kind = measured_peak_gbs()
-    nbytes = groups * (w["nneg"] + w["nreuse"]) * row
-    achieved = nbytes / (evalneg_ms * 1e-3) / 1e9 if evalneg_ms > 0 else None
-    default_shape = all(w[k] == DEFAULT_WORKLOAD[k] for k in ("vocab", "dim", "ntokens", "nneg", "nreuse", "nskip"))
-    traffic = EVALNEG_DRAM_TRAFFIC_BYTES if default_shape else None
-    return {"bound": "hbm", "kernel": "neg_update_staged_kernel<%d,%d,%d,true>" % (
-                w["nneg"], w["nreuse"], (w["dim"] // 4 + 31) // 32),
-            "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-            "frac": (achieved / peak) if achieved else None, "traffic": traffic,
-            "algorithmic_bytes_per_launch": nbytes, "avg_launch_ms": evalneg_ms,
-            "dram_frac": (traffic / (evalneg_ms * 1e-3) / 1e9 / peak) if (traffic and evalneg_ms > 0) else None,
-            "memory_bound": ({"gather_only_ms": bounds[1],
-                              "kernel_over_gather_only": evalneg_ms / bounds[1]} if bounds else None)}
 
 
 def config_dict(args, extra=None):
@@ -249,10 +266,9 @@ def config_dict(args, extra=None):
          "vocab": w["vocab"], "dim": w["dim"], "tokens_per_minibatch": w["ntokens"], "nskip": w["nskip"],
          "nneg": w["nneg"], "nreuse": w["nreuse"], "wsample": w["wsample"], "lrate": w["lrate"],
          "vexp": w["vexp"], "minibatch_pool": POOL,
-         "parallelism": f"dp{args.gpus}: replicas, own minibatches, all-reduce(avg) of both matrices "
+         "parallelism": f"dp{args.gpus}: replicas, own minibatches, both matrices averaged over the replicas "
                         f"every {args.sync_every} minibatches"
-                        + (" (overlapped with the next minibatch)" if args.overlap_sync else
-                           " (head rows only, the reference's schedule)" if args.head_sync else " (blocking)")
+                        + (" (head rows only, the reference's schedule)" if args.head_sync else "")
                         if args.gpus > 1 else "single GPU",
          "l2_policy": "inputs larger than L2: 2.4 GB of embedding rows gathered per Zipf draw; no flush"}
     if w.get("topics"):
@@ -274,6 +290,8 @@ def config_dict(args, extra=None):
 # ---------------------------------------------------------------------------
 
 def run_ours(args):
+    import ctypes as C
+
     import torch
     import torch.distributed as dist
 
@@ -298,10 +316,26 @@ def run_ours(args):
              lrate=w["lrate"], texp=w["texp"], vexp=w["vexp"], wsample=w["wsample"], seed=17 + rank,
              sortPermute=args.sort_permute)
     model = Word2Vec(o, device=torch.device("cuda", local)).init(N)
-    # configs[1]: both matrices random
     g = torch.Generator(device="cuda")
-    g.manual_seed(5)
-    model.modelmats[1].copy_((torch.rand(w["vocab"], w["dim"], device="cuda", generator=g) - 0.5) / w["dim"])
+
+    def randomise_model():
+        # configs[1] / configs[2]: both matrices U(-0.5, 0.5) / dim from a seed
+        g.manual_seed(5)
+        for m in model.modelmats:
+            m.copy_((torch.rand(w["vocab"], w["dim"], device="cuda", generator=g) - 0.5) / w["dim"])
+
+    # the exchange: in place through the NVLink multicast mapping where the platform has one
+    exchange = "none"
+    if world > 1:
+        exchange = "nccl"
+        if args.exchange in ("auto", "nvls") and not args.head_sync and model.enableSymmetric():
+            exchange = "nvls"
+        elif args.exchange == "nvls":
+            raise SystemExit("--exchange nvls: no symmetric memory with a multicast mapping here (%s)"
+                             % getattr(model, "_symm_error", "no multicast address"))
+    overlap = world > 1 and not args.head_sync and (
+        args.sync_mode == "overlap" or (args.sync_mode == "auto" and exchange == "nvls"))
+    randomise_model()
     if world > 1:
         for m in model.modelmats:
             dist.broadcast(m, src=0)
@@ -310,6 +344,7 @@ def run_ours(args):
     host = [torch.from_numpy(p).pin_memory() for p in pool]
     devt = [h.cuda() for h in host]
     stream = torch.cuda.current_stream()
+    exch_events = []   # (start, end) events around every exchange of the current region
 
     def sync_all():
         torch.cuda.synchronize()
@@ -317,70 +352,112 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize()
 
-    def run_steps(nsteps, host_path, first_pos):
+    def exchange_now(k):
+        """The averaging exchange that follows minibatch k of a region (1-based)."""
+        if args.head_sync:
+            # the reference's schedule (Learner.scala:654-655, Word2Vec.scala:548): sync k averages
+            # the first headlen << trailingZeros(k * world) rows of each matrix
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            model.mergeModelFn(None, k * world // args.sync_every)
+            b.record(stream)
+            exch_events.append((a, b))
+        elif overlap:
+            model.startMerge()          # runs beside the next minibatch; finishMerge follows it
+            exch_events.append(None)
+        else:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            model.mergeModelFn()
+            b.record(stream)
+            exch_events.append((a, b))
+
+    def run_steps(nsteps, host_path, first_pos, mode, exchanges=True):
+        """nsteps minibatches.  Exchanges follow the minibatches k with (nsteps - k) % sync_every == 0,
+        so that a region holds ceil(nsteps / sync_every) of them, never fewer than its share."""
         pos = first_pos
-        for s in range(nsteps):
+        for s in range(1, nsteps + 1):
             pos += N
-            if args.mode == "eval":
+            b = (s - 1) % POOL
+            if mode == "eval":
                 if host_path:
-                    model.evalbatchg([host[s % POOL].numpy()], 0, pos)
+                    model.evalbatchg([host[b].numpy()], 0, pos)
                 else:
-                    model.evalbatch([devt[s % POOL]], 0, pos)
+                    model.evalbatch([devt[b]], 0, pos)
                 continue
             if host_path:
-                model.dobatchg([host[s % POOL].numpy()], 0, pos)
+                model.dobatchg([host[b].numpy()], 0, pos)
             else:
-                model.dobatch([devt[s % POOL]], 0, pos)
-            if world > 1:
-                if args.head_sync:
-                    # the reference's schedule (Learner.scala:654-655, Word2Vec.scala:548): sync k
-                    # averages the first headlen << trailingZeros(k * world) rows of each matrix
-                    if (s + 1) % args.sync_every == 0:
-                        model.mergeModelFn(None, (s + 1) * world // args.sync_every)
-                elif not args.overlap_sync:
-                    if (s + 1) % args.sync_every == 0:
-                        model.mergeModelFn()
-                else:   # the exchange runs beside the next minibatch and is folded in after it
-                    if s % args.sync_every == 0:
-                        model.finishMerge()
-                    if (s + 1) % args.sync_every == 0:
-                        model.startMerge()
+                model.dobatch([devt[b]], 0, pos)
+            if world > 1 and exchanges:
+                if overlap:
+                    model.finishMerge()          # an exchange started after the previous minibatch
+                if (nsteps - s) % args.sync_every == 0:
+                    exchange_now(s)
         return pos
 
-    def timed(host_path, pos):
-        pos = run_steps(args.warmup, host_path, pos)
-        sync_all()
-        lib.w2v_set_timing(model._ctx, 0 if host_path else 1)
-        launches0 = lib.w2v_launch_count()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        sampler.window_open()
-        e0.record(stream)
-        pos = run_steps(args.steps, host_path, pos)
+    def timed(host_path, pos, mode, steps, warmup):
+        """One warm-up stretch, then args.repeats regions of exactly `steps` minibatches, each
+        bracketed by a device barrier; returns per-region ms (max over ranks) and bookkeeping
+        of the median region."""
+        pos = run_steps(warmup, host_path, pos, mode)
         if world > 1:
-            model.finishMerge()   # an exchange still in flight belongs to the timed region
-        e1.record(stream)
-        sync_all()
-        sampler.window_close()
-        clocks = sampler.summary()
-        ms = e0.elapsed_time(e1)
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()), lib.w2v_launch_count() - launches0, clocks, pos
+            model.finishMerge()
+        regions = []
+        for r in range(args.repeats):
+            sync_all()
+            lib.w2v_set_timing(model._ctx, 0 if host_path else 1)
+            launches0 = lib.w2v_launch_count()
+            del exch_events[:]
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            sampler.window_open()
+            e0.record(stream)
+            pos = run_steps(steps, host_path, pos, mode)
+            if world > 1:
+                model.finishMerge()   # an exchange still in flight belongs to the timed region
+            e1.record(stream)
+            sync_all()
+            sampler.window_close()
+            ms = e0.elapsed_time(e1)
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            tm = _lib.W2VTiming()
+            lib.w2v_get_timing(model._ctx, tm)
+            ex_ms = [a.elapsed_time(b) for (a, b) in [e for e in exch_events if e is not None]]
+            regions.append({"ms": float(t.item()), "launches": lib.w2v_launch_count() - launches0,
+                            "clocks": sampler.summary(), "timing": tm, "exchanges": len(exch_events),
+                            "exchange_ms": ex_ms})
+        order = sorted(range(len(regions)), key=lambda i: regions[i]["ms"])
+        med = regions[order[len(order) // 2]]
+        all_ms = [x["ms"] for x in regions]
+        med["all_ms_per_step"] = [x / steps for x in all_ms]
+        med["spread"] = (max(all_ms) - min(all_ms)) / med["ms"] if med["ms"] > 0 else None
+        return med, pos
 
-    def probe_bounds(reps=8):
+    probe = None
+
+    def probe_bounds(reps=6):
         """The memory side of the negative kernels alone, on the workload's own columns:
         the update kernel's atomic row reductions with zeros (nothing else), and the
         scoring kernel's row reads (nothing else).  ms per launch, CUDA events."""
+        nonlocal probe
+        path = os.path.join(os.path.dirname(_lib.LIB_PATH), "libw2vrowprobe.so")
+        if not os.path.exists(path):
+            return None
+        if probe is None:
+            probe = C.CDLL(path)
+            probe.w2v_rowprobe.argtypes = [C.c_int] * 4 + [C.c_void_p] * 4 + [C.c_int, C.c_void_p]
         out = []
         for mode in (0, 1):
             tot = 0.0
             for r in range(reps + 2):
-                model.wordMats([devt[r % POOL]], batch_id=1000 + r)
+                _, _, _, wa, wb = model.wordMats([devt[r % POOL]], batch_id=1000 + r)
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record(stream)
-                err = lib.w2v_probe_rows(model._ctx, model.modelmats[1].data_ptr(), model.modelmats[0].data_ptr(),
-                                         mode, model._stream())
+                err = probe.w2v_rowprobe(w["dim"], wa.shape[0], w["nneg"], w["nreuse"], wa.data_ptr(), wb.data_ptr(),
+                                         model.modelmats[1].data_ptr(), model.modelmats[0].data_ptr(), mode,
+                                         model._stream())
                 b.record(stream)
                 torch.cuda.synchronize()
                 if err:
@@ -390,46 +467,113 @@ def run_ours(args):
             out.append(tot / reps)
         return out
 
+    def distinct_rows():
+        """Distinct rows of A and of B that one minibatch's negative columns name (mean over the pool)."""
+        na = nb_ = 0.0
+        for k in range(POOL):
+            _, _, _, wa, wb = model.wordMats([devt[k]], batch_id=2000 + k)
+            na += float(torch.unique(wa).numel())
+            nb_ += float(torch.unique(wb).numel())
+        return na / POOL, nb_ / POOL
+
+    def collective_alone(reps=3):
+        """The exchange by itself, nothing else on the GPU: ms per exchange (max over ranks)."""
+        out = []
+        for _ in range(reps + 1):
+            sync_all()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            model.mergeModelFn()
+            b.record(stream)
+            sync_all()
+            t = torch.tensor([a.elapsed_time(b)], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            out.append(float(t.item()))
+        return out[1:]
+
+    peak, peak_kind = measured_peak_gbs()
+    row = 4 * w["dim"]
+    nr = (w["dim"] // 4 + 31) // 32
+    default_shape = all(w[k] == DEFAULT_WORKLOAD[k] for k in ("vocab", "dim", "ntokens", "nneg", "nreuse", "nskip"))
+
+    def eval_block(dev_r, e2e_r, steps, bounds):
+        tm = dev_r["timing"]
+        nb = max(1, tm.eval_batches)
+        eg, ep = tm.eval_groups / nb, tm.eval_pairs / nb
+        evalneg_ms, evalpos_ms = tm.evalneg_ms / nb, tm.evalpos_ms / nb
+        nbytes = eg * (w["nneg"] + w["nreuse"]) * row
+        achieved = nbytes / (evalneg_ms * 1e-3) / 1e9 if evalneg_ms > 0 else None
+        traffic = EVALNEG_DRAM_TRAFFIC_BYTES if default_shape else None
+        return {"metric": "SGNS eval (log-likelihood scoring) words/sec at vocab 1M dim 300",
+                "workload": "configs[2]: scoring path, fixed random matrices, no update",
+                "value": world * N * steps / (dev_r["ms"] * 1e-3), "unit": UNIT, "steps": steps,
+                "ms_per_step": dev_r["ms"] / steps, "ms_per_step_all": dev_r["all_ms_per_step"],
+                "e2e": {"value": world * N * steps / (e2e_r["ms"] * 1e-3), "unit": UNIT,
+                        "h2d_bytes_per_step": 8 * N, "d2h_bytes_per_step": 8},
+                "gpu_launches": int(dev_r["launches"]),
+                "phases": {"prep_ms": tm.prep_ms / nb, "permute_ms": tm.permute_ms / nb,
+                           "evalpos_ms": evalpos_ms, "evalneg_ms": evalneg_ms,
+                           "evalpos_algorithmic_gbs": (N + ep) * row / evalpos_ms / 1e6 if evalpos_ms > 0 else None},
+                "roofline": {"bound": "hbm", "kernel": "neg_update_staged_kernel<%d,%d,%d,true>" % (
+                                 w["nneg"], w["nreuse"], nr),
+                             "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                             "frac": (achieved / peak) if achieved else None, "traffic": traffic,
+                             "algorithmic_bytes_per_launch": nbytes, "avg_launch_ms": evalneg_ms,
+                             "dram_frac": (traffic / (evalneg_ms * 1e-3) / 1e9 / peak)
+                             if (traffic and evalneg_ms > 0) else None,
+                             "memory_bound": ({"gather_only_ms": bounds[1],
+                                               "kernel_over_gather_only": evalneg_ms / bounds[1]}
+                                              if bounds else None)}}
+
+    K = args.steps
     pos = 0
-    ms_dev, launches, clocks, pos = timed(False, pos)
-    tm = _lib.W2VTiming()
-    lib.w2v_get_timing(model._ctx, tm)
-    ms_e2e, _, clocks_e2e, pos = timed(True, pos)
+    if args.mode == "eval":
+        dev_r, pos = timed(False, pos, "eval", K, args.warmup)
+        e2e_r, pos = timed(True, pos, "eval", K, args.warmup)
+        bounds = probe_bounds() if (rank == 0 and world == 1) else None
+        sampler.stop()
+        if rank == 0:
+            blk = eval_block(dev_r, e2e_r, K, bounds)
+            line = {"metric": blk.pop("metric"), "value": blk["value"], "unit": UNIT, "n_gpus": world,
+                    "steps": K, "warmup": args.warmup, "ms_per_step": blk["ms_per_step"],
+                    "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                    "data": "synthetic",
+                    "config": config_dict(args, extra={"workload": blk.pop("workload")}),
+                    "e2e": blk["e2e"], "gpu_launches": blk["gpu_launches"], "phases": blk["phases"],
+                    "roofline": blk["roofline"], "repeats": {"n": args.repeats,
+                                                             "ms_per_step": blk["ms_per_step_all"],
+                                                             "spread": dev_r["spread"]},
+                    "clocks": dev_r["clocks"]}
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    dev_r, pos = timed(False, pos, "train", K, args.warmup)
+    e2e_r, pos = timed(True, pos, "train", K, args.warmup)
+    coll_alone = collective_alone() if world > 1 and not args.head_sync else None
+    # the scoring path on fixed random matrices (configs[2]), a shorter stretch
+    eval_blk = None
+    if not args.no_eval:
+        randomise_model()
+        ke = max(4, min(K, 24))
+        ev_dev, pos = timed(False, pos, "eval", ke, 3)
+        ev_e2e, pos = timed(True, pos, "eval", ke, 3)
     bounds = probe_bounds() if (rank == 0 and world == 1) else None
+    rows_a, rows_b = distinct_rows() if rank == 0 else (0, 0)
     sampler.stop()
+    if not args.no_eval and rank == 0:
+        eval_blk = eval_block(ev_dev, ev_e2e, ke, bounds)
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    K = args.steps
-    if args.mode == "eval":
-        nb = max(1, tm.eval_batches)
-        row = 4 * w["dim"]
-        eg, ep = tm.eval_groups / nb, tm.eval_pairs / nb
-        line = {"metric": "SGNS eval (log-likelihood scoring) words/sec at vocab 1M dim 300",
-                "value": world * N * K / (ms_dev * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K,
-                "warmup": args.warmup, "ms_per_step": ms_dev / K, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": config_dict(args, extra={"workload": "configs[2]: scoring path, fixed random matrices"}),
-                "e2e": {"value": world * N * K / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 8 * N,
-                        "d2h_bytes_per_step": 8},
-                "gpu_launches": int(launches),
-                "phases": {"prep_ms": tm.prep_ms / nb, "permute_ms": tm.permute_ms / nb,
-                           "evalpos_ms": tm.evalpos_ms / nb, "evalneg_ms": tm.evalneg_ms / nb,
-                           "evalneg_algorithmic_gbs": eg * (w["nneg"] + w["nreuse"]) * row / (tm.evalneg_ms / nb) / 1e6,
-                           "evalpos_algorithmic_gbs": (N + ep) * row / (tm.evalpos_ms / nb) / 1e6},
-                "roofline": eval_roofline(w, eg, row, tm.evalneg_ms / nb, bounds),
-                "clocks": clocks}
-        print(json.dumps(line), flush=True)
-        if world > 1:
-            dist.destroy_process_group()
-        return
+    ms_dev, ms_e2e = dev_r["ms"], e2e_r["ms"]
+    tm = dev_r["timing"]
     value = world * N * K / (ms_dev * 1e-3)
     e2e_value = world * N * K / (ms_e2e * 1e-3)
-    peak, peak_kind = measured_peak_gbs()
-    row = 4 * w["dim"]
     nb = max(1, tm.train_batches)
     groups, pairs = tm.groups / nb, tm.pairs / nb
     neg_bytes = 2.0 * groups * (w["nneg"] + w["nreuse"]) * row
@@ -439,17 +583,22 @@ def run_ours(args):
     # positive kernel, same accounting: (centres-with-pairs + pairs) rows read and written;
     # every token is kept in this workload, so centres ~ tokens
     pos_bytes = 2.0 * (N + pairs) * row
-    # the ncu capture was taken on the default workload; another vocabulary or minibatch size
-    # changes the L2 hit rate, so no traffic figure is claimed for it
-    default_shape = all(w[k] == DEFAULT_WORKLOAD[k] for k in ("vocab", "dim", "ntokens", "nneg", "nreuse", "nskip"))
-    traffic = NEG_DRAM_TRAFFIC_BYTES if default_shape else None
+    # the DRAM traffic figure is an ncu capture of the default workload at the default rate; another
+    # vocabulary, minibatch size or rate changes the L2 hit rate and the folding period
+    traffic = NEG_DRAM_TRAFFIC_BYTES if (default_shape and w["lrate"] == DEFAULT_WORKLOAD["lrate"]) else None
+    # what no kernel can avoid: every distinct row the launch names read once and written once
+    compulsory = 2.0 * row * (rows_a + rows_b)
     roofline = {"bound": "hbm", "kernel": "neg_update_staged_kernel<%d,%d,%d,false>" % (
-                    w["nneg"], w["nreuse"], (w["dim"] // 4 + 31) // 32), "achieved": achieved, "peak": peak,
+                    w["nneg"], w["nreuse"], nr), "achieved": achieved, "peak": peak,
                 "peak_kind": peak_kind, "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
                 "traffic": traffic, "algorithmic_bytes_per_launch": neg_bytes,
                 "avg_launch_ms": neg_s * 1e3,
                 # the same fraction from the measured DRAM bytes instead of the algorithmic ones
                 "dram_frac": (traffic / neg_s / 1e9 / peak) if (traffic and neg_s > 0) else None,
+                # distinct rows read once + written once: at most 1 of peak by construction
+                "compulsory_bytes": compulsory, "distinct_rows": {"A": rows_a, "B": rows_b},
+                "compulsory_frac": (compulsory / neg_s / 1e9 / peak) if neg_s > 0 else None,
+                "traffic_over_compulsory": (traffic / compulsory) if (traffic and compulsory) else None,
                 # what the kernel's atomic row reductions take with nothing else in the kernel
                 # (zeros added to the same rows), and what reading those rows takes: ms per launch
                 "memory_bound": ({"scatter_only_ms": bounds[0], "gather_only_ms": bounds[1],
@@ -461,27 +610,39 @@ def run_ours(args):
               "update_kernels_frac_of_peak": ((neg_bytes + pos_bytes) / (neg_s + pos_s) / 1e9 / peak)
               if neg_s + pos_s > 0 else None}
 
+    collective = None
+    if world > 1:
+        nbytes = 4 * model._flat.numel()
+        collective = {"kind": ("multimem.ld_reduce/st kernel over the NVLink multicast mapping (w2v_nvls_average)"
+                               if exchange == "nvls" else "ncclAllReduce(avg) via torch.distributed"),
+                      "overlapped_with_next_minibatch": bool(overlap), "bytes": nbytes,
+                      "sync_every": args.sync_every, "exchanges_in_region": dev_r["exchanges"],
+                      "share_of_region": K / args.sync_every,
+                      "in_region_ms": dev_r["exchange_ms"] or None}
+        if coll_alone:
+            t = float(np.median(coll_alone))
+            collective.update({"alone_ms": t, "alone_all_ms": coll_alone,
+                               "bus_gbs": 2.0 * (world - 1) / world * nbytes / (t * 1e-3) / 1e9,
+                               "alg_gbs": nbytes / (t * 1e-3) / 1e9})
+        if args.head_sync:
+            collective["kind"] = "ncclAllReduce(avg) of the head rows (the reference's schedule)"
+
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
-        cores = os.cpu_count() or 1
-        kind = cpu_kind()
-        orc, state = cpu_arm_setup(pool[0])
-        cpu_arm_step(orc, state, kind, cores)
-        reps = 3
-        t = min(cpu_arm_step(orc, state, kind, cores) for _ in range(reps))
-        cpu = {"value": CPU_SAMPLE / t, "unit": UNIT, "cores": cores, "kind": kind,
-               "sample": f"first {CPU_SAMPLE} tokens of one minibatch, positive + negative update kernels "
-                         f"of the reference's BIDMach_CPUMACH.c with {cores} OpenMP threads, best of {reps}; "
-                         "preprocessing untimed"}
+        cpu = cpu_baseline(pool[0], reps=3)
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": args.warmup,
         "ms_per_step": ms_dev / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic", "config": config_dict(args),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 8 * N, "d2h_bytes_per_step": 8,
-                "ms_per_step": ms_e2e / K},
-        "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu, "phases": phases,
-        "clocks": clocks, "clocks_e2e": clocks_e2e,
+                "ms_per_step": ms_e2e / K, "ms_per_step_all": e2e_r["all_ms_per_step"],
+                "spread": e2e_r["spread"]},
+        "gpu_launches": int(dev_r["launches"]), "roofline": roofline, "cpu_baseline": cpu, "phases": phases,
+        "repeats": {"n": args.repeats, "ms_per_step": dev_r["all_ms_per_step"], "spread": dev_r["spread"],
+                    "reported": "median region"},
+        "eval": eval_blk, "collective": collective,
+        "clocks": dev_r["clocks"], "clocks_e2e": e2e_r["clocks"],
     }
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -493,15 +654,21 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=96)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--repeats", type=int, default=3,
+                    help="timed regions of --steps minibatches each; the median region is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sync-every", type=int, default=8)
-    ap.add_argument("--overlap-sync", action="store_true",
-                    help="multi-GPU: run the averaging all-reduce beside the next minibatch (snapshot + "
-                         "delayed correction) instead of blocking on it")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "nvls", "nccl"],
+                    help="multi-GPU: average the model in place through the NVLink multicast mapping "
+                         "(nvls; auto picks it where the platform has one) or with NCCL")
+    ap.add_argument("--sync-mode", default="auto", choices=["auto", "overlap", "blocking"],
+                    help="multi-GPU: run the exchange beside the next minibatch or block on it "
+                         "(auto: overlap with nvls, blocking with nccl)")
     ap.add_argument("--head-sync", action="store_true",
                     help="average only the growing head of the vocabulary at each sync, as the reference's "
                          "mergeModelFn does, instead of the whole model")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-eval", action="store_true", help="skip the scoring stretch of the default run")
     ap.add_argument("--mode", default="train", choices=["train", "eval"],
                     help="eval: time the scoring path (evalbatch) instead of the update path")
     ap.add_argument("--vocab", type=int, default=None, help="override the workload's vocabulary (profiling)")

@@ -50,7 +50,6 @@ SIGNATURES = {
     "word2vecEvalPos": (_I, [_I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "word2vecEvalNeg": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "word2vecEvalNegNoAlloc": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P]),
-    "w2v_probe_rows": (_I, [_P, _P, _P, _I, _P]),
     "bidmach_xxh32": (C.c_uint32, [_P, C.c_int64, C.c_uint32]),
     "bidmach_lz4_compress_bound": (C.c_int64, [C.c_int64]),
     "bidmach_lz4_compress": (C.c_int64, [_P, C.c_int64, _P, C.c_int64]),
@@ -79,6 +78,14 @@ SIGNATURES = {
     "w2v_dobatch_host": (_I, [_P, _P, _P, _P, C.c_int64, C.c_uint64, C.POINTER(C.c_int64), _P]),
     "w2v_evalbatch_host": (_I, [_P, _P, _P, _P, C.c_uint64, C.POINTER(C.c_double), _P]),
     "w2v_apply_average": (_I, [_P, _P, _P, C.c_int64, _P]),
+    "w2v_comm_init_all": (_I, [_I, C.POINTER(_I), C.POINTER(_P)]),
+    "w2v_comm_unique_id": (_I, [_P]),
+    "w2v_comm_init_rank": (_I, [_I, _I, _P, C.POINTER(_P)]),
+    "w2v_comm_register": (_I, [_P, _P, C.c_int64]),
+    "w2v_allreduce_avg": (_I, [_P, _P, _P, C.c_int64, _P]),
+    "w2v_comm_destroy": (None, [_P]),
+    "w2v_nvls_average": (_I, [_P, C.c_int64, _I, _I, _I, _P]),
+    "w2v_reserve_sms": (_I, [_P, _I]),
     "w2v_set_timing": (_I, [_P, _I]),
     "w2v_get_timing": (_I, [_P, C.POINTER(W2VTiming)]),
     "w2v_launch_count": (C.c_longlong, []),

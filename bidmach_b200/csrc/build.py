@@ -21,8 +21,12 @@ LIB_NAME = "libbidmachcuda-linux-x86_64.so"
 LIB_PATH = os.path.join(PKG, LIB_NAME)
 OBJ_DIR = os.path.join(HERE, "build")
 
-SOURCES = ["w2v_kernels.cu", "w2v_batch.cu", "w2v_noalloc.cu", "jni_shim.cpp", "matio_codec.cpp"]
-HEADERS = ["w2v_device.cuh", "w2v_internal.h", "jni_min.h",
+SOURCES = ["w2v_kernels.cu", "w2v_batch.cu", "w2v_noalloc.cu", "w2v_exchange.cu", "jni_shim.cpp",
+           "matio_codec.cpp"]
+# measuring aid of bench.py, a library of its own: nothing of it is in the C-ABI library
+PROBE_SOURCE = "bench_rowprobe.cu"
+PROBE_LIB_PATH = os.path.join(PKG, "libw2vrowprobe.so")
+HEADERS = ["w2v_device.cuh", "w2v_internal.h", "w2v_rows.cuh", "jni_min.h",
            os.path.join("..", "..", "include", "bidmach_b200.h")]
 
 NVCC_FLAGS = [
@@ -59,11 +63,15 @@ def _compile(src: str, force: bool, verbose: bool) -> str:
 
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ_DIR, exist_ok=True)
-    with concurrent.futures.ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
-        objs = list(pool.map(lambda s: _compile(s, force, verbose), SOURCES))
+    with concurrent.futures.ThreadPoolExecutor(max_workers=len(SOURCES) + 1) as pool:
+        objs = list(pool.map(lambda s: _compile(s, force, verbose), SOURCES + [PROBE_SOURCE]))
+    probe_obj = objs.pop()
     if force or _stale(LIB_PATH, objs):
         subprocess.check_call([_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a",
-                               *objs, "-o", LIB_PATH])
+                               *objs, "-o", LIB_PATH, "-ldl"])
+    if force or _stale(PROBE_LIB_PATH, [probe_obj]):
+        subprocess.check_call([_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a",
+                               probe_obj, "-o", PROBE_LIB_PATH])
     return LIB_PATH
 
 

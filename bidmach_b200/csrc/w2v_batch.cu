@@ -294,6 +294,9 @@ struct w2v_ctx {
   float *retvals;  // [0] positive, [1] negative
   float *hot_buf;  // replica rows of the hot ids
   w2v::HotRows hot;
+  w2v::EvalScratch *eval;  // accumulator of the scoring kernels (inside `counts`)
+  int *fault_host;         // pinned: set by a staged kernel that gave up waiting for its copies
+  int sm_reserve;          // SMs the update kernels leave free (w2v_reserve_sms)
   void *cub_tmp;
   size_t cub_tmp_bytes;
   // pinned host
@@ -441,6 +444,7 @@ void w2v_destroy(w2v_ctx *c) {
   cudaFree(c->wa); cudaFree(c->key_in); cudaFree(c->key_out); cudaFree(c->retvals);
   cudaFree(c->cub_tmp); cudaFree(c->hot_buf);
   cudaFreeHost(c->counts_host); cudaFreeHost(c->retvals_host);
+  if (c->fault_host) cudaFreeHost(c->fault_host);
   for (int r = 0; r < kRing; r++)
     for (int k = 0; k < 5; k++) if (c->ev[r][k]) cudaEventDestroy(c->ev[r][k]);
   if (c->ev_counts) cudaEventDestroy(c->ev_counts);
@@ -484,6 +488,9 @@ int w2v_create(const w2v_opts *opts, int ncols, w2v_ctx **out) {
   if (e == cudaSuccess) e = cudaMalloc(&c->cnt, n4);
   if (e == cudaSuccess) e = cudaMalloc(&c->off, n4);
   if (e == cudaSuccess) e = cudaMalloc(&c->counts, 256);
+  if (e == cudaSuccess) e = cudaMemset(c->counts, 0, 256);
+  if (e == cudaSuccess) e = cudaHostAlloc(&c->fault_host, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable);
+  if (e == cudaSuccess) *c->fault_host = 0;
   if (e == cudaSuccess) e = cudaMalloc(&c->ctx_in, p4);
   if (e == cudaSuccess) e = cudaMalloc(&c->ctx_out, p4);
   if (e == cudaSuccess) e = cudaMalloc(&c->key_in, p4);
@@ -511,7 +518,14 @@ int w2v_create(const w2v_opts *opts, int ncols, w2v_ctx **out) {
     return (int)e;
   }
   c->hot.stats = c->counts + 8;
+  c->eval = reinterpret_cast<w2v::EvalScratch *>(c->counts + 32);
   *out = c;
+  return 0;
+}
+
+int w2v_reserve_sms(w2v_ctx *c, int sms) {
+  if (!c || sms < 0) return 1;
+  c->sm_reserve = sms;
   return 0;
 }
 
@@ -552,9 +566,20 @@ static w2v::PermKeys make_perm_keys(const w2v_opts &o, uint64_t batch_id) {
   return k;
 }
 
+// A staged kernel of an earlier minibatch gave up waiting for its copies (it dropped the
+// rest of its columns): reported once, by the first call that finds the flag raised.
+static int take_fault(w2v_ctx *c) {
+  if (c->fault_host && *reinterpret_cast<volatile int *>(c->fault_host)) {
+    *c->fault_host = 0;
+    return (int)cudaErrorLaunchTimeout;
+  }
+  return 0;
+}
+
 int w2v_wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64_t batch_id,
                  void *stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
+  if (int fault = take_fault(c)) return fault;
   const w2v_opts &o = c->o;
   const int n = c->ncols;
   const int threads = 256, blocks = (n + threads - 1) / threads;
@@ -660,6 +685,7 @@ int w2v_dobatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, float *A, 
   const float nsteps = (float)pos / (float)c->first_pos;
   const float lrpos = o.lrate * (float)pow((double)nsteps, -(double)o.texp);
   const float lrneg = o.eqPosNeg ? lrpos : lrpos / (float)o.nneg;
+  w2v::SmReserve reserve(c->sm_reserve);
   int err = w2v_wordmats(c, tokens, u, batch_id, stream);
   if (err) return err;
   err = w2v::pos_update_async(o.dim, c->ncols, nullptr, o.nskip, c->words, c->lb, c->ub, A, B,
@@ -670,7 +696,7 @@ int w2v_dobatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, float *A, 
   const int *groups_dev = nullptr;
   group_count(c, &groups, &groups_dev);
   err = w2v::neg_update_async(o.dim, groups, groups_dev, 0x7fffffff, o.nneg, o.nreuse, c->wa,
-                              c->ctx_out, A, B, lrneg, o.vexp, c->hot, stream);
+                              c->ctx_out, A, B, lrneg, o.vexp, c->hot, c->fault_host, stream);
   mark(c, 4, stream);
   if (c->timing_on) c->ev_state[c->slot] = 1;
   return err;
@@ -684,14 +710,14 @@ int w2v_evalbatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, const fl
   if (err) return err;
   W2V_CHECK(cudaMemsetAsync(c->retvals, 0, 2 * sizeof(float), stream));
   err = w2v::pos_eval_async(o.dim, c->ncols, nullptr, o.nskip, c->words, c->lb, c->ub, A, B,
-                            c->retvals, stream);
+                            c->retvals, c->eval, stream);
   if (err) return err;
   mark(c, 3, stream);
   int groups = 0;
   const int *groups_dev = nullptr;
   group_count(c, &groups, &groups_dev);
   err = w2v::neg_eval_async(o.dim, groups, groups_dev, o.nneg, o.nreuse, c->wa, c->ctx_out, A, B,
-                            c->retvals + 1, stream);
+                            c->retvals + 1, c->eval, c->fault_host, stream);
   if (err) return err;
   mark(c, 4, stream);
   if (c->timing_on) c->ev_state[c->slot] = 2;
@@ -699,23 +725,13 @@ int w2v_evalbatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, const fl
   W2V_CHECK(cudaStreamSynchronize(stream));
   err = settle_counts(c);
   if (err) return err;
-  err = w2v::take_stage_fault();
+  err = take_fault(c);
   if (err) return err;
   const double epos = c->retvals_host[0], eneg = c->retvals_host[1];
   const double denom = (double)c->ngroups * o.nreuse;
   // (epos + eneg / nneg) / goodwords.length  (Word2Vec.scala:209)
   *score_host = denom > 0 ? (epos + eneg / (o.eqPosNeg ? 1 : o.nneg)) / denom : 0.0;
   return 0;
-}
-
-int w2v_probe_rows(w2v_ctx *c, float *A, float *B, int mode, void *stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
-  if (!c) return 1;
-  int groups = 0;
-  const int *groups_dev = nullptr;
-  group_count(c, &groups, &groups_dev);
-  return w2v::row_probe_async(c->o.dim, groups, groups_dev, c->o.nneg, c->o.nreuse, c->wa, c->ctx_out,
-                              A, B, c->hot, mode, c->retvals + 2, stream);
 }
 
 // Uploads a host minibatch into the token buffer whose turn it is, on the copy

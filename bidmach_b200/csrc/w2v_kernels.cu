@@ -60,10 +60,12 @@
 
 #include <algorithm>
 #include <atomic>
+#include <mutex>
 #include <type_traits>
 
 #include "w2v_device.cuh"
 #include "w2v_internal.h"
+#include "w2v_rows.cuh"
 
 namespace w2v {
 
@@ -84,20 +86,6 @@ __device__ __forceinline__ int window_word(const int *__restrict__ W, int i, int
   int t = i + j;
   if (t < 0 || t >= ncols) return -1;
   return W[t];
-}
-
-// Destination of an update to row w of matrix M: the row itself, or for a hot
-// id one of its replica rows in the side buffer (picked by the warp's number).
-__device__ __forceinline__ float *update_target(float *M, float *shadow, const HotRows &hot, int w,
-                                                int dim, unsigned pick) {
-  if (w + 1 < hot.limit) {
-    // level L holds the 2^L ids with 2^L <= id + 1 < 2^(L+1), each with rmax >> L replicas
-    const int level = 31 - __clz(w + 1);
-    const int reps = hot.rmax >> level;
-    const int row = hot.rmax * level + (w + 1 - (1 << level)) * reps + (int)(pick & (unsigned)(reps - 1));
-    return shadow + (int64_t)row * dim;
-  }
-  return M + (int64_t)w * dim;
 }
 
 // Folding period for this launch.  Updates to a hot row sit in its replicas until
@@ -249,40 +237,6 @@ __device__ __forceinline__ Neighbour look_at_neighbour(const int *__restrict__ W
     }
   }
   return nb;
-}
-
-// Only the last of a lane's NR vectors can fall off the end of a row (NR is
-// ceil(nvec / 32)), so one flag per lane replaces a bounds test per access.
-template <int NR>
-__device__ __forceinline__ bool vec_ok(int q, bool tail) {
-  return q < NR - 1 || tail;
-}
-
-// prow_load for a lane that already knows whether its last vector exists;
-// `base` points at the lane's first vector.
-template <int NR>
-__device__ __forceinline__ void prow_load_lane(PRow<NR> &r, const ulonglong2 *base, bool tail) {
-#pragma unroll
-  for (int q = 0; q < NR; q++) {
-    ulonglong2 t = make_ulonglong2(0ull, 0ull);
-    if (vec_ok<NR>(q, tail)) t = base[32 * q];
-    r.v[q][0] = t.x;
-    r.v[q][1] = t.y;
-  }
-}
-
-// dst[...] += r, `dst` pointing at the lane's first vector of the destination row.
-template <int NR>
-__device__ __forceinline__ void prow_red_lane(float *dst, bool tail, const PRow<NR> &r) {
-#pragma unroll
-  for (int q = 0; q < NR; q++) {
-    if (vec_ok<NR>(q, tail)) {
-      float4 v;
-      unpack2(r.v[q][0], v.x, v.y);
-      unpack2(r.v[q][1], v.z, v.w);
-      red_add_v4(dst + 128 * q, v);
-    }
-  }
 }
 
 // Shared memory: per warp, (2*skip+1) slots of nvec float4 (one context-row
@@ -699,7 +653,6 @@ __global__ void __launch_bounds__(kNegThreads)
 constexpr int kStagedHeader = 256;
 constexpr int kWaitPolls = 1 << 20;  // polls of a stage's barrier before giving up
 
-static __device__ int g_stage_fault;  // set when a stage never arrived; checked by the host
 
 // The smaller side of the column (NX rows) is held in registers, the larger
 // side (NY rows) is read from the stage twice: for the dot products and for the
@@ -725,7 +678,8 @@ template <int NWA, int NWB, int NR, bool EVAL>
 __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
     neg_update_staged_kernel(int dim, int ncols, const int *__restrict__ ncols_dev, int nwords,
                       const int *__restrict__ WA, const int *__restrict__ WB, float *A, float *B,
-                      float lrate, float vexp, HotRows hot, EvalScratch *scratch, float *retval) {
+                      float lrate, float vexp, HotRows hot, EvalScratch *scratch, float *retval,
+                      int *fault) {
   using S = Spread<NWA * NWB>;
   constexpr int NROWS = NWA + NWB;
   constexpr int NST = 1;
@@ -787,7 +741,10 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
     if (!__all_sync(kFullMask, mbar_wait_bounded(&bars[st], (unsigned)(i / NST) & 1u, kWaitPolls))) {
       // the copies never completed within the limit (this warp has no other
       // copy in flight): report and stop, the whole warp together
-      if (lane == 0) atomicExch(&g_stage_fault, 1);
+      if (lane == 0 && fault) {
+        *reinterpret_cast<volatile int *>(fault) = 1;
+        __threadfence_system();
+      }
       break;
     }
     const int myw = (lane < 16) ? ids[st * 16 + lane] : -1;
@@ -942,14 +899,20 @@ __global__ void __launch_bounds__(kNegThreads, (NegEvalShape<NWA, NWB, NR>::bloc
 #pragma unroll
     for (int x = 0; x < NX; x++) {
       const int64_t w = __shfl_sync(kFullMask, myw, XOFF + x);
-      prow_load_lane(X[x], reinterpret_cast<const ulonglong2 *>(MX + w * dim) + lane, tail);
+      if (w >= 0)   // a masked id (-1) scores as a zero row, as in the staged kernel
+        prow_load_lane(X[x], reinterpret_cast<const ulonglong2 *>(MX + w * dim) + lane, tail);
+      else
+        prow_zero(X[x]);
     }
     float p[NWA * NWB];
 #pragma unroll
     for (int y = 0; y < NY; y++) {
       const int64_t w = __shfl_sync(kFullMask, myw, YOFF + y);
       PRow<NR> Y;
-      prow_load_lane(Y, reinterpret_cast<const ulonglong2 *>(MY + w * dim) + lane, tail);
+      if (w >= 0)
+        prow_load_lane(Y, reinterpret_cast<const ulonglong2 *>(MY + w * dim) + lane, tail);
+      else
+        prow_zero(Y);
 #pragma unroll
       for (int x = 0; x < NX; x++)
         p[HOLD_B ? (y * NWB + x) : (x * NWB + y)] = prow_dot_partial(X[x], Y);
@@ -1048,6 +1011,12 @@ static std::atomic<long long> g_launches{0};
 long long launch_count() { return g_launches.load(); }
 void count_launch(int n) { g_launches.fetch_add(n); }
 
+// SMs the calling thread's launches leave free (see SmReserve).
+static thread_local int t_sm_reserve = 0;
+
+SmReserve::SmReserve(int sms) : previous(t_sm_reserve) { t_sm_reserve = sms > 0 ? sms : 0; }
+SmReserve::~SmReserve() { t_sm_reserve = previous; }
+
 int device_sm_count() {
   thread_local int cached_dev = -1, cached_sms = 0;
   int dev = 0;
@@ -1059,29 +1028,7 @@ int device_sm_count() {
     cached_dev = dev;
     cached_sms = sms;
   }
-  return cached_sms;
-}
-
-// One small zero-initialised accumulator per (host thread, device): the eval
-// kernels sum in double there and re-arm it themselves, so concurrent callers
-// on different threads or devices never share it.
-int eval_scratch(EvalScratch **out) {
-  constexpr int kMaxDev = 64;
-  thread_local EvalScratch *per_dev[kMaxDev] = {nullptr};
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return (int)e;
-  if (dev < 0 || dev >= kMaxDev) return (int)cudaErrorInvalidDevice;
-  if (!per_dev[dev]) {
-    EvalScratch *p = nullptr;
-    e = cudaMalloc(&p, 256);
-    if (e != cudaSuccess) return (int)e;
-    e = cudaMemset(p, 0, 256);
-    if (e != cudaSuccess) return (int)e;
-    per_dev[dev] = p;
-  }
-  *out = per_dev[dev];
-  return 0;
+  return std::max(1, cached_sms - t_sm_reserve);
 }
 
 // Replica rows for the hot ids: 64 rows per level and matrix, sized for the
@@ -1127,28 +1074,96 @@ HotRows hot_rows_at(float *buffer, int levels) {
   return h;
 }
 
-int thread_hot_rows(HotRows *out) {
-  constexpr int kMaxDev = 64;
-  thread_local float *per_dev[kMaxDev] = {nullptr};
-  const int levels = hot_levels_default();
-  if (levels == 0) {
-    *out = hot_rows_at(nullptr, 0);
-    return 0;
-  }
+// Pool of launcher scratch sets, one list per device.
+namespace {
+constexpr int kPoolMaxDev = 64;
+std::mutex g_pool_mutex;
+LaunchScratch *g_pool_free[kPoolMaxDev] = {nullptr};
+constexpr size_t kScratchTail = 256;  // bytes after the replica rows: stats at +0, accumulator at +64
+}  // namespace
+
+int acquire_launch_scratch(LaunchScratch **out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
-  if (dev < 0 || dev >= kMaxDev) return (int)cudaErrorInvalidDevice;
-  if (!per_dev[dev]) {
-    float *p = nullptr;
-    e = cudaMalloc(&p, hot_rows_bytes());
-    if (e != cudaSuccess) return (int)e;
-    e = cudaMemset(p, 0, hot_rows_bytes());
-    if (e != cudaSuccess) return (int)e;
-    per_dev[dev] = p;
+  if (dev < 0 || dev >= kPoolMaxDev) return (int)cudaErrorInvalidDevice;
+  {
+    std::lock_guard<std::mutex> lock(g_pool_mutex);
+    if (LaunchScratch *s = g_pool_free[dev]) {
+      g_pool_free[dev] = s->next;
+      s->next = nullptr;
+      *out = s;
+      return 0;
+    }
   }
-  *out = hot_rows_at(per_dev[dev], levels);
+  // every set on this device is in use by another thread's call: make one more
+  const size_t hot_bytes = hot_levels_default() > 0 ? hot_rows_bytes() : 0;
+  unsigned char *p = nullptr;
+  e = cudaMalloc(&p, hot_bytes + kScratchTail);
+  if (e != cudaSuccess) return (int)e;
+  int *fault = nullptr;
+  e = cudaHostAlloc(&fault, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable);
+  if (e == cudaSuccess) {
+    *fault = 0;
+    e = cudaMemsetAsync(p, 0, hot_bytes + kScratchTail, cudaStreamPerThread);
+  }
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    if (fault) cudaFreeHost(fault);
+    return (int)e;
+  }
+  LaunchScratch *s = new LaunchScratch();
+  s->hot_buf = hot_bytes ? reinterpret_cast<float *>(p) : nullptr;
+  s->stats = reinterpret_cast<int *>(p + hot_bytes);
+  s->eval = reinterpret_cast<EvalScratch *>(p + hot_bytes + 64);
+  s->fault = fault;
+  s->device = dev;
+  s->next = nullptr;
+  *out = s;
   return 0;
+}
+
+void release_launch_scratch(LaunchScratch *s) {
+  if (!s) return;
+  std::lock_guard<std::mutex> lock(g_pool_mutex);
+  s->next = g_pool_free[s->device];
+  g_pool_free[s->device] = s;
+}
+
+__global__ void hot_share_kernel(const int *__restrict__ ids, int64_t n, int nwords,
+                                 int *__restrict__ stats) {
+  int valid = 0, zeros = 0;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int w = ids[i];
+    valid += (w >= 0 && w < nwords);
+    zeros += (w == 0);
+  }
+  __shared__ int part[2];
+  if (threadIdx.x == 0) part[0] = part[1] = 0;
+  __syncthreads();
+  valid = __reduce_add_sync(kFullMask, valid);
+  zeros = __reduce_add_sync(kFullMask, zeros);
+  if ((threadIdx.x & 31) == 0) {
+    if (valid) atomicAdd(&part[0], valid);
+    if (zeros) atomicAdd(&part[1], zeros);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (part[0]) atomicAdd(&stats[0], part[0]);
+    if (part[1]) atomicAdd(&stats[1], part[1]);
+  }
+}
+
+int count_hot_share_async(const int *ids, int64_t n, int nwords, int *stats, cudaStream_t stream) {
+  cudaError_t e = cudaMemsetAsync(stats, 0, 2 * sizeof(int), stream);
+  if (e != cudaSuccess) return (int)e;
+  if (n <= 0) return 0;
+  const int threads = 256;
+  const int blocks = (int)std::min<int64_t>((n + threads * 8 - 1) / (threads * 8), (int64_t)device_sm_count() * 4);
+  hot_share_kernel<<<std::max(1, blocks), threads, 0, stream>>>(ids, n, nwords, stats);
+  count_launch(1);
+  return (int)cudaGetLastError();
 }
 
 static void fold_hot_rows(int dim, const HotRows &hot, float *A, float *B, cudaStream_t stream) {
@@ -1235,12 +1250,9 @@ int pos_update_async(int dim, int ncols, const int *ncols_dev, int skip, const i
 
 int pos_eval_async(int dim, int ncols, const int *ncols_dev, int skip, const int *W, const int *LB,
                    const int *UB, const float *A, const float *B, float *retval,
-                   cudaStream_t stream) {
+                   EvalScratch *scratch, cudaStream_t stream) {
   if (ncols <= 0) return 0;
   if (skip < 1 || skip > 15) return 1;
-  EvalScratch *scratch = nullptr;
-  int err = eval_scratch(&scratch);
-  if (err) return err;
   if (vector_ok(dim, A, B)) {
     const int nr = (dim / 4 + 31) / 32;
     const int grid = grid_for(ncols, kPosThreads, 8);
@@ -1271,7 +1283,8 @@ template <int NWA, int NWB, int NR, bool EVAL>
 static cudaError_t launch_neg_staged(int grid, int warps, size_t smem, cudaStream_t stream, int dim,
                                      int ncols, const int *ncols_dev, int nwords, const int *WA,
                                      const int *WB, float *A, float *B, float lrate, float vexp,
-                                     const HotRows &hot, EvalScratch *scratch, float *retval) {
+                                     const HotRows &hot, EvalScratch *scratch, float *retval,
+                                     int *fault) {
   // never more threads than the kernel was compiled for
   constexpr int kMaxWarps = StagedShape<NWA, NWB, NR>::max_threads / 32;
   if (warps > kMaxWarps) {
@@ -1284,7 +1297,7 @@ static cudaError_t launch_neg_staged(int grid, int warps, size_t smem, cudaStrea
     if (e != cudaSuccess) return e;
   }
   neg_update_staged_kernel<NWA, NWB, NR, EVAL><<<grid, warps * 32, smem, stream>>>(
-      dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval);
+      dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault);
   return cudaSuccess;
 }
 
@@ -1293,38 +1306,21 @@ static cudaError_t launch_neg_staged_any(bool eval, int grid, int warps, size_t 
                                          cudaStream_t stream, int dim, int ncols,
                                          const int *ncols_dev, int nwords, const int *WA,
                                          const int *WB, float *A, float *B, float lrate, float vexp,
-                                         const HotRows &hot, EvalScratch *scratch, float *retval) {
+                                         const HotRows &hot, EvalScratch *scratch, float *retval,
+                                         int *fault) {
   return eval ? launch_neg_staged<NWA, NWB, NR, true>(grid, warps, smem, stream, dim, ncols, ncols_dev,
                                                       nwords, WA, WB, A, B, lrate, vexp, hot, scratch,
-                                                      retval)
+                                                      retval, fault)
               : launch_neg_staged<NWA, NWB, NR, false>(grid, warps, smem, stream, dim, ncols, ncols_dev,
                                                        nwords, WA, WB, A, B, lrate, vexp, hot, scratch,
-                                                       retval);
-}
-
-// Reads and clears the flag a staged kernel raises when a stage never arrived.
-// Call after the stream has been synchronised.
-int take_stage_fault() {
-  int v = 0;
-  cudaError_t e = cudaMemcpyFromSymbol(&v, g_stage_fault, sizeof(int));
-  if (e != cudaSuccess) return (int)e;
-  if (v) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(g_stage_fault, &zero, sizeof(int));
-    return (int)cudaErrorLaunchTimeout;
-  }
-  return 0;
+                                                       retval, fault);
 }
 
 template <int NWA, int NWB>
 static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int nwords,
                         const int *WA, const int *WB, float *A, float *B, float lrate, float vexp,
-                        float *retval, const HotRows &hot, cudaStream_t stream) {
-  EvalScratch *scratch = nullptr;
-  if (eval) {
-    int err = eval_scratch(&scratch);
-    if (err) return err;
-  }
+                        float *retval, const HotRows &hot, EvalScratch *scratch, int *fault,
+                        cudaStream_t stream) {
   const int nr = (dim / 4 + 31) / 32;
   // rows of a column live in registers: (NWA + NWB) * nr vectors per lane, which
   // fits for up to 10 rows of 3 vectors or 15 rows of 2
@@ -1346,10 +1342,10 @@ static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int
     const int grid = std::max(1, std::min(device_sm_count(), (ncols + 8 * staged_warps - 1) / (8 * staged_warps)));
     cudaError_t e = cudaSuccess;
     switch (nr) {
-      case 1: e = launch_neg_staged_any<NWA, NWB, 1>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval); break;
-      case 2: e = launch_neg_staged_any<NWA, NWB, 2>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval); break;
-      case 3: e = launch_neg_staged_any<NWA, NWB, 3>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval); break;
-      default: e = launch_neg_staged_any<NWA, NWB, 4>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval); break;
+      case 1: e = launch_neg_staged_any<NWA, NWB, 1>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault); break;
+      case 2: e = launch_neg_staged_any<NWA, NWB, 2>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault); break;
+      case 3: e = launch_neg_staged_any<NWA, NWB, 3>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault); break;
+      default: e = launch_neg_staged_any<NWA, NWB, 4>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault); break;
     }
     if (e != cudaSuccess) return (int)e;
     if (!eval) fold_hot_rows(dim, hot, A, B, stream);
@@ -1386,116 +1382,33 @@ static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int
 
 static int neg_any(bool eval, int dim, int ncols, const int *ncols_dev, int nwords, int nwa,
                    int nwb, const int *WA, const int *WB, float *A, float *B, float lrate,
-                   float vexp, float *retval, const HotRows &hot, cudaStream_t stream) {
+                   float vexp, float *retval, const HotRows &hot, EvalScratch *scratch, int *fault,
+                   cudaStream_t stream) {
   if (ncols <= 0) return 0;
   if (dim <= 0) return 1;
   const int which = nwa * 10000 + nwb;
   switch (which) {
-    case 50001: return neg_dispatch<5, 1>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, stream);
-    case 50005: return neg_dispatch<5, 5>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, stream);
-    case 100005: return neg_dispatch<10, 5>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, stream);
-    case 50010: return neg_dispatch<5, 10>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, stream);
+    case 50001: return neg_dispatch<5, 1>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, scratch, fault, stream);
+    case 50005: return neg_dispatch<5, 5>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, scratch, fault, stream);
+    case 100005: return neg_dispatch<10, 5>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, scratch, fault, stream);
+    case 50010: return neg_dispatch<5, 10>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, scratch, fault, stream);
     default: return 1;
   }
 }
 
 int neg_update_async(int dim, int ncols, const int *ncols_dev, int nwords, int nwa, int nwb,
                      const int *WA, const int *WB, float *A, float *B, float lrate, float vexp,
-                     const HotRows &hot, cudaStream_t stream) {
+                     const HotRows &hot, int *fault, cudaStream_t stream) {
   return neg_any(false, dim, ncols, ncols_dev, nwords, nwa, nwb, WA, WB, A, B, lrate, vexp, nullptr,
-                 hot, stream);
+                 hot, nullptr, fault, stream);
 }
 
 int neg_eval_async(int dim, int ncols, const int *ncols_dev, int nwa, int nwb, const int *WA,
                    const int *WB, const float *A, const float *B, float *retval,
-                   cudaStream_t stream) {
+                   EvalScratch *scratch, int *fault, cudaStream_t stream) {
   return neg_any(true, dim, ncols, ncols_dev, 0x7fffffff, nwa, nwb, WA, WB, const_cast<float *>(A),
-                 const_cast<float *>(B), 0.f, 0.f, retval, hot_rows_at(nullptr, 0), stream);
-}
-
-// ---------------------------------------------------------------------------
-// Row-traffic probe: the memory side of the negative update or scoring with
-// the arithmetic left out, on the same columns.  MODE 0 adds a row of zeros to
-// every row of every column with the update kernel's atomic reductions (the
-// model is left as it was); MODE 1 reads every row.  The time of a launch is
-// what the memory system needs for the kernel's scatter or gather alone.
-// ---------------------------------------------------------------------------
-template <int NR, int MODE>
-__global__ void __launch_bounds__(512) row_probe_kernel(int dim, int ncols,
-                                                        const int *__restrict__ ncols_dev, int nwa,
-                                                        int nwb, const int *__restrict__ WA,
-                                                        const int *__restrict__ WB, float *A, float *B,
-                                                        HotRows hot, float *sink) {
-  const int lane = threadIdx.x & 31;
-  const int nvec = dim >> 2;
-  const bool tail = lane + 32 * (NR - 1) < nvec;
-  const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int nwarps = (gridDim.x * blockDim.x) >> 5;
-  if (ncols_dev) ncols = *ncols_dev;
-  PRow<NR> zero;
-  prow_zero(zero);
-  float seen = 0.f;
-  __shared__ __align__(16) float zero_row[MODE == 2 ? 32 * 4 * NR : 4];
-  if (MODE == 2) {
-    for (int k = threadIdx.x; k < 32 * 4 * NR; k += blockDim.x) zero_row[k] = 0.f;
-    async_proxy_fence();
-    __syncthreads();
-  }
-  int in_flight = 0;
-  for (int col = gwarp; col < ncols; col += nwarps) {
-    int myw = 0;
-    if (lane < nwa)
-      myw = WA[(int64_t)col * nwa + lane];
-    else if (lane < nwa + nwb)
-      myw = WB[(int64_t)col * nwb + (lane - nwa)];
-    for (int r = 0; r < nwa + nwb; r++) {
-      const int w = __shfl_sync(kFullMask, myw, r);
-      if (MODE == 0) {
-        float *dst = (r < nwa) ? update_target(A, hot.shadowA, hot, w, dim, gwarp)
-                               : update_target(B, hot.shadowB, hot, w, dim, gwarp);
-        prow_red_lane(dst + 4 * lane, tail, zero);
-      } else if (MODE == 2) {
-        // the same additions as one bulk reduction per row, issued by one lane
-        float *dst = (r < nwa) ? update_target(A, hot.shadowA, hot, w, dim, gwarp)
-                               : update_target(B, hot.shadowB, hot, w, dim, gwarp);
-        if (lane == 0) bulk_reduce_add_row(dst, zero_row, (unsigned)dim * 4u);
-      } else {
-        PRow<NR> row;
-        prow_load_lane(row, reinterpret_cast<const ulonglong2 *>((r < nwa ? A : B) + (int64_t)w * dim) + lane, tail);
-        seen += prow_dot_partial(row, row);
-      }
-    }
-    if (MODE == 2 && lane == 0) {
-      bulk_commit_group();
-      if (++in_flight > 4) bulk_wait_group_read<4>();
-    }
-  }
-  if (MODE == 2 && lane == 0) bulk_wait_group_all();
-  if (MODE == 1 && seen == -1.0f) *sink = seen;  // keeps the loads alive; never true
-}
-
-int row_probe_async(int dim, int ncols, const int *ncols_dev, int nwa, int nwb, const int *WA,
-                    const int *WB, float *A, float *B, const HotRows &hot, int mode, float *sink,
-                    cudaStream_t stream) {
-  if (ncols <= 0) return 0;
-  if (!vector_ok(dim, A, B) || nwa + nwb > 32 || mode < 0 || mode > 2) return 1;
-  const int nr = (dim / 4 + 31) / 32;
-  if (nr > 10) return 1;
-  // the scatter takes the same time with 16 to 128 warps per SM (4.02 - 4.16 ms on the benchmark
-  // workload); the gather needs the many warps
-  const int grid = device_sm_count() * 8;
-  if (mode == 0) {
-    W2V_NR_SWITCH(nr, (row_probe_kernel<NR, 0><<<grid, 512, 0, stream>>>(dim, ncols, ncols_dev, nwa, nwb, WA,
-                                                                       WB, A, B, hot, sink)));
-  } else if (mode == 1) {
-    W2V_NR_SWITCH(nr, (row_probe_kernel<NR, 1><<<grid, 512, 0, stream>>>(dim, ncols, ncols_dev, nwa, nwb, WA,
-                                                                       WB, A, B, hot, sink)));
-  } else {
-    W2V_NR_SWITCH(nr, (row_probe_kernel<NR, 2><<<grid, 512, 0, stream>>>(dim, ncols, ncols_dev, nwa, nwb, WA,
-                                                                       WB, A, B, hot, sink)));
-  }
-  count_launch(1);
-  return (int)cudaGetLastError();
+                 const_cast<float *>(B), 0.f, 0.f, retval, hot_rows_at(nullptr, 0), scratch, fault,
+                 stream);
 }
 
 bool neg_shape_supported(int nwa, int nwb) {
@@ -1512,14 +1425,38 @@ bool neg_shape_supported(int nwa, int nwb) {
 // cudaError_t; an unsupported shape prints a line and returns 1.
 // ---------------------------------------------------------------------------
 
-static int finish_sync(int launch_err) {
-  if (launch_err) return launch_err;
-  cudaError_t e = cudaStreamSynchronize(cudaStreamPerThread);
-  if (e != cudaSuccess) return (int)e;
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return (int)e;
-  return w2v::take_stage_fault();
-}
+namespace {
+
+// A scratch set borrowed from the device's pool for the duration of one launcher call.
+struct ScratchLease {
+  w2v::LaunchScratch *s = nullptr;
+  ~ScratchLease() { w2v::release_launch_scratch(s); }
+  int acquire() { return w2v::acquire_launch_scratch(&s); }
+  // Replica rows with the hot-word share of this launch's own word list, so that the
+  // folding period adapts to dense text as it does behind w2v_dobatch.
+  int hot_rows(const int *ids, int64_t n, int nwords, w2v::HotRows *out) {
+    *out = w2v::hot_rows_at(s->hot_buf, s->hot_buf ? w2v::hot_levels_default() : 0);
+    if (out->fold_every <= 0 || n <= 0) return 0;
+    out->stats = s->stats;
+    return w2v::count_hot_share_async(ids, n, nwords, s->stats, cudaStreamPerThread);
+  }
+  // Waits for the call's kernels; a staged kernel that gave up waiting for its copies has
+  // raised this call's own flag.
+  int finish(int launch_err) {
+    if (launch_err) return launch_err;
+    cudaError_t e = cudaStreamSynchronize(cudaStreamPerThread);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    if (*reinterpret_cast<volatile int *>(s->fault)) {
+      *s->fault = 0;
+      return (int)cudaErrorLaunchTimeout;
+    }
+    return 0;
+  }
+};
+
+}  // namespace
 
 extern "C" {
 
@@ -1533,37 +1470,42 @@ int word2vecPos(int nrows, int ncols, int shift, int *W, int *LB, int *UB, float
     printf("word2vecPos too many rows %d\n", nrows);
     return 1;
   }
-  w2v::HotRows hot;
-  int err = w2v::thread_hot_rows(&hot);
+  if (ncols <= 0) return 0;
+  ScratchLease lease;
+  int err = lease.acquire();
   if (err) return err;
-  return finish_sync(w2v::pos_update_async(nrows, ncols, nullptr, shift, W, LB, UB, A, B, lrate,
-                                           vexp, hot, cudaStreamPerThread));
+  w2v::HotRows hot;
+  err = lease.hot_rows(W, ncols, 0x7fffffff, &hot);
+  if (err) return err;
+  return lease.finish(w2v::pos_update_async(nrows, ncols, nullptr, shift, W, LB, UB, A, B, lrate,
+                                            vexp, hot, cudaStreamPerThread));
+}
+
+static int neg_launcher(int nrows, int ncols, int nwords, int nwa, int nwb, int *WA, int *WB,
+                        float *A, float *B, float lrate, float vexp) {
+  if (!w2v::neg_shape_supported(nwa, nwb)) {
+    printf("word2vec unsupport size combination %d %d\n", nwa, nwb);
+    return 1;
+  }
+  if (ncols <= 0) return 0;
+  ScratchLease lease;
+  int err = lease.acquire();
+  if (err) return err;
+  w2v::HotRows hot;
+  err = lease.hot_rows(WB, (int64_t)ncols * nwb, nwords, &hot);
+  if (err) return err;
+  return lease.finish(w2v::neg_update_async(nrows, ncols, nullptr, nwords, nwa, nwb, WA, WB, A, B,
+                                            lrate, vexp, hot, lease.s->fault, cudaStreamPerThread));
 }
 
 int word2vecNeg(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A, float *B,
                 float lrate, float vexp) {
-  if (!w2v::neg_shape_supported(nwa, nwb)) {
-    printf("word2vec unsupport size combination %d %d\n", nwa, nwb);
-    return 1;
-  }
-  w2v::HotRows hot;
-  int err = w2v::thread_hot_rows(&hot);
-  if (err) return err;
-  return finish_sync(w2v::neg_update_async(nrows, ncols, nullptr, 0x7fffffff, nwa, nwb, WA, WB, A,
-                                           B, lrate, vexp, hot, cudaStreamPerThread));
+  return neg_launcher(nrows, ncols, 0x7fffffff, nwa, nwb, WA, WB, A, B, lrate, vexp);
 }
 
 int word2vecNegFilt(int nrows, int ncols, int nwords, int nwa, int nwb, int *WA, int *WB, float *A,
                     float *B, float lrate, float vexp) {
-  if (!w2v::neg_shape_supported(nwa, nwb)) {
-    printf("word2vec unsupport size combination %d %d\n", nwa, nwb);
-    return 1;
-  }
-  w2v::HotRows hot;
-  int err = w2v::thread_hot_rows(&hot);
-  if (err) return err;
-  return finish_sync(w2v::neg_update_async(nrows, ncols, nullptr, nwords, nwa, nwb, WA, WB, A, B,
-                                           lrate, vexp, hot, cudaStreamPerThread));
+  return neg_launcher(nrows, ncols, nwords, nwa, nwb, WA, WB, A, B, lrate, vexp);
 }
 
 int word2vecEvalPos(int nrows, int ncols, int shift, int *W, int *LB, int *UB, float *A, float *B,
@@ -1576,8 +1518,12 @@ int word2vecEvalPos(int nrows, int ncols, int shift, int *W, int *LB, int *UB, f
     printf("word2vecEvalPos nrows too large %d\n", nrows);
     return 1;
   }
-  return finish_sync(w2v::pos_eval_async(nrows, ncols, nullptr, shift, W, LB, UB, A, B, Retval,
-                                         cudaStreamPerThread));
+  if (ncols <= 0) return 0;
+  ScratchLease lease;
+  int err = lease.acquire();
+  if (err) return err;
+  return lease.finish(w2v::pos_eval_async(nrows, ncols, nullptr, shift, W, LB, UB, A, B, Retval,
+                                          lease.s->eval, cudaStreamPerThread));
 }
 
 int word2vecEvalNeg(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A, float *B,
@@ -1586,8 +1532,12 @@ int word2vecEvalNeg(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, fl
     printf("word2vecEvalNeg unsupport size combination %d %d\n", nwa, nwb);
     return 1;
   }
-  return finish_sync(w2v::neg_eval_async(nrows, ncols, nullptr, nwa, nwb, WA, WB, A, B, Retval,
-                                         cudaStreamPerThread));
+  if (ncols <= 0) return 0;
+  ScratchLease lease;
+  int err = lease.acquire();
+  if (err) return err;
+  return lease.finish(w2v::neg_eval_async(nrows, ncols, nullptr, nwa, nwb, WA, WB, A, B, Retval,
+                                          lease.s->eval, lease.s->fault, cudaStreamPerThread));
 }
 
 long long w2v_launch_count(void) { return w2v::launch_count(); }

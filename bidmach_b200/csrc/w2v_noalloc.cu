@@ -5,11 +5,10 @@
 // its own device-memory cache and is routinely sized to fill the card, so a
 // cudaMalloc issued by a native library in the middle of a run can fail or
 // take memory the cache counted on.  The same holds for serving processes that
-// freeze their memory map after warm-up, and for callers that record their
-// work into a CUDA stream capture, inside which allocation calls are illegal.
-// The regular scoring entry points keep a small accumulator that they obtain
-// with cudaMalloc on first use; this one takes none: its scratch memory is a
-// fixed array compiled into the library's device image.
+// freeze their memory map after warm-up.  The regular scoring entry points
+// borrow a small accumulator from a pool that grows with cudaMalloc when every
+// set is in use; this one takes none: its scratch memory is a fixed array
+// compiled into the library's device image.
 //
 // What that costs.  The array (kScratchBytes, about 64 KiB) exists on every GPU
 // that loads the library, for the life of the process, whether or not this
@@ -25,13 +24,14 @@
 //
 // Set-up.  In host code the array's name is only a handle; the device address
 // that a kernel can use comes from cudaGetSymbolAddress, once per device, with
-// that device current.  The first call on each device does this; make that
-// first call outside any stream capture.
+// that device current.  The first call on each device does this.  Like the
+// other launchers the function runs on the calling thread's default stream and
+// waits for the kernel before it returns.
 //
 // Results.  Each block sums its own columns in double; the block that finishes
 // last adds the partial sums in slot order, so the total does not depend on
 // the order in which blocks finish.  It equals word2vecEvalNeg's up to the
-// order of double additions.
+// order of double additions; a negative word id counts as a zero row, as there.
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -82,9 +82,9 @@ __global__ void __launch_bounds__(kThreads)
     for (int c = lane; c < dim; c += 32) {
       float av[NWA], bv[NWB];
 #pragma unroll
-      for (int j = 0; j < NWA; j++) av[j] = A[(int64_t)wa[j] * dim + c];
+      for (int j = 0; j < NWA; j++) av[j] = (wa[j] >= 0) ? A[(int64_t)wa[j] * dim + c] : 0.f;
 #pragma unroll
-      for (int k = 0; k < NWB; k++) bv[k] = B[(int64_t)wb[k] * dim + c];
+      for (int k = 0; k < NWB; k++) bv[k] = (wb[k] >= 0) ? B[(int64_t)wb[k] * dim + c] : 0.f;
 #pragma unroll
       for (int j = 0; j < NWA; j++)
 #pragma unroll

@@ -61,6 +61,9 @@ class LearnerOpts:
     updateAll: bool = False
     syncStep: int = 2
     overlapSync: bool = False   # not in the reference: exchange beside the next minibatch
+    exchange: str = "auto"      # "nvls": average in place through the NVLink multicast mapping of the
+                                # model buffer (w2v_nvls_average); "nccl": all-reduce; "auto": nvls where
+                                # the platform has symmetric memory with multicast, else nccl
     headSync: bool = False      # the reference's schedule: syncs average a growing head of the vocabulary
     checkPointFile: str | None = None   # e.g. "ckpt/w2v%03d/": a checkpoint directory per number
     checkPointInterval: float = 0.0     # in passes over the data (Learner.scala:1074-1077)
@@ -119,9 +122,16 @@ class Learner:
         self._next_ckpt = self.opts.nextCheckPoint
         while self.ipass < self.opts.npasses:
             self.nextPass()
-        if self.opts.checkPointFile is not None:        # Learner.wrapUp (Learner.scala:258-259)
+        self._before_wrapup()
+        if self.opts.checkPointFile is not None and self._writes_checkpoints():   # Learner.wrapUp (Learner.scala:258-259)
             self.model.save(self.opts.checkPointFile % self._next_ckpt)
         return self
+
+    def _before_wrapup(self):
+        pass
+
+    def _writes_checkpoints(self) -> bool:
+        return True
 
     def loadCheckPoint(self, checkPointNumber: int = -1):
         """Learner.loadCheckPoint (Learner.scala:397-425): loads the given checkpoint, or
@@ -189,11 +199,12 @@ class Learner:
             if o.checkPointFile is not None and \
                     self.ipass + dsp > o.checkPointInterval * (1 + self._next_ckpt - o.nextCheckPoint):
                 # Learner.scala:242-249: save, then drop the checkpoint keepCheckPoints back
-                self.model.save(o.checkPointFile % self._next_ckpt)
                 old = self._next_ckpt - o.keepCheckPoints
+                if self._writes_checkpoints():
+                    self.model.save(o.checkPointFile % self._next_ckpt)
+                    if o.keepCheckPoints > 0 and old >= 0:
+                        self.model.delete(o.checkPointFile % old)
                 self._next_ckpt += 1
-                if o.keepCheckPoints > 0 and old >= 0:
-                    self.model.delete(o.checkPointFile % old)
         self.ipass += 1
 
     def predict(self, datasource: MatSource) -> list[float]:
@@ -227,6 +238,10 @@ class ParLearner(Learner):
         import torch.distributed as dist
         super().init()
         if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            if self.opts.exchange in ("auto", "nvls") and not self.opts.headSync \
+                    and dist.get_backend(self.group) == "nccl":
+                if not self.model.enableSymmetric(self.group) and self.opts.exchange == "nvls":
+                    raise RuntimeError("exchange='nvls': no symmetric memory with a multicast mapping here")
             for m in self.model.modelmats:
                 dist.broadcast(m, src=dist.get_global_rank(self.group, 0) if self.group else 0,
                                group=self.group)
@@ -260,8 +275,12 @@ class ParLearner(Learner):
             self.model.mergeModelFn(self.group)
             self._since_sync = 0
 
-    def train(self, do_init: bool = True):
-        super().train(do_init)
+    def _before_wrapup(self):
+        # an exchange still in flight belongs to the model that the wrap-up checkpoint holds
         if self.opts.overlapSync:
             self.model.finishMerge()
-        return self
+
+    def _writes_checkpoints(self) -> bool:
+        # the replicas share one checkpoint path: rank 0 writes and deletes, the others keep count
+        import torch.distributed as dist
+        return not dist.is_initialized() or dist.get_rank(self.group) == 0

@@ -98,6 +98,9 @@ class Word2Vec:
         self._batches = 0
         self._flat = None
         self._merge = None   # state of an averaging exchange in flight
+        self._mc = 0         # NVLink multicast address of the model buffer (0: not in symmetric memory)
+        self._symm = None
+        self._tick = None
 
     # -- life cycle ---------------------------------------------------------
     def init(self, ncols: int, refresh: bool = True):
@@ -288,6 +291,11 @@ class Word2Vec:
             if rows < self.opts.vocabSize:
                 mats = flat if flat is not None else self.modelmats
                 bufs = [mats[j][:rows] for j in range(2)]   # the head of a matrix is contiguous
+        if getattr(self, "_mc", 0) and istep <= 0:
+            # the model lives in symmetric memory: one multimem kernel per replica, fenced by two
+            # one-element collectives (all replicas done updating / all slices written)
+            self._nvls_average(group, 0)
+            return
         avg = dist.ReduceOp.AVG if dist.get_backend(group) == "nccl" else None
         for m in bufs:
             if avg is not None:
@@ -296,18 +304,90 @@ class Word2Vec:
                 dist.all_reduce(m, op=dist.ReduceOp.SUM, group=group)
                 m.mul_(1.0 / dist.get_world_size(group))
 
+    # SMs the overlapped NVLS average runs on, per replica count: a replica pulls 1/world of the
+    # buffer through the switch, so fewer SMs keep up as the job grows
+    NVLS_BLOCKS = {2: 24, 3: 16, 4: 12}
+
+    def enableSymmetric(self, group=None) -> bool:
+        """Moves the model into symmetric memory mapped on every replica's GPU through an NVLink
+        multicast address, so that the exchange can run as w2v_nvls_average.  Collective: every
+        rank of ``group`` calls it.  Returns False (and changes nothing) where the platform offers
+        no multicast mapping; the exchange then stays with NCCL."""
+        import torch.distributed as dist
+        if getattr(self, "_mc", 0):
+            return True
+        if not dist.is_initialized() or dist.get_world_size(group) == 1 or self._flat is None:
+            return False
+        ok, hdl, buf = 1, None, None
+        try:
+            import torch.distributed._symmetric_memory as symm
+            buf = symm.empty(self._flat.numel(), dtype=torch.float32, device=self.device)
+            hdl = symm.rendezvous(buf, group=group if group is not None else dist.group.WORLD)
+            if not int(getattr(hdl, "multicast_ptr", 0) or 0):
+                ok = 0
+        except Exception as e:   # no symmetric memory here: say why, stay with NCCL
+            self._symm_error = repr(e)
+            ok = 0
+        flag = torch.tensor([ok], dtype=torch.int32, device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        if int(flag.item()) == 0:
+            return False
+        buf.copy_(self._flat.view(-1))
+        self._flat = buf.view(2, self.opts.vocabSize, self.opts.dim)
+        self.modelmats = [self._flat[0], self._flat[1]]
+        self._symm, self._mc = hdl, int(hdl.multicast_ptr)
+        self._tick = torch.zeros(1, dtype=torch.float32, device=self.device)
+        return True
+
+    def _nvls_average(self, group, blocks: int):
+        """Enqueues fence, w2v_nvls_average, fence on the current stream."""
+        import torch.distributed as dist
+        dist.all_reduce(self._tick, group=group)     # every replica has finished its updates
+        with torch.cuda.device(self.device):
+            _check(_lib.load().w2v_nvls_average(self._mc, self._flat.numel(), dist.get_rank(group),
+                                                dist.get_world_size(group), blocks, self._stream()),
+                   "w2v_nvls_average")
+        dist.all_reduce(self._tick, group=group)     # every replica's slice has been written everywhere
+
+    def reserveSMs(self, sms: int):
+        """Keeps ``sms`` SMs out of the grids of the following minibatches' update kernels (0 = use
+        all), so that a kernel on another stream finds room."""
+        with torch.cuda.device(self.device):
+            _check(_lib.load().w2v_reserve_sms(self._ctx, int(sms)), "w2v_reserve_sms")
+
     def startMerge(self, group=None):
-        """Overlapped form of mergeModelFn: snapshots the model, starts the
-        all-reduce of the snapshot on a side stream and returns; training goes
-        on.  ``finishMerge`` (called by the learner one minibatch later, or by the
-        next start) adds ``average - snapshot`` to the live model, so updates made
-        while the exchange was in flight are kept.  Needs two extra model-sized
-        buffers."""
+        """Overlapped form of mergeModelFn; training goes on while the exchange runs on a side
+        stream, and ``finishMerge`` (called by the learner one minibatch later, or by the next
+        start) makes the compute stream wait for it.
+
+        With the model in symmetric memory the average is taken in place by w2v_nvls_average on a
+        few SMs (the update kernels of the next minibatch leave them free): an element is read on
+        all replicas, averaged and written back within microseconds, so it keeps every update
+        made before and after that moment and loses only those that land in between.  Otherwise
+        the model is snapshotted, the snapshot averaged with NCCL, and ``finishMerge`` adds
+        ``average - snapshot`` to the live model (two extra model-sized buffers)."""
         import torch.distributed as dist
         if not dist.is_initialized() or dist.get_world_size(group) == 1:
             return
         self.finishMerge()
         world = dist.get_world_size(group)
+        if getattr(self, "_mc", 0):
+            if getattr(self, "_comm", None) is None:
+                self._comm = torch.cuda.Stream(device=self.device, priority=-1)
+            compute = torch.cuda.current_stream(self.device)
+            taken = torch.cuda.Event()
+            taken.record(compute)
+            blocks = self.NVLS_BLOCKS.get(world, 8)
+            with torch.cuda.stream(self._comm):
+                self._comm.wait_event(taken)
+                self._nvls_average(group, blocks)
+                done = torch.cuda.Event()
+                done.record(self._comm)
+            self.reserveSMs(blocks)
+            self._merge = done
+            self._merge_inplace = True
+            return
+        self._merge_inplace = False
         n = self._flat.numel()
         if getattr(self, "_snap", None) is None:
             self._snap = torch.empty_like(self._flat)
@@ -319,16 +399,20 @@ class Word2Vec:
         self._snap.copy_(self._flat)
         taken = torch.cuda.Event()
         taken.record(compute)
+        nccl = dist.get_backend(group) == "nccl"   # other backends have no AVG: sum, then scale
+        op = dist.ReduceOp.AVG if nccl else dist.ReduceOp.SUM
         with torch.cuda.stream(self._comm):
             self._comm.wait_event(taken)
-            if self._shard is not None:
+            if self._shard is not None and nccl:
                 # all-reduce as reduce-scatter + all-gather: both out of place, so the
                 # snapshot survives without a second model-sized copy
-                dist.reduce_scatter_tensor(self._shard, self._snap.view(-1), op=dist.ReduceOp.AVG, group=group)
+                dist.reduce_scatter_tensor(self._shard, self._snap.view(-1), op=op, group=group)
                 dist.all_gather_into_tensor(self._avg.view(-1), self._shard, group=group)
             else:
                 self._avg.copy_(self._snap)
-                dist.all_reduce(self._avg, op=dist.ReduceOp.AVG, group=group)
+                dist.all_reduce(self._avg, op=op, group=group)
+                if not nccl:
+                    self._avg.mul_(1.0 / world)
             done = torch.cuda.Event()
             done.record(self._comm)
         self._merge = done
@@ -339,6 +423,9 @@ class Word2Vec:
         compute = torch.cuda.current_stream(self.device)
         compute.wait_event(self._merge)
         self._merge = None
+        if getattr(self, "_merge_inplace", False):
+            self.reserveSMs(0)
+            return
         with torch.cuda.device(self.device):
             _check(_lib.load().w2v_apply_average(self._flat.data_ptr(), self._snap.data_ptr(),
                                                  self._avg.data_ptr(), self._flat.numel(),

@@ -32,7 +32,11 @@ extern "C" {
  * Part 1 -- launchers with the reference's prototypes.
  * Each runs on the calling thread's default stream and returns after the
  * kernel has finished (the reference synchronises the same way,
- * jni/src/DNN127.cu:1417-1419).
+ * jni/src/DNN127.cu:1417-1419).  A call borrows a few MB of scratch memory from
+ * a per-device pool; the pool allocates (cudaMalloc) only while more calls are
+ * in flight on that device than ever before, so a host with one thread per GPU
+ * sees one allocation per GPU for the life of the process, however many
+ * threads come and go.
  * ---------------------------------------------------------------------- */
 
 /* Replaces word2vecPos, jni/include/MatKernel.hpp:77 (launcher
@@ -70,14 +74,14 @@ int word2vecEvalNeg(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, fl
 
 /* No counterpart in the reference.  Same contract as word2vecEvalNeg, for
  * hosts that must not allocate device memory while they run (a JVM whose matrix
- * cache already owns the card, a process that froze its memory map, work being
- * recorded into a stream capture): the partial sums live in an array built into
- * the library's device image (about 64 KiB on every GPU that loads the library)
- * instead of a buffer obtained with cudaMalloc.  At most 2,097,152 columns per
- * call; a larger ncols prints a message and returns 1.  The first call on a
- * device looks up the array's device address and should therefore be made
- * outside any stream capture.  Calls on the same GPU share the array: do not
- * let two of them run at the same time. */
+ * cache already owns the card, a process that froze its memory map): the
+ * partial sums live in an array built into the library's device image (about
+ * 64 KiB on every GPU that loads the library) instead of a buffer obtained with
+ * cudaMalloc.  At most 2,097,152 columns per call; a larger ncols prints a
+ * message and returns 1.  The first call on a device looks up the array's
+ * device address.  The function waits for its kernel, like the launchers
+ * above.  Calls on the same GPU share the array: do not let two of them run at
+ * the same time. */
 int word2vecEvalNegNoAlloc(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A,
                            float *B, float *Retval);
 
@@ -242,6 +246,57 @@ int w2v_dobatch_host(w2v_ctx *ctx, const int *tokens_host, float *A, float *B, i
 int w2v_evalbatch_host(w2v_ctx *ctx, const int *tokens_host, const float *A, const float *B,
                        uint64_t batch_id, double *score_host, void *stream);
 
+/* ---- model exchange between replicas (multi-GPU) --------------------------
+ * Replaces Word2Vec.mergeModelFn (networks/Word2Vec.scala:547-568), which
+ * averages the model matrices of all GPUs through host-driven peer copies, and
+ * ParLearner.syncmodels that calls it (Learner.scala:655).
+ *
+ * For a host with one thread per GPU in one process (the reference's ParLearner,
+ * Learner.scala:589-655) or one process per GPU: a communicator per GPU, then
+ * w2v_allreduce_avg on every replica at the same point of its minibatch
+ * sequence.  NCCL (libnccl.so.2) is loaded at run time; without it these
+ * return 2.  Other errors: 1 for bad arguments, a cudaError_t, or 2000 + the
+ * ncclResult_t. */
+typedef struct w2v_comm w2v_comm;
+/* One process, ndev devices (null `devices` = 0..ndev-1): comms[i] belongs to
+ * devices[i] and is to be used by the thread that drives that GPU. */
+int w2v_comm_init_all(int ndev, const int *devices, w2v_comm **comms);
+/* One process per GPU: rank 0 fills a 128-byte id with w2v_comm_unique_id and
+ * hands it to the other ranks (any channel); every rank then calls
+ * w2v_comm_init_rank with its device current. */
+int w2v_comm_unique_id(void *id128);
+int w2v_comm_init_rank(int nranks, int rank, const void *id128, w2v_comm **out);
+/* Optional: registers the model buffer with the communicator, so that NCCL can
+ * run the collective on the buffer in place (NVLink SHARP / zero copy) instead
+ * of staging it.  The buffer stays the caller's. */
+int w2v_comm_register(w2v_comm *comm, void *buf, int64_t bytes);
+/* A[i] and B[i] (n_each floats each, device memory of the communicator's GPU)
+ * become their mean over all replicas, in place, enqueued on `stream`.  When
+ * B == A + n_each the two matrices travel as one collective. */
+int w2v_allreduce_avg(w2v_comm *comm, float *A, float *B, int64_t n_each, void *stream);
+void w2v_comm_destroy(w2v_comm *comm);
+
+/* The same average without NCCL, for a buffer that is mapped on every replica's
+ * GPU through an NVLink multicast address (symmetric memory of one process per
+ * GPU): replica `rank` of `world` averages its 1/world slice of the n floats
+ * with multimem.ld_reduce (the NVSwitch adds the replicas' values) and
+ * multimem.st (the mean goes back to every replica).  `mc_base` is the
+ * multicast address of the first float, 16-byte aligned, n a multiple of 4.
+ * `blocks` limits the kernel to that many SMs (0 = all), so that it can run
+ * beside the update kernels of the next minibatch.  The kernel waits for
+ * nobody: the caller orders it after every replica's last update (a barrier or
+ * any collective on the same stream) unless it accepts the relaxed form below.
+ * Concurrent use: an update that lands on an element between the kernel's read
+ * and its write of that element (a few microseconds) is overwritten by the
+ * mean; updates before are averaged in, updates after are kept. */
+int w2v_nvls_average(float *mc_base, int64_t n, int rank, int world, int blocks, void *stream);
+
+/* Keeps `sms` SMs out of the grids of the update kernels that the following
+ * w2v_dobatch / w2v_dobatch_host calls launch (0 = use every SM again), so that
+ * a kernel on another stream -- the overlapped w2v_nvls_average -- finds free
+ * SMs while a minibatch trains. */
+int w2v_reserve_sms(w2v_ctx *ctx, int sms);
+
 /* Second half of an overlapped model average (multi-GPU): the caller snapshots
  * its replica into `base`, averages the snapshots of all replicas into `avg`
  * with an all-reduce that runs beside the following minibatches, and then
@@ -264,16 +319,6 @@ typedef struct w2v_timing {
 } w2v_timing;
 int w2v_set_timing(w2v_ctx *ctx, int on);
 int w2v_get_timing(w2v_ctx *ctx, w2v_timing *out); /* synchronises the last stream used */
-
-/* Diagnostic: the memory side of the negative kernels alone, on the columns of
- * the latest w2v_wordmats.  mode 0: a row of zeros is added to every row of
- * every column with the update kernel's atomic reductions (A and B keep their
- * values); mode 1: every row is read; mode 2: as mode 0 with one bulk
- * reduction (shared -> global, add.f32) per row in place of the per-lane
- * reductions.  The duration of the call's kernel is
- * what the memory system needs for the scatter (the gather) of one negative
- * update (scoring) launch: the bound bench.py --mode bound reports. */
-int w2v_probe_rows(w2v_ctx *ctx, float *A, float *B, int mode, void *stream);
 
 /* Number of kernels this library has launched in this process (all threads). */
 long long w2v_launch_count(void);

@@ -21,7 +21,8 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("BIDMACH_REFERENCE", "/root/reference")
+# a BIDMach checkout: $BIDMACH_REFERENCE, else a directory "reference" beside this repository
+REF_ROOT = os.environ.get("BIDMACH_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 REF_SRC = os.path.join(REF_ROOT, "jni", "src", "BIDMach_CPUMACH.c")
 
 ORACLE_SO = os.path.join(HERE, "libw2v_oracle.so")

@@ -82,6 +82,16 @@ def have_reference() -> bool:
     return ref_lib() is not None
 
 
+def set_threads(n: int) -> int:
+    """Fixes the OpenMP team size of both back ends (they share one OpenMP runtime) and returns
+    the number of threads a parallel region then really runs with."""
+    got = int(port_lib().orc_set_threads(C.c_int(n)))
+    ref = ref_lib()
+    if ref is not None and hasattr(ref, "ref_set_threads"):
+        got = int(ref.ref_set_threads(C.c_int(n)))
+    return got
+
+
 def _i32(a):
     a = np.ascontiguousarray(a, dtype=np.int32)
     return a

@@ -18,6 +18,7 @@
  * the Scala code in w2v_oracle.c.
  */
 #include <jni.h>
+#include <omp.h>
 
 static void *drv_get_critical(JNIEnv *env, jarray arr, jboolean *is_copy) {
   (void)env;
@@ -82,4 +83,19 @@ double ref_word2vecEvalNeg(int nrows, int ncols, int nwa, int nwb, int *WA, int 
   JNIEnv env = &drv_table;
   return Java_edu_berkeley_bid_CPUMACH_word2vecEvalNeg(&env, 0, nrows, ncols, nwa, nwb,
                                                        WA, WB, A, B, nthreads);
+}
+
+/* The reference runs its chunks under "#pragma omp parallel for" with as many chunks as
+ * `nthreads`; how many of them run at once is OpenMP's decision (OMP_NUM_THREADS, which
+ * launchers such as torch.distributed.run set to 1).  ref_set_threads fixes the team size
+ * and returns the size of the team a parallel region then really gets. */
+int ref_set_threads(int n) {
+  int got = 0;
+  if (n > 0) omp_set_num_threads(n);
+#pragma omp parallel
+  {
+#pragma omp single
+    got = omp_get_num_threads();
+  }
+  return got;
 }

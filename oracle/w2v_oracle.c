@@ -19,6 +19,7 @@
  * and race on shared rows without synchronisation, as the reference does.
  */
 #include <math.h>
+#include <omp.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -293,4 +294,18 @@ ORC_API void orc_negative_ids(int64_t n, const float *u, float expt, int vocab, 
     int id = (v >= 2147483647.0) ? 2147483647 : (int)v;
     out[i] = id < vocab - 1 ? id : vocab - 1;
   }
+}
+
+/* Size of the OpenMP team the chunked loops above really get: launchers such as
+ * torch.distributed.run export OMP_NUM_THREADS=1, under which `nthreads` chunks run one
+ * after the other.  n > 0 sets the team size first. */
+ORC_API int orc_set_threads(int n) {
+  int got = 0;
+  if (n > 0) omp_set_num_threads(n);
+#pragma omp parallel
+  {
+#pragma omp single
+    got = omp_get_num_threads();
+  }
+  return got;
 }

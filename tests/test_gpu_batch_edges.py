@@ -98,23 +98,26 @@ def test_unsupported_options_are_refused():
 
 
 def test_row_probe_leaves_the_model_unchanged():
-    """w2v_probe_rows: the memory side of the negative kernels alone (zeros added with
-    the update kernel's reductions or with bulk reductions, or rows read); a diagnostic, so the model must come
-    out bit for bit as it went in."""
+    """The benchmark's row-traffic probe (a library of its own, libw2vrowprobe.so): zeros added
+    with the update kernel's reductions, or rows read; the model must come out bit for bit as it
+    went in."""
+    import ctypes as C
+    import os
     from bidmach_b200 import _lib
     n = 3000
     m = _model(n, dim=300)
     toks = torch.from_numpy(_toks(n, 500, seed=4, doc=37)).cuda()
-    m.dobatch([toks], 0, n)                      # non-trivial matrices, replicas used
-    m.wordMats([toks], batch_id=9)
+    m.dobatch([toks], 0, n)                      # non-trivial matrices
+    _, _, _, wa, wb = m.wordMats([toks], batch_id=9)
     before = [x.clone() for x in m.modelmats]
-    lib = _lib.load()
-    for mode in (0, 1, 2):
-        assert lib.w2v_probe_rows(m._ctx, m.modelmats[1].data_ptr(), m.modelmats[0].data_ptr(), mode,
-                                  m._stream()) == 0
+    probe = C.CDLL(os.path.join(os.path.dirname(_lib.LIB_PATH), "libw2vrowprobe.so"))
+    probe.w2v_rowprobe.argtypes = [C.c_int] * 4 + [C.c_void_p] * 4 + [C.c_int, C.c_void_p]
+    args = (300, wa.shape[0], 5, 5, wa.data_ptr(), wb.data_ptr(), m.modelmats[1].data_ptr(), m.modelmats[0].data_ptr())
+    for mode in (0, 1):
+        assert probe.w2v_rowprobe(*args, mode, m._stream()) == 0
     torch.cuda.synchronize()
     assert all(torch.equal(a, b) for a, b in zip(before, m.modelmats))
-    assert lib.w2v_probe_rows(m._ctx, m.modelmats[1].data_ptr(), m.modelmats[0].data_ptr(), 7, m._stream()) == 1
+    assert probe.w2v_rowprobe(*args, 7, m._stream()) == 1
 
 
 def test_jni_binders_of_the_whole_minibatch_calls():

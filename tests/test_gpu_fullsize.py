@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import conflict_free_neg, conflict_free_pos, rel_err
+from helpers import conflict_free_neg, conflict_free_pos, elem_rel_err, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -44,9 +44,29 @@ def test_neg_conflict_free_200k_columns_matches_oracle(oracle, big_model):
     assert CUMACH.word2vecNeg(D, G, 5, 5, dev(WA), dev(WB), dA, dB, 0.02, 0.5) == 0
     gA, gB = dA.cpu().numpy(), dB.cpu().numpy()
     assert rel_err(gA - A, A_ref - A) <= 1e-5 and rel_err(gB - B, B_ref - B) <= 1e-5
+    rows = WA.ravel()[:50_000]
+    assert elem_rel_err(gA[rows] - A[rows], A_ref[rows] - A[rows]) <= 1e-4
     touched = np.zeros(V, bool)
     touched[WA.ravel()] = True
     assert np.array_equal(gA[~touched], A[~touched])
+
+
+@pytest.mark.parametrize("nwa,nwb,G", [(5, 10, 100_000), (5, 1, 200_000)])
+def test_neg_other_shapes_conflict_free_at_vocab_1m(oracle, big_model, nwa, nwb, G):
+    """The (5,10) and (5,1) column shapes of the reference's table (jni/src/DNN127.cu:1423-1452)
+    at the benchmark's vocabulary and row width, as many conflict-free columns as it allows."""
+    from bidmach_b200 import CUMACH
+    A, B = big_model
+    WA, WB = conflict_free_neg(G, V, nwa, nwb, 7 + nwb)
+    A_ref, B_ref = A.copy(), B.copy()
+    oracle.word2vecNeg(D, G, nwa, nwb, WA, WB, A_ref, B_ref, 0.02, 0.5, THREADS)
+    dA, dB = dev(A), dev(B)
+    assert CUMACH.word2vecNeg(D, G, nwa, nwb, dev(WA), dev(WB), dA, dB, 0.02, 0.5) == 0
+    gA, gB = dA.cpu().numpy(), dB.cpu().numpy()
+    assert rel_err(gA - A, A_ref - A) <= 1e-5 and rel_err(gB - B, B_ref - B) <= 1e-5
+    ra, rb = WA.ravel()[:50_000], WB.ravel()[:50_000]
+    assert elem_rel_err(gA[ra] - A[ra], A_ref[ra] - A[ra]) <= 1e-4
+    assert elem_rel_err(gB[rb] - B[rb], B_ref[rb] - B[rb]) <= 1e-4
 
 
 def test_pos_conflict_free_1m_tokens_matches_oracle(oracle, big_model):
@@ -57,8 +77,12 @@ def test_pos_conflict_free_1m_tokens_matches_oracle(oracle, big_model):
     oracle.word2vecPos(D, N, 5, W, LB, UB, A_ref, B_ref, 0.05, 0.5, 1)
     dA, dB = dev(A), dev(B)
     assert CUMACH.word2vecPos(D, N, 5, dev(W), dev(LB), dev(UB), dA, dB, 0.05, 0.5) == 0
-    assert rel_err(dA.cpu().numpy() - A, A_ref - A) <= 1e-5
-    assert rel_err(dB.cpu().numpy() - B, B_ref - B) <= 1e-5
+    gA, gB = dA.cpu().numpy(), dB.cpu().numpy()
+    assert rel_err(gA - A, A_ref - A) <= 1e-5
+    assert rel_err(gB - B, B_ref - B) <= 1e-5
+    rows = W[W >= 0][:50_000]
+    assert elem_rel_err(gA[rows] - A[rows], A_ref[rows] - A[rows]) <= 1e-4
+    assert elem_rel_err(gB[rows] - B[rows], B_ref[rows] - B[rows]) <= 1e-4
 
 
 def test_full_minibatch_preprocessing_properties(oracle):
@@ -216,3 +240,102 @@ def test_dense_text_at_the_script_rate_stays_bounded():
     assert torch.isfinite(m.modelmats[0]).all() and torch.isfinite(m.modelmats[1]).all()
     assert float(m.modelmats[0].abs().max()) < 100 and float(m.modelmats[1].abs().max()) < 100
     assert m.evalbatch([pool[0]], 0, N) > -10.0
+
+
+def test_ten_heldout_minibatches_score_like_the_oracle(oracle, big_model):
+    """The scoring path of BASELINE configs[2] over ten held-out 1M-token minibatches with fixed
+    random matrices: every minibatch's positive sum, negative sum and score agree with the CPU
+    oracle (on the word lists the library produced) to 1e-5 relative."""
+    from bidmach_b200 import Word2Vec
+    from bidmach_b200.corpus import zipf_cdf, zipf_corpus
+    from bidmach_b200.word2vec import Opts
+    A, B = big_model
+    o = Opts(dim=D, vocabSize=V, wsample=1.0, seed=31)
+    model = Word2Vec(o).init(N)
+    model.modelmats[0].copy_(dev(B) * 0.02)
+    model.modelmats[1].copy_(dev(A) * 0.02)
+    As, Bs = model.modelmats[1].cpu().numpy(), model.modelmats[0].cpu().numpy()
+    cdf = zipf_cdf(V, 1.07)
+    for k in range(10):
+        toks = zipf_corpus(V, N, 1.07, seed=700 + k, doc_len=1000, cdf=cdf, first_doc=1000 * k)
+        dt = dev(toks)
+        # evalbatch numbers its minibatches itself; wordMats with the same id reproduces its lists
+        score = model.evalbatch([dt], 0, N)
+        words, lb, ub, wa, wb = model.wordMats([dt], batch_id=model._batches)
+        want_pos = oracle.word2vecEvalPos(D, N, 5, words.cpu().numpy(), lb.cpu().numpy(), ub.cpu().numpy(),
+                                          As, Bs, THREADS)
+        want_neg = oracle.word2vecEvalNeg(D, wa.shape[0], 5, 5, wa.cpu().numpy(), wb.cpu().numpy(), As, Bs,
+                                          THREADS)
+        want = oracle.eval_score(want_pos, want_neg, 5, wb.numel())
+        assert abs(score - want) <= 1e-5 * abs(want), (k, score, want)
+        epos = model.evalPositives(5, words, lb, ub, model.modelmats[1], model.modelmats[0])
+        eneg = model.evalNegatives(5, 5, wa, wb, model.modelmats[1], model.modelmats[0])
+        assert abs(epos - want_pos) <= 1e-5 * abs(want_pos) and abs(eneg - want_neg) <= 1e-5 * abs(want_neg)
+
+
+@pytest.fixture(scope="module")
+def model_3m():
+    """Both matrices of BASELINE configs[4]'s shape: vocab 3M, dim 300 (3.6 GB each)."""
+    V3 = 3_000_000
+    rng = np.random.default_rng(2)
+    A = np.empty((V3, D), np.float32)
+    B = np.empty((V3, D), np.float32)
+    for M in (A, B):
+        rng.random(out=M, dtype=np.float32)
+        M -= np.float32(0.5)
+        M *= np.float32(0.5)
+    return A, B
+
+
+def test_neg_10_5_conflict_free_300k_columns_at_vocab_3m(oracle, model_3m):
+    """configs[4]'s kernel shape at its size: 10 negatives + 5 contexts per column, vocab 3M,
+    dim 300; 300k columns use all 3M ids once as a negative."""
+    from bidmach_b200 import CUMACH
+    A, B = model_3m
+    V3, G = A.shape[0], 300_000
+    WA, WB = conflict_free_neg(G, V3, 10, 5, 13)
+    ra, rb = WA.ravel(), WB.ravel()
+    want_a, want_b = A[ra].copy(), B[rb].copy()
+    # the oracle works in place: keep the touched rows only, run, read the deltas, restore
+    oracle.word2vecNeg(D, G, 10, 5, WA, WB, A, B, 0.02, 0.5, THREADS)
+    want_a, A[ra] = A[ra] - want_a, want_a
+    want_b, B[rb] = B[rb] - want_b, want_b
+    dA, dB = dev(A), dev(B)
+    assert CUMACH.word2vecNeg(D, G, 10, 5, dev(WA), dev(WB), dA, dB, 0.02, 0.5) == 0
+    ia, ib = dev(ra.astype(np.int64)), dev(rb.astype(np.int64))
+    got_a = (dA[ia] - dev(A[ra])).cpu().numpy()
+    got_b = (dB[ib] - dev(B[rb])).cpu().numpy()
+    assert rel_err(got_a, want_a) <= 1e-5 and rel_err(got_b, want_b) <= 1e-5
+    assert elem_rel_err(got_a[:50_000], want_a[:50_000]) <= 1e-4
+    # rows of B that no column names are bit for bit what they were
+    untouched = np.ones(V3, bool)
+    untouched[rb] = False
+    sample = np.flatnonzero(untouched)[:: 37]
+    assert np.array_equal(dB[dev(sample)].cpu().numpy(), B[sample])
+
+
+def test_eval_neg_10_5_on_a_real_minibatch_at_vocab_3m(oracle, model_3m):
+    """word2vecEvalNeg with 10 negatives on the columns of a real (conflicting) 1M-token
+    minibatch at vocab 3M, against the CPU oracle to 1e-5 relative."""
+    from bidmach_b200 import Word2Vec
+    from bidmach_b200.corpus import zipf_corpus
+    from bidmach_b200.word2vec import Opts
+    A, B = model_3m
+    V3 = A.shape[0]
+    o = Opts(dim=D, vocabSize=V3, nneg=10, wsample=1.0, seed=3)
+    model = Word2Vec(o).init(N)
+    model.modelmats[0].copy_(dev(B))
+    model.modelmats[0].mul_(0.02)
+    model.modelmats[1].copy_(dev(A))
+    model.modelmats[1].mul_(0.02)
+    As, Bs = model.modelmats[1].cpu().numpy(), model.modelmats[0].cpu().numpy()
+    toks = zipf_corpus(V3, N, 1.07, seed=4, doc_len=1000)
+    words, lb, ub, wa, wb = model.wordMats([dev(toks)], batch_id=1)
+    assert wa.shape[1] == 10 and wb.shape[1] == 5 and wa.shape[0] > 1_100_000
+    eneg = model.evalNegatives(10, 5, wa, wb, model.modelmats[1], model.modelmats[0])
+    want = oracle.word2vecEvalNeg(D, wa.shape[0], 10, 5, wa.cpu().numpy(), wb.cpu().numpy(), As, Bs, THREADS)
+    assert abs(eneg - want) <= 1e-5 * abs(want), (eneg, want)
+    epos = model.evalPositives(5, words, lb, ub, model.modelmats[1], model.modelmats[0])
+    want_pos = oracle.word2vecEvalPos(D, N, 5, words.cpu().numpy(), lb.cpu().numpy(), ub.cpu().numpy(), As, Bs,
+                                      THREADS)
+    assert abs(epos - want_pos) <= 1e-5 * abs(want_pos)

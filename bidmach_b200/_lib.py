@@ -49,6 +49,10 @@ SIGNATURES = {
     "word2vecNegFilt": (_I, [_I, _I, _I, _I, _I, _P, _P, _P, _P, _F, _F]),
     "word2vecEvalPos": (_I, [_I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "word2vecEvalNeg": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "word2vecPosSlice": (_I, [_I, _I, _I, _P, _P, _P, _P, _P, _F, _F, _I, _I, _I, _I]),
+    "word2vecNegSlice": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _F, _F, _I, _I, _I, _I]),
+    "word2vecEvalPosSlice": (_I, [_I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I]),
+    "word2vecEvalNegSlice": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I]),
     "word2vecEvalNegNoAlloc": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "bidmach_xxh32": (C.c_uint32, [_P, C.c_int64, C.c_uint32]),
     "bidmach_lz4_compress_bound": (C.c_int64, [C.c_int64]),
@@ -86,6 +90,8 @@ SIGNATURES = {
     "w2v_comm_destroy": (None, [_P]),
     "w2v_nvls_average": (_I, [_P, C.c_int64, _I, _I, _I, _P]),
     "w2v_reserve_sms": (_I, [_P, _I]),
+    "w2v_set_slice": (_I, [_P, _I, _I, _I, _I]),
+    "w2v_slice_rows": (C.c_int64, [_I, _I, _I]),
     "w2v_set_timing": (_I, [_P, _I]),
     "w2v_get_timing": (_I, [_P, C.POINTER(W2VTiming)]),
     "w2v_launch_count": (C.c_longlong, []),

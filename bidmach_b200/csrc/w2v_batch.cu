@@ -297,6 +297,7 @@ struct w2v_ctx {
   w2v::EvalScratch *eval;  // accumulator of the scoring kernels (inside `counts`)
   int *fault_host;         // pinned: set by a staged kernel that gave up waiting for its copies
   int sm_reserve;          // SMs the update kernels leave free (w2v_reserve_sms)
+  w2v::SliceMap slice;     // which rows of the vocabulary the caller's matrices hold (w2v_set_slice)
   void *cub_tmp;
   size_t cub_tmp_bytes;
   // pinned host
@@ -465,6 +466,7 @@ int w2v_create(const w2v_opts *opts, int ncols, w2v_ctx **out) {
   c->o = o;
   c->ncols = ncols;
   c->first_pos = -1;
+  c->slice = w2v::whole_vocabulary();
   c->max_pairs = (int64_t)2 * o.nskip * ncols;
   if (c->max_pairs > 0x7fffffffLL) { delete c; return 1; }
   // expt and salpha exactly as Word2Vec.init forms them (Word2Vec.scala:139,150)
@@ -521,6 +523,18 @@ int w2v_create(const w2v_opts *opts, int ncols, w2v_ctx **out) {
   c->eval = reinterpret_cast<w2v::EvalScratch *>(c->counts + 32);
   *out = c;
   return 0;
+}
+
+int w2v_set_slice(w2v_ctx *c, int islice, int nslices, int nHead, int doHead) {
+  if (!c || nslices < 1 || islice < 0 || islice >= nslices || nHead < 0) return 1;
+  c->slice = w2v::SliceMap{nHead, nslices, islice, doHead};
+  return 0;
+}
+
+int64_t w2v_slice_rows(int vocabSize, int nslices, int nHead) {
+  // Word2Vec.init: nHeadTerms + 1 + (nfeats - nHeadTerms - 1) / nSlices (networks/Word2Vec.scala:106)
+  if (nslices <= 1) return vocabSize;
+  return (int64_t)nHead + 1 + (vocabSize - nHead - 1) / nslices;
 }
 
 int w2v_reserve_sms(w2v_ctx *c, int sms) {
@@ -689,14 +703,14 @@ int w2v_dobatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, float *A, 
   int err = w2v_wordmats(c, tokens, u, batch_id, stream);
   if (err) return err;
   err = w2v::pos_update_async(o.dim, c->ncols, nullptr, o.nskip, c->words, c->lb, c->ub, A, B,
-                              lrpos, o.vexp, c->hot, stream);
+                              lrpos, o.vexp, c->hot, c->slice, stream);
   if (err) return err;
   mark(c, 3, stream);
   int groups = 0;
   const int *groups_dev = nullptr;
   group_count(c, &groups, &groups_dev);
   err = w2v::neg_update_async(o.dim, groups, groups_dev, 0x7fffffff, o.nneg, o.nreuse, c->wa,
-                              c->ctx_out, A, B, lrneg, o.vexp, c->hot, c->fault_host, stream);
+                              c->ctx_out, A, B, lrneg, o.vexp, c->hot, c->fault_host, c->slice, stream);
   mark(c, 4, stream);
   if (c->timing_on) c->ev_state[c->slot] = 1;
   return err;
@@ -710,14 +724,14 @@ int w2v_evalbatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, const fl
   if (err) return err;
   W2V_CHECK(cudaMemsetAsync(c->retvals, 0, 2 * sizeof(float), stream));
   err = w2v::pos_eval_async(o.dim, c->ncols, nullptr, o.nskip, c->words, c->lb, c->ub, A, B,
-                            c->retvals, c->eval, stream);
+                            c->retvals, c->eval, c->slice, stream);
   if (err) return err;
   mark(c, 3, stream);
   int groups = 0;
   const int *groups_dev = nullptr;
   group_count(c, &groups, &groups_dev);
   err = w2v::neg_eval_async(o.dim, groups, groups_dev, o.nneg, o.nreuse, c->wa, c->ctx_out, A, B,
-                            c->retvals + 1, c->eval, c->fault_host, stream);
+                            c->retvals + 1, c->eval, c->fault_host, c->slice, stream);
   if (err) return err;
   mark(c, 4, stream);
   if (c->timing_on) c->ev_state[c->slot] = 2;

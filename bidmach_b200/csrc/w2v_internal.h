@@ -27,6 +27,33 @@ struct HotRows {
   // (see fold_period in w2v_kernels.cu); null = fold_every as it stands.
   const int *stats;
 };
+// Vocabulary slicing of the reference's multi-node mode (Word2Vec.Opts nSlices / iSlice /
+// nHeadTerms / doHead; mapIndx, networks/Word2Vec.scala:665-672 and BIDMach_CPUMACH.c:80-88):
+// ids below `nhead` (the head) have a row on every slice, an id at or above it belongs to slice
+// `id % nslices` and is stored there at row (id - nhead) / nslices + nhead.  A pair is worked on
+// when both of its words have a row here, except head-head pairs unless do_head > 1; head rows
+// are written only when do_head > 0.  nslices == 1 with nhead == 0 is the whole vocabulary.
+struct SliceMap {
+  int nhead, nslices, islice, do_head;
+  __host__ __device__ bool whole() const { return nslices <= 1; }
+  // row of a global id on this slice, or -1 when the slice holds none
+  __host__ __device__ int local(int id) const {
+    if (id < nhead) return id;   // head ids, and a masked id (-1) as it is
+    if (id % nslices != islice) return -1;
+    return (id - nhead) / nslices + nhead;
+  }
+  // the global id stored at a local row (what the per-word rate scale is computed from)
+  __host__ __device__ int global(int row) const {
+    if (row < nhead) return row;
+    int r = (islice - nhead) % nslices;
+    if (r < 0) r += nslices;
+    return nhead + (row - nhead) * nslices + r;
+  }
+  __host__ __device__ bool skips_head_pairs() const { return do_head <= 1; }
+  __host__ __device__ bool freezes_head() const { return do_head <= 0; }
+};
+inline SliceMap whole_vocabulary() { return SliceMap{0, 1, 0, 1}; }
+
 size_t hot_rows_bytes();
 int hot_levels_default();
 HotRows hot_rows_at(float *zeroed_buffer, int levels);
@@ -69,19 +96,21 @@ bool neg_shape_supported(int nwa, int nwb);
 // device int that overrides `ncols` inside the kernel (so a column count
 // produced on the device never has to visit the host); `ncols` is then only an
 // upper bound used to size the grid.
+// `slice` other than whole_vocabulary(): W / WA / WB hold global ids, A and B the rows of this
+// slice only (see SliceMap).
 int pos_update_async(int dim, int ncols, const int *ncols_dev, int skip, const int *W,
                      const int *LB, const int *UB, float *A, float *B, float lrate, float vexp,
-                     const HotRows &hot, cudaStream_t stream);
+                     const HotRows &hot, const SliceMap &slice, cudaStream_t stream);
 // `scratch` is the caller's zeroed accumulator (the kernels leave it zeroed again); `fault`
 // is where a staged kernel that gave up waiting for its copies writes 1 (host-visible memory).
 int pos_eval_async(int dim, int ncols, const int *ncols_dev, int skip, const int *W, const int *LB,
                    const int *UB, const float *A, const float *B, float *retval,
-                   EvalScratch *scratch, cudaStream_t stream);
+                   EvalScratch *scratch, const SliceMap &slice, cudaStream_t stream);
 int neg_update_async(int dim, int ncols, const int *ncols_dev, int nwords, int nwa, int nwb,
                      const int *WA, const int *WB, float *A, float *B, float lrate, float vexp,
-                     const HotRows &hot, int *fault, cudaStream_t stream);
+                     const HotRows &hot, int *fault, const SliceMap &slice, cudaStream_t stream);
 int neg_eval_async(int dim, int ncols, const int *ncols_dev, int nwa, int nwb, const int *WA,
                    const int *WB, const float *A, const float *B, float *retval,
-                   EvalScratch *scratch, int *fault, cudaStream_t stream);
+                   EvalScratch *scratch, int *fault, const SliceMap &slice, cudaStream_t stream);
 
 }  // namespace w2v

@@ -243,12 +243,15 @@ __device__ __forceinline__ Neighbour look_at_neighbour(const int *__restrict__ W
 // delta each), all zero whenever they hold nothing.  Lane l only ever touches
 // elements l, l+32, ... of a slot, so no synchronisation is needed between the
 // lanes of the owning warp.
-template <int NR>
+// SLICED: W holds global ids and A / B the rows of one vocabulary slice (SliceMap): a word
+// without a row here is skipped like a masked one, head-head pairs and writes to head rows
+// follow the slice's do_head (word2vecPosSlice, BIDMach_CPUMACH.c:90-184).
+template <int NR, bool SLICED>
 __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
     pos_update_kernel(int dim, int ncols, const int *__restrict__ ncols_dev, int skip,
                       const int *__restrict__ W, const int *__restrict__ LB,
                       const int *__restrict__ UB, float *A, float *B, float lrate, float vexp,
-                      HotRows hot) {
+                      HotRows hot, SliceMap sl) {
   constexpr int kChunk = ChunkOf<NR>::value;
   extern __shared__ ulonglong2 ring_storage[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -300,6 +303,7 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
     const int u = t + lane - skip;
     const bool in = t < last;
     wraw = (in && lane <= 2 * skip && u >= 0 && u < ncols) ? W[u] : -1;
+    if (SLICED) wraw = sl.local(wraw);
     lbt = in ? max(LB[t], -skip) : 0;
     ubt = in ? min(UB[t], skip) : 0;
   };
@@ -315,7 +319,9 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
       Neighbour nb = {-1, false};
       {
         const int j = lane - skip;
-        if (j != 0 && j >= lbt && j <= ubt && wraw >= 0) {
+        bool pair = j != 0 && j >= lbt && j <= ubt && wraw >= 0;
+        if (SLICED && sl.skips_head_pairs() && wt < sl.nhead && wraw < sl.nhead) pair = false;
+        if (pair) {
           nb.word = wraw;
           nb.t_is_centre = true;
         }
@@ -325,7 +331,7 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
         // lane 31 never carries a neighbour (at most 31 offsets), so it
         // evaluates the centre's scale while the others do their context's
         const int sid = (lane == 31) ? wt : nb.word;
-        const float sc = (sid >= 0) ? freq_scale(sid, vexp) : 0.f;
+        const float sc = (sid >= 0) ? freq_scale(SLICED ? sl.global(sid) : sid, vexp) : 0.f;
         const float sa = __shfl_sync(kFullMask, sc, 31);
         PRow<NR> a, da;
         prow_load_lane(a, reinterpret_cast<const ulonglong2 *>(A + (int64_t)wt * dim) + lane, tail);
@@ -336,14 +342,15 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
           constexpr int CH = decltype(width)::value;
           static_assert(Spread<CH>::FIN == 1, "one total per lane expected");
           int src[CH];
+          int wc[CH];
           PRow<NR> rows[CH];
           float p[CH];
 #pragma unroll
           for (int c = 0; c < CH; c++) {
             src[c] = __ffs(todo) - 1;
             todo &= todo - 1;
-            const int64_t w = __shfl_sync(kFullMask, nb.word, src[c]);
-            prow_load_lane(rows[c], reinterpret_cast<const ulonglong2 *>(B + w * dim) + lane, tail);
+            wc[c] = __shfl_sync(kFullMask, nb.word, src[c]);
+            prow_load_lane(rows[c], reinterpret_cast<const ulonglong2 *>(B + (int64_t)wc[c] * dim) + lane, tail);
           }
 #pragma unroll
           for (int c = 0; c < CH; c++) p[c] = prow_dot_partial(a, rows[c]);
@@ -354,6 +361,7 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
             const float g = __shfl_sync(kFullMask, mine, Spread<CH>::lane_of(c));
             const float sb = __shfl_sync(kFullMask, sc, src[c]);
             prow_axpy(da, sa * g, rows[c]);
+            if (SLICED && sl.freezes_head() && wc[c] < sl.nhead) continue;  // head rows are read-only
             // context side: slot(u) += (sb * g) * a
             int slot = wslot + src[c];  // position t - skip + src[c]
             if (slot >= slots) slot -= slots;
@@ -378,7 +386,8 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
           cnt -= n;
           take_n<1, kChunk>(n, take);
         }
-        prow_red_lane(update_target(A, hot.shadowA, hot, wt, dim, gwarp) + 4 * lane, tail, da);
+        if (!(SLICED && sl.freezes_head() && wt < sl.nhead))
+          prow_red_lane(update_target(A, hot.shadowA, hot, wt, dim, gwarp) + 4 * lane, tail, da);
       }
     }
     // no later centre of this warp reaches position t - skip
@@ -395,7 +404,9 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
   for (int k = 0; k < slots && dirty; k++) {  // positions last - skip ... last + skip
     const int u = last - skip + k;
     // a dirty slot belongs to a position inside the minibatch that holds a word
-    retire((u >= 0 && u < ncols) ? W[u] : 0, wslot);
+    int wu = (u >= 0 && u < ncols) ? W[u] : 0;
+    if (SLICED) wu = sl.local(wu);
+    retire(wu, wslot);
     wslot = (wslot + 1 == slots) ? 0 : wslot + 1;
   }
 }
@@ -427,12 +438,14 @@ __device__ __forceinline__ void finish_eval_sum(double lane_sum, EvalScratch *sc
   }
 }
 
-template <int NR>
+// SLICED: pairs whose two words both have a row on this slice (evalPosCPUslice,
+// networks/Word2Vec.scala:1007-1068).
+template <int NR, bool SLICED>
 __global__ void __launch_bounds__(kPosThreads)
     pos_eval_kernel(int dim, int ncols, const int *__restrict__ ncols_dev, int skip,
                     const int *__restrict__ W, const int *__restrict__ LB,
                     const int *__restrict__ UB, const float *__restrict__ A,
-                    const float *__restrict__ B, EvalScratch *scratch, float *retval) {
+                    const float *__restrict__ B, EvalScratch *scratch, float *retval, SliceMap sl) {
   constexpr int kChunk = EvalChunkOf<NR>::value;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = dim >> 2;
@@ -446,10 +459,14 @@ __global__ void __launch_bounds__(kPosThreads)
   // neighbouring positions go to the warps of one block: their windows overlap,
   // so most context rows are found in L1
   for (int t = first + warp; t < last; t += (int)(blockDim.x >> 5)) {
-    const int wt = W[t];
+    const int wt = SLICED ? sl.local(W[t]) : W[t];
     if (wt < 0) continue;
     const int lbt = max(LB[t], -skip), ubt = min(UB[t], skip);
-    const Neighbour nb = look_at_neighbour(W, t, lbt, ubt, skip, ncols, lane);
+    Neighbour nb = look_at_neighbour(W, t, lbt, ubt, skip, ncols, lane);
+    if (SLICED && nb.t_is_centre) {
+      nb.word = sl.local(nb.word);
+      nb.t_is_centre = nb.word >= 0;
+    }
     unsigned todo = __ballot_sync(kFullMask, nb.t_is_centre);
     if (todo == 0) continue;
     PRow<NR> own;
@@ -674,12 +691,17 @@ __host__ __device__ inline size_t staged_warp_bytes(int nrows_per_col, int dim, 
 // EVAL = true turns the same pipeline into the scoring kernel (the name keeps
 // "update" for both): no updates, the lane that holds a pair's dot product adds
 // log(max(1 - sigmoid, 1e-20)).
-template <int NWA, int NWB, int NR, bool EVAL>
+// SLICED: WA / WB hold global ids and A / B the rows of one vocabulary slice (SliceMap).  A word
+// without a row here acts as a masked one; head-head pairs contribute nothing unless do_head > 1
+// and head rows are written only when do_head > 0 (word2vecNegSlice, BIDMach_CPUMACH.c:267-366);
+// the score counts the pairs whose two words both have a row here (evalNegCPUslice,
+// networks/Word2Vec.scala:1134-1200).
+template <int NWA, int NWB, int NR, bool EVAL, bool SLICED>
 __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
     neg_update_staged_kernel(int dim, int ncols, const int *__restrict__ ncols_dev, int nwords,
                       const int *__restrict__ WA, const int *__restrict__ WB, float *A, float *B,
                       float lrate, float vexp, HotRows hot, EvalScratch *scratch, float *retval,
-                      int *fault) {
+                      int *fault, SliceMap sl) {
   using S = Spread<NWA * NWB>;
   constexpr int NROWS = NWA + NWB;
   constexpr int NST = 1;
@@ -730,8 +752,12 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
     }
   };
   auto ids_of = [&](int i) {
-    return column_word<NWA, NWB>(WA, WB, gwarp + (int64_t)i * nwarps, nwords, lane);
+    int w = column_word<NWA, NWB>(WA, WB, gwarp + (int64_t)i * nwarps, nwords, lane);
+    if (SLICED) w = sl.local(w);
+    return w;
   };
+  // a row that takes part may still be closed to writes (head rows of a slice with do_head 0)
+  auto writable = [&](int w) { return w >= 0 && !(SLICED && sl.freezes_head() && w < sl.nhead); };
 
   if (mycols > 0) fill(0, ids_of(0));
   int ahead = (mycols > 1) ? ids_of(1) : -1;  // word ids of the next column to fill
@@ -748,7 +774,7 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
       break;
     }
     const int myw = (lane < 16) ? ids[st * 16 + lane] : -1;
-    const float mysc = (myw >= 0) ? freq_scale(myw, vexp) : 0.f;
+    const float mysc = (myw >= 0) ? freq_scale(SLICED ? sl.global(myw) : myw, vexp) : 0.f;
     const ulonglong2 *stage = reinterpret_cast<const ulonglong2 *>(stages + st * stage_bytes) + lane;
     auto staged_row = [&](int r) {  // this lane's first vector of row r of the stage
       return reinterpret_cast<const ulonglong2 *>(reinterpret_cast<const unsigned char *>(stage) +
@@ -799,11 +825,28 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
       if constexpr (EVAL) {
         for_valid_totals<NWA * NWB>(
             lane, [&](auto q) { acc += pair_score(1.0f - sigmoid_guard(p[decltype(q)::value])); });
+        if constexpr (SLICED) {
+          // a pair with a word that has no row here was scored as a pair with a zero row,
+          // log(1/2): take those out again, the slice's score counts only its own pairs
+          const unsigned have = __ballot_sync(kFullMask, myw >= 0);
+          const int na = __popc(have & ((1u << NWA) - 1u)), nb = __popc(have >> NWA);
+          if (lane == 0) acc -= (double)(NWA * NWB - na * nb) * pair_score(0.5f);
+        }
       } else {
 #pragma unroll
         for (int q = 0; q < S::FIN; q++) p[q] = -lrate * sigmoid_guard(p[q]);
         float g[NWA * NWB];
         broadcast_totals<NWA * NWB>(p, g);
+        if constexpr (SLICED) {
+          if (sl.skips_head_pairs()) {
+            const unsigned head = __ballot_sync(kFullMask, myw >= 0 && myw < sl.nhead);
+#pragma unroll
+            for (int j = 0; j < NWA; j++)
+#pragma unroll
+              for (int k = 0; k < NWB; k++)
+                if (((head >> j) & 1u) && ((head >> (NWA + k)) & 1u)) g[j * NWB + k] = 0.f;
+          }
+        }
         // rows of the streamed side: their deltas need the held rows only
 #pragma unroll
         for (int y = 0; y < NY; y++) {
@@ -814,7 +857,7 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
 #pragma unroll
           for (int x = 1; x < NX; x++)
             prow_axpy(dY, sy * g[HOLD_B ? (y * NWB + x) : (x * NWB + y)], X[x]);
-          if (!CHECKED || wy >= 0)
+          if (!CHECKED || writable(wy))
             prow_red_lane(update_target(MY, SY, hot, wy, dim, gwarp) + 4 * lane, tail, dY);
         }
         // rows of the held side: the held rows themselves are dead by now, their
@@ -839,11 +882,11 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
         }
 #pragma unroll
         for (int x = 0; x < NX; x++)
-          if (!CHECKED || wx[x] >= 0)
+          if (!CHECKED || writable(wx[x]))
             prow_red_lane(update_target(MX, SX, hot, wx[x], dim, gwarp) + 4 * lane, tail, X[x]);
       }
     };
-    if (__all_sync(kFullMask, lane >= NROWS || myw >= 0))
+    if (!SLICED && __all_sync(kFullMask, lane >= NROWS || myw >= 0))
       column(std::false_type());
     else
       column(std::true_type());
@@ -1199,18 +1242,18 @@ static inline int grid_for(int work_items, int threads, int blocks_per_sm) {
     default: { constexpr int NR = 10; CALL; } break; \
   }
 
-template <int NR>
+template <int NR, bool SLICED>
 static cudaError_t launch_pos_update(int grid, size_t smem, cudaStream_t stream, int dim, int ncols,
                                      const int *ncols_dev, int skip, const int *W, const int *LB,
                                      const int *UB, float *A, float *B, float lrate, float vexp,
-                                     const HotRows &hot) {
+                                     const HotRows &hot, const SliceMap &sl) {
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(pos_update_kernel<NR>,
+    cudaError_t e = cudaFuncSetAttribute(pos_update_kernel<NR, SLICED>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  pos_update_kernel<NR><<<grid, kPosThreads, smem, stream>>>(dim, ncols, ncols_dev, skip, W, LB, UB, A,
-                                                             B, lrate, vexp, hot);
+  pos_update_kernel<NR, SLICED><<<grid, kPosThreads, smem, stream>>>(dim, ncols, ncols_dev, skip, W, LB,
+                                                                     UB, A, B, lrate, vexp, hot, sl);
   return cudaSuccess;
 }
 
@@ -1222,10 +1265,15 @@ static size_t pos_ring_bytes(int dim, int skip) {
 
 int pos_update_async(int dim, int ncols, const int *ncols_dev, int skip, const int *W,
                      const int *LB, const int *UB, float *A, float *B, float lrate, float vexp,
-                     const HotRows &hot, cudaStream_t stream) {
+                     const HotRows &hot, const SliceMap &slice, cudaStream_t stream) {
   if (ncols <= 0) return 0;
   if (skip < 1 || skip > 15) return 1;
   const size_t smem = pos_ring_bytes(dim, skip);
+  const bool sliced = !slice.whole();
+  if (sliced && !(vector_ok(dim, A, B) && smem <= 227 * 1024)) {
+    printf("word2vecPosSlice needs rows of a multiple of 4 floats, 16-byte aligned matrices (dim %d)\n", dim);
+    return 1;
+  }
   if (vector_ok(dim, A, B) && smem <= 227 * 1024) {
     const int nr = (dim / 4 + 31) / 32;
     const int resident = (int)std::min<size_t>(4, (227 * 1024) / smem);
@@ -1235,8 +1283,13 @@ int pos_update_async(int dim, int ncols, const int *ncols_dev, int skip, const i
     const int max_grid = std::max(1, ncols / (64 * (kPosThreads / 32)));
     grid = std::max(1, std::min(grid, max_grid));
     cudaError_t e = cudaSuccess;
-    W2V_NR_SWITCH(nr, (e = launch_pos_update<NR>(grid, smem, stream, dim, ncols, ncols_dev, skip, W,
-                                                 LB, UB, A, B, lrate, vexp, hot)));
+    if (sliced) {
+      W2V_NR_SWITCH(nr, (e = launch_pos_update<NR, true>(grid, smem, stream, dim, ncols, ncols_dev, skip, W,
+                                                         LB, UB, A, B, lrate, vexp, hot, slice)));
+    } else {
+      W2V_NR_SWITCH(nr, (e = launch_pos_update<NR, false>(grid, smem, stream, dim, ncols, ncols_dev, skip, W,
+                                                          LB, UB, A, B, lrate, vexp, hot, slice)));
+    }
     if (e != cudaSuccess) return (int)e;
     fold_hot_rows(dim, hot, A, B, stream);
   } else {
@@ -1250,14 +1303,24 @@ int pos_update_async(int dim, int ncols, const int *ncols_dev, int skip, const i
 
 int pos_eval_async(int dim, int ncols, const int *ncols_dev, int skip, const int *W, const int *LB,
                    const int *UB, const float *A, const float *B, float *retval,
-                   EvalScratch *scratch, cudaStream_t stream) {
+                   EvalScratch *scratch, const SliceMap &slice, cudaStream_t stream) {
   if (ncols <= 0) return 0;
   if (skip < 1 || skip > 15) return 1;
+  const bool sliced = !slice.whole();
+  if (sliced && !vector_ok(dim, A, B)) {
+    printf("word2vecEvalPosSlice needs rows of a multiple of 4 floats, 16-byte aligned matrices (dim %d)\n", dim);
+    return 1;
+  }
   if (vector_ok(dim, A, B)) {
     const int nr = (dim / 4 + 31) / 32;
     const int grid = grid_for(ncols, kPosThreads, 8);
-    W2V_NR_SWITCH(nr, (pos_eval_kernel<NR><<<grid, kPosThreads, 0, stream>>>(
-                          dim, ncols, ncols_dev, skip, W, LB, UB, A, B, scratch, retval)));
+    if (sliced) {
+      W2V_NR_SWITCH(nr, (pos_eval_kernel<NR, true><<<grid, kPosThreads, 0, stream>>>(
+                            dim, ncols, ncols_dev, skip, W, LB, UB, A, B, scratch, retval, slice)));
+    } else {
+      W2V_NR_SWITCH(nr, (pos_eval_kernel<NR, false><<<grid, kPosThreads, 0, stream>>>(
+                            dim, ncols, ncols_dev, skip, W, LB, UB, A, B, scratch, retval, slice)));
+    }
   } else {
     const int grid = grid_for(ncols, kGenericThreads, 16);
     pos_eval_generic_kernel<<<grid, kGenericThreads, 0, stream>>>(
@@ -1279,12 +1342,12 @@ static bool neg_staged_enabled() {
   return on;
 }
 
-template <int NWA, int NWB, int NR, bool EVAL>
+template <int NWA, int NWB, int NR, bool EVAL, bool SLICED>
 static cudaError_t launch_neg_staged(int grid, int warps, size_t smem, cudaStream_t stream, int dim,
                                      int ncols, const int *ncols_dev, int nwords, const int *WA,
                                      const int *WB, float *A, float *B, float lrate, float vexp,
                                      const HotRows &hot, EvalScratch *scratch, float *retval,
-                                     int *fault) {
+                                     int *fault, const SliceMap &sl) {
   // never more threads than the kernel was compiled for
   constexpr int kMaxWarps = StagedShape<NWA, NWB, NR>::max_threads / 32;
   if (warps > kMaxWarps) {
@@ -1292,12 +1355,12 @@ static cudaError_t launch_neg_staged(int grid, int warps, size_t smem, cudaStrea
     smem = staged_warp_bytes(NWA + NWB, dim, 1) * warps;
   }
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(neg_update_staged_kernel<NWA, NWB, NR, EVAL>,
+    cudaError_t e = cudaFuncSetAttribute(neg_update_staged_kernel<NWA, NWB, NR, EVAL, SLICED>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  neg_update_staged_kernel<NWA, NWB, NR, EVAL><<<grid, warps * 32, smem, stream>>>(
-      dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault);
+  neg_update_staged_kernel<NWA, NWB, NR, EVAL, SLICED><<<grid, warps * 32, smem, stream>>>(
+      dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault, sl);
   return cudaSuccess;
 }
 
@@ -1307,20 +1370,20 @@ static cudaError_t launch_neg_staged_any(bool eval, int grid, int warps, size_t 
                                          const int *ncols_dev, int nwords, const int *WA,
                                          const int *WB, float *A, float *B, float lrate, float vexp,
                                          const HotRows &hot, EvalScratch *scratch, float *retval,
-                                         int *fault) {
-  return eval ? launch_neg_staged<NWA, NWB, NR, true>(grid, warps, smem, stream, dim, ncols, ncols_dev,
-                                                      nwords, WA, WB, A, B, lrate, vexp, hot, scratch,
-                                                      retval, fault)
-              : launch_neg_staged<NWA, NWB, NR, false>(grid, warps, smem, stream, dim, ncols, ncols_dev,
-                                                       nwords, WA, WB, A, B, lrate, vexp, hot, scratch,
-                                                       retval, fault);
+                                         int *fault, const SliceMap &sl) {
+#define W2V_STAGED(EV, SL)                                                                                  \
+  launch_neg_staged<NWA, NWB, NR, EV, SL>(grid, warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, \
+                                          A, B, lrate, vexp, hot, scratch, retval, fault, sl)
+  if (sl.whole()) return eval ? W2V_STAGED(true, false) : W2V_STAGED(false, false);
+  return eval ? W2V_STAGED(true, true) : W2V_STAGED(false, true);
+#undef W2V_STAGED
 }
 
 template <int NWA, int NWB>
 static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int nwords,
                         const int *WA, const int *WB, float *A, float *B, float lrate, float vexp,
                         float *retval, const HotRows &hot, EvalScratch *scratch, int *fault,
-                        cudaStream_t stream) {
+                        const SliceMap &sl, cudaStream_t stream) {
   const int nr = (dim / 4 + 31) / 32;
   // rows of a column live in registers: (NWA + NWB) * nr vectors per lane, which
   // fits for up to 10 rows of 3 vectors or 15 rows of 2
@@ -1335,17 +1398,22 @@ static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int
   // the benchmark workload: 1.32 ms staged against 1.72 ms with rows loaded into registers,
   // 2.41 against 3.62 ms for 10+5 columns); the register-resident kernels are the fallback
   const bool want_staged = true;
-  if (want_staged && vector_ok(dim, A, B) && nr <= 4 && staged_warps >= 2 && neg_staged_enabled()) {
+  const bool staged_fits = vector_ok(dim, A, B) && nr <= 4 && staged_warps >= 2;
+  if (!sl.whole() && !staged_fits) {
+    printf("word2vecNegSlice needs rows of a multiple of 4 floats, at most 512, 16-byte aligned matrices (dim %d)\n", dim);
+    return 1;
+  }
+  if (want_staged && staged_fits && (neg_staged_enabled() || !sl.whole())) {
     const size_t smem = per_warp * staged_warps;
     // at least 8 columns per warp: a small launch then still applies its updates in several
     // rounds instead of computing every column from the same stale rows
     const int grid = std::max(1, std::min(device_sm_count(), (ncols + 8 * staged_warps - 1) / (8 * staged_warps)));
     cudaError_t e = cudaSuccess;
     switch (nr) {
-      case 1: e = launch_neg_staged_any<NWA, NWB, 1>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault); break;
-      case 2: e = launch_neg_staged_any<NWA, NWB, 2>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault); break;
-      case 3: e = launch_neg_staged_any<NWA, NWB, 3>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault); break;
-      default: e = launch_neg_staged_any<NWA, NWB, 4>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault); break;
+      case 1: e = launch_neg_staged_any<NWA, NWB, 1>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault, sl); break;
+      case 2: e = launch_neg_staged_any<NWA, NWB, 2>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault, sl); break;
+      case 3: e = launch_neg_staged_any<NWA, NWB, 3>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault, sl); break;
+      default: e = launch_neg_staged_any<NWA, NWB, 4>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault, sl); break;
     }
     if (e != cudaSuccess) return (int)e;
     if (!eval) fold_hot_rows(dim, hot, A, B, stream);
@@ -1383,31 +1451,31 @@ static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int
 static int neg_any(bool eval, int dim, int ncols, const int *ncols_dev, int nwords, int nwa,
                    int nwb, const int *WA, const int *WB, float *A, float *B, float lrate,
                    float vexp, float *retval, const HotRows &hot, EvalScratch *scratch, int *fault,
-                   cudaStream_t stream) {
+                   const SliceMap &sl, cudaStream_t stream) {
   if (ncols <= 0) return 0;
   if (dim <= 0) return 1;
   const int which = nwa * 10000 + nwb;
   switch (which) {
-    case 50001: return neg_dispatch<5, 1>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, scratch, fault, stream);
-    case 50005: return neg_dispatch<5, 5>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, scratch, fault, stream);
-    case 100005: return neg_dispatch<10, 5>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, scratch, fault, stream);
-    case 50010: return neg_dispatch<5, 10>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, scratch, fault, stream);
+    case 50001: return neg_dispatch<5, 1>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, scratch, fault, sl, stream);
+    case 50005: return neg_dispatch<5, 5>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, scratch, fault, sl, stream);
+    case 100005: return neg_dispatch<10, 5>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, scratch, fault, sl, stream);
+    case 50010: return neg_dispatch<5, 10>(eval, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, retval, hot, scratch, fault, sl, stream);
     default: return 1;
   }
 }
 
 int neg_update_async(int dim, int ncols, const int *ncols_dev, int nwords, int nwa, int nwb,
                      const int *WA, const int *WB, float *A, float *B, float lrate, float vexp,
-                     const HotRows &hot, int *fault, cudaStream_t stream) {
+                     const HotRows &hot, int *fault, const SliceMap &sl, cudaStream_t stream) {
   return neg_any(false, dim, ncols, ncols_dev, nwords, nwa, nwb, WA, WB, A, B, lrate, vexp, nullptr,
-                 hot, nullptr, fault, stream);
+                 hot, nullptr, fault, sl, stream);
 }
 
 int neg_eval_async(int dim, int ncols, const int *ncols_dev, int nwa, int nwb, const int *WA,
                    const int *WB, const float *A, const float *B, float *retval,
-                   EvalScratch *scratch, int *fault, cudaStream_t stream) {
+                   EvalScratch *scratch, int *fault, const SliceMap &sl, cudaStream_t stream) {
   return neg_any(true, dim, ncols, ncols_dev, 0x7fffffff, nwa, nwb, WA, WB, const_cast<float *>(A),
-                 const_cast<float *>(B), 0.f, 0.f, retval, hot_rows_at(nullptr, 0), scratch, fault,
+                 const_cast<float *>(B), 0.f, 0.f, retval, hot_rows_at(nullptr, 0), scratch, fault, sl,
                  stream);
 }
 
@@ -1458,16 +1526,24 @@ struct ScratchLease {
 
 }  // namespace
 
-extern "C" {
+namespace {
 
-int word2vecPos(int nrows, int ncols, int shift, int *W, int *LB, int *UB, float *A, float *B,
-                float lrate, float vexp) {
+// nslices, islice, nHead, doHead as the reference's slice functions take them; the id's slice
+// is id % nslices (BIDMach_CPUMACH.c:85), so islice must lie in [0, nslices)
+bool slice_args_ok(const char *name, int islice, int nslices, int nhead) {
+  if (nslices >= 1 && islice >= 0 && islice < nslices && nhead >= 0) return true;
+  printf("%s bad slice arguments islice %d nslices %d nHead %d\n", name, islice, nslices, nhead);
+  return false;
+}
+
+int pos_launcher(const char *name, int nrows, int ncols, int shift, int *W, int *LB, int *UB, float *A,
+                 float *B, float lrate, float vexp, const w2v::SliceMap &sl) {
   if (shift != 5 && shift != 3 && shift != 2) {
-    printf("word2vecPos unsupport size %d\n", shift);
+    printf("%s unsupport size %d\n", name, shift);
     return 1;
   }
   if (nrows > 1280) {
-    printf("word2vecPos too many rows %d\n", nrows);
+    printf("%s too many rows %d\n", name, nrows);
     return 1;
   }
   if (ncols <= 0) return 0;
@@ -1478,11 +1554,11 @@ int word2vecPos(int nrows, int ncols, int shift, int *W, int *LB, int *UB, float
   err = lease.hot_rows(W, ncols, 0x7fffffff, &hot);
   if (err) return err;
   return lease.finish(w2v::pos_update_async(nrows, ncols, nullptr, shift, W, LB, UB, A, B, lrate,
-                                            vexp, hot, cudaStreamPerThread));
+                                            vexp, hot, sl, cudaStreamPerThread));
 }
 
-static int neg_launcher(int nrows, int ncols, int nwords, int nwa, int nwb, int *WA, int *WB,
-                        float *A, float *B, float lrate, float vexp) {
+int neg_launcher(int nrows, int ncols, int nwords, int nwa, int nwb, int *WA, int *WB, float *A,
+                 float *B, float lrate, float vexp, const w2v::SliceMap &sl) {
   if (!w2v::neg_shape_supported(nwa, nwb)) {
     printf("word2vec unsupport size combination %d %d\n", nwa, nwb);
     return 1;
@@ -1495,27 +1571,17 @@ static int neg_launcher(int nrows, int ncols, int nwords, int nwa, int nwb, int 
   err = lease.hot_rows(WB, (int64_t)ncols * nwb, nwords, &hot);
   if (err) return err;
   return lease.finish(w2v::neg_update_async(nrows, ncols, nullptr, nwords, nwa, nwb, WA, WB, A, B,
-                                            lrate, vexp, hot, lease.s->fault, cudaStreamPerThread));
+                                            lrate, vexp, hot, lease.s->fault, sl, cudaStreamPerThread));
 }
 
-int word2vecNeg(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A, float *B,
-                float lrate, float vexp) {
-  return neg_launcher(nrows, ncols, 0x7fffffff, nwa, nwb, WA, WB, A, B, lrate, vexp);
-}
-
-int word2vecNegFilt(int nrows, int ncols, int nwords, int nwa, int nwb, int *WA, int *WB, float *A,
-                    float *B, float lrate, float vexp) {
-  return neg_launcher(nrows, ncols, nwords, nwa, nwb, WA, WB, A, B, lrate, vexp);
-}
-
-int word2vecEvalPos(int nrows, int ncols, int shift, int *W, int *LB, int *UB, float *A, float *B,
-                    float *Retval) {
+int eval_pos_launcher(const char *name, int nrows, int ncols, int shift, int *W, int *LB, int *UB,
+                      float *A, float *B, float *Retval, const w2v::SliceMap &sl) {
   if (shift != 5 && shift != 3 && shift != 2) {
-    printf("word2vecEvalPos unsupport size %d\n", shift);
+    printf("%s unsupport size %d\n", name, shift);
     return 1;
   }
   if (nrows > 1280) {
-    printf("word2vecEvalPos nrows too large %d\n", nrows);
+    printf("%s nrows too large %d\n", name, nrows);
     return 1;
   }
   if (ncols <= 0) return 0;
@@ -1523,13 +1589,13 @@ int word2vecEvalPos(int nrows, int ncols, int shift, int *W, int *LB, int *UB, f
   int err = lease.acquire();
   if (err) return err;
   return lease.finish(w2v::pos_eval_async(nrows, ncols, nullptr, shift, W, LB, UB, A, B, Retval,
-                                          lease.s->eval, cudaStreamPerThread));
+                                          lease.s->eval, sl, cudaStreamPerThread));
 }
 
-int word2vecEvalNeg(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A, float *B,
-                    float *Retval) {
+int eval_neg_launcher(const char *name, int nrows, int ncols, int nwa, int nwb, int *WA, int *WB,
+                      float *A, float *B, float *Retval, const w2v::SliceMap &sl) {
   if (!w2v::neg_shape_supported(nwa, nwb)) {
-    printf("word2vecEvalNeg unsupport size combination %d %d\n", nwa, nwb);
+    printf("%s unsupport size combination %d %d\n", name, nwa, nwb);
     return 1;
   }
   if (ncols <= 0) return 0;
@@ -1537,7 +1603,70 @@ int word2vecEvalNeg(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, fl
   int err = lease.acquire();
   if (err) return err;
   return lease.finish(w2v::neg_eval_async(nrows, ncols, nullptr, nwa, nwb, WA, WB, A, B, Retval,
-                                          lease.s->eval, lease.s->fault, cudaStreamPerThread));
+                                          lease.s->eval, lease.s->fault, sl, cudaStreamPerThread));
+}
+
+}  // namespace
+
+extern "C" {
+
+int word2vecPos(int nrows, int ncols, int shift, int *W, int *LB, int *UB, float *A, float *B,
+                float lrate, float vexp) {
+  return pos_launcher("word2vecPos", nrows, ncols, shift, W, LB, UB, A, B, lrate, vexp,
+                      w2v::whole_vocabulary());
+}
+
+int word2vecNeg(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A, float *B,
+                float lrate, float vexp) {
+  return neg_launcher(nrows, ncols, 0x7fffffff, nwa, nwb, WA, WB, A, B, lrate, vexp,
+                      w2v::whole_vocabulary());
+}
+
+int word2vecNegFilt(int nrows, int ncols, int nwords, int nwa, int nwb, int *WA, int *WB, float *A,
+                    float *B, float lrate, float vexp) {
+  return neg_launcher(nrows, ncols, nwords, nwa, nwb, WA, WB, A, B, lrate, vexp, w2v::whole_vocabulary());
+}
+
+int word2vecEvalPos(int nrows, int ncols, int shift, int *W, int *LB, int *UB, float *A, float *B,
+                    float *Retval) {
+  return eval_pos_launcher("word2vecEvalPos", nrows, ncols, shift, W, LB, UB, A, B, Retval,
+                           w2v::whole_vocabulary());
+}
+
+int word2vecEvalNeg(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A, float *B,
+                    float *Retval) {
+  return eval_neg_launcher("word2vecEvalNeg", nrows, ncols, nwa, nwb, WA, WB, A, B, Retval,
+                           w2v::whole_vocabulary());
+}
+
+// Vocabulary slices (the device forms of CPUMACH.word2vecPosSlice / word2vecNegSlice and of
+// Word2Vec.evalPosCPUslice / evalNegCPUslice).
+int word2vecPosSlice(int nrows, int ncols, int shift, int *W, int *LB, int *UB, float *A, float *B,
+                     float lrate, float vexp, int islice, int nslices, int nHead, int doHead) {
+  if (!slice_args_ok("word2vecPosSlice", islice, nslices, nHead)) return 1;
+  return pos_launcher("word2vecPosSlice", nrows, ncols, shift, W, LB, UB, A, B, lrate, vexp,
+                      w2v::SliceMap{nHead, nslices, islice, doHead});
+}
+
+int word2vecNegSlice(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A, float *B,
+                     float lrate, float vexp, int islice, int nslices, int nHead, int doHead) {
+  if (!slice_args_ok("word2vecNegSlice", islice, nslices, nHead)) return 1;
+  return neg_launcher(nrows, ncols, 0x7fffffff, nwa, nwb, WA, WB, A, B, lrate, vexp,
+                      w2v::SliceMap{nHead, nslices, islice, doHead});
+}
+
+int word2vecEvalPosSlice(int nrows, int ncols, int shift, int *W, int *LB, int *UB, float *A, float *B,
+                         float *Retval, int islice, int nslices, int nHead) {
+  if (!slice_args_ok("word2vecEvalPosSlice", islice, nslices, nHead)) return 1;
+  return eval_pos_launcher("word2vecEvalPosSlice", nrows, ncols, shift, W, LB, UB, A, B, Retval,
+                           w2v::SliceMap{nHead, nslices, islice, 1});
+}
+
+int word2vecEvalNegSlice(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A, float *B,
+                         float *Retval, int islice, int nslices, int nHead) {
+  if (!slice_args_ok("word2vecEvalNegSlice", islice, nslices, nHead)) return 1;
+  return eval_neg_launcher("word2vecEvalNegSlice", nrows, ncols, nwa, nwb, WA, WB, A, B, Retval,
+                           w2v::SliceMap{nHead, nslices, islice, 1});
 }
 
 long long w2v_launch_count(void) { return w2v::launch_count(); }

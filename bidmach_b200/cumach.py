@@ -55,6 +55,33 @@ class CUMACH:
                                            _addr(B), _addr(retVal))
 
 
+class CUMACHSlice:
+    """Device forms of ``CPUMACH.word2vecPosSlice`` / ``word2vecNegSlice``
+    (src/main/java/edu/berkeley/bid/CPUMACH.java) and of the Scala scoring twins
+    ``Word2Vec.evalPosCPUslice`` / ``evalNegCPUslice``: one vocabulary slice per call, its rows in
+    one matrix per side (no ``maxCols`` blocks, no ``dualMode``)."""
+
+    @staticmethod
+    def word2vecPosSlice(nrows, ncols, shift, W, LB, UB, A, B, lrate, vexp, islice, nslices, nHead, doHead=1) -> int:
+        return _lib.load().word2vecPosSlice(nrows, ncols, shift, _addr(W), _addr(LB), _addr(UB), _addr(A),
+                                            _addr(B), lrate, vexp, islice, nslices, nHead, doHead)
+
+    @staticmethod
+    def word2vecNegSlice(nrows, ncols, nwa, nwb, WA, WB, A, B, lrate, vexp, islice, nslices, nHead, doHead=1) -> int:
+        return _lib.load().word2vecNegSlice(nrows, ncols, nwa, nwb, _addr(WA), _addr(WB), _addr(A), _addr(B),
+                                            lrate, vexp, islice, nslices, nHead, doHead)
+
+    @staticmethod
+    def word2vecEvalPosSlice(nrows, ncols, shift, W, LB, UB, A, B, retVal, islice, nslices, nHead) -> int:
+        return _lib.load().word2vecEvalPosSlice(nrows, ncols, shift, _addr(W), _addr(LB), _addr(UB), _addr(A),
+                                                _addr(B), _addr(retVal), islice, nslices, nHead)
+
+    @staticmethod
+    def word2vecEvalNegSlice(nrows, ncols, nwa, nwb, WA, WB, A, B, retVal, islice, nslices, nHead) -> int:
+        return _lib.load().word2vecEvalNegSlice(nrows, ncols, nwa, nwb, _addr(WA), _addr(WB), _addr(A),
+                                                _addr(B), _addr(retVal), islice, nslices, nHead)
+
+
 def word2vecEvalNegNoAlloc(nrows, ncols, nwa, nwb, WA, WB, A, B, retVal) -> int:
     """``CUMACH.word2vecEvalNeg`` for callers that cannot allocate device memory
     while running (the Java class has no such method).  Same arguments and

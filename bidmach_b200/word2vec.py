@@ -79,7 +79,12 @@ class Word2Vec:
     """SGNS model.  ``modelmats[0]`` is the context/embedding matrix (random
     init) and ``modelmats[1]`` the centre/negative matrix (zeros), both stored
     as ``[vocabSize, dim]`` fp32 CUDA tensors, i.e. the reference's column-major
-    ``dim x vocabSize`` (Word2Vec.scala:113-117)."""
+    ``dim x vocabSize`` (Word2Vec.scala:113-117).
+
+    With ``nSlices > 1`` the model holds one vocabulary slice (Word2Vec.scala:104-135, 665-672):
+    the ``nHeadTerms`` most frequent words, which every slice has, followed by the words with
+    ``id % nSlices == iSlice``; the matrices then have ``sliceRows()`` rows, minibatches still
+    carry global ids, and every slice of a job sees every minibatch."""
 
     Opts = Opts
 
@@ -87,9 +92,11 @@ class Word2Vec:
         self.opts = opts or Opts()
         if not self.opts.useGPU:
             raise RuntimeError("this build has no CPU path: useGPU must stay true")
-        if self.opts.nSlices != 1 or self.opts.dualMode or self.opts.nHeadTerms != 0:
-            raise NotImplementedError("model slicing (nSlices/dualMode/nHeadTerms) is a CPU-only "
-                                      "feature of the reference and is not part of this path")
+        if self.opts.dualMode:
+            raise NotImplementedError("dualMode keeps half of the model in host memory for the reference's "
+                                      "CPU kernels; this build has no CPU path")
+        if self.opts.nSlices < 1 or not 0 <= self.opts.iSlice < self.opts.nSlices or self.opts.nHeadTerms < 0:
+            raise ValueError("need nSlices >= 1, 0 <= iSlice < nSlices, nHeadTerms >= 0")
         self.device = torch.device(device if device is not None else "cuda")
         self.modelmats: list[torch.Tensor] = []
         self.ncols = 0
@@ -102,6 +109,12 @@ class Word2Vec:
         self._symm = None
         self._tick = None
 
+    def sliceRows(self) -> int:
+        """Rows of each matrix: nHeadTerms + 1 + (vocabSize - nHeadTerms - 1) / nSlices
+        (Word2Vec.scala:106), the whole vocabulary for one slice."""
+        o = self.opts
+        return int(_lib.load().w2v_slice_rows(o.vocabSize, o.nSlices, o.nHeadTerms))
+
     # -- life cycle ---------------------------------------------------------
     def init(self, ncols: int, refresh: bool = True):
         """Word2Vec.init (Word2Vec.scala:100-165): allocate both matrices and the
@@ -113,9 +126,12 @@ class Word2Vec:
         with torch.cuda.device(self.device):
             if refresh or not self.modelmats:
                 # both matrices in one buffer, so that one collective moves the whole model
-                self._flat = torch.empty(2, o.vocabSize, o.dim, dtype=torch.float32, device=self.device)
+                rows = self.sliceRows()
+                self._flat = torch.empty(2, rows, o.dim, dtype=torch.float32, device=self.device)
                 mm0, mm1 = self._flat[0], self._flat[1]
-                _check(lib.w2v_init_model(C.byref(self._copts), mm1.data_ptr(), mm0.data_ptr(),
+                shape = o.to_c()
+                shape.vocabSize = rows     # the rows this model stores
+                _check(lib.w2v_init_model(C.byref(shape), mm1.data_ptr(), mm0.data_ptr(),
                                           self._stream()), "w2v_init_model")
                 self.modelmats = [mm0, mm1]
             ctx = C.c_void_p()
@@ -124,6 +140,8 @@ class Word2Vec:
                 raise RuntimeError(f"w2v_create failed ({err}): unsupported options or out of memory")
             self._free_ctx()
             self._ctx = ctx
+            if o.nSlices > 1:
+                _check(lib.w2v_set_slice(ctx, o.iSlice, o.nSlices, o.nHeadTerms, o.doHead), "w2v_set_slice")
         return self
 
     def _free_ctx(self):
@@ -333,7 +351,7 @@ class Word2Vec:
         if int(flag.item()) == 0:
             return False
         buf.copy_(self._flat.view(-1))
-        self._flat = buf.view(2, self.opts.vocabSize, self.opts.dim)
+        self._flat = buf.view(2, self.sliceRows(), self.opts.dim)
         self.modelmats = [self._flat[0], self._flat[1]]
         self._symm, self._mc = hdl, int(hdl.multicast_ptr)
         self._tick = torch.zeros(1, dtype=torch.float32, device=self.device)

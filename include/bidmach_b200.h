@@ -72,6 +72,29 @@ int word2vecEvalPos(int nrows, int ncols, int shift, int *W, int *LB, int *UB, f
 int word2vecEvalNeg(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A, float *B,
                     float *Retval);
 
+/* Vocabulary slices: the device forms of the reference's multi-node CPU kernels.  The model of
+ * slice `islice` of `nslices` holds the rows of the head (ids below nHead, present on every
+ * slice) followed by the rows of the ids with id % nslices == islice, id at row
+ * (id - nHead) / nslices + nHead (mapIndx, jni/src/BIDMach_CPUMACH.c:80-88); A and B are those
+ * two matrices (one per side: the reference cuts them into Java arrays of maxCols words, device
+ * memory needs no such cut).  W / WA / WB hold global word ids.  A pair is worked on when both
+ * words have a row here and, unless doHead > 1, not both are head words; head rows are written
+ * only when doHead > 0.  Rows must be a multiple of 4 floats and the matrices 16-byte aligned.
+ *
+ * word2vecPosSlice replaces CPUMACH.word2vecPosSlice (jni/src/BIDMach_CPUMACH.c:90-184; called
+ * from networks/Word2Vec.scala:425), word2vecNegSlice replaces CPUMACH.word2vecNegSlice
+ * (BIDMach_CPUMACH.c:267-366; Word2Vec.scala:459).  The two scoring functions replace
+ * Word2Vec.evalPosCPUslice / evalNegCPUslice (Word2Vec.scala:1007-1068, 1134-1200): the sum over
+ * the pairs whose two words both have a row on this slice. */
+int word2vecPosSlice(int nrows, int ncols, int shift, int *W, int *LB, int *UB, float *A, float *B,
+                     float lrate, float vexp, int islice, int nslices, int nHead, int doHead);
+int word2vecNegSlice(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A, float *B,
+                     float lrate, float vexp, int islice, int nslices, int nHead, int doHead);
+int word2vecEvalPosSlice(int nrows, int ncols, int shift, int *W, int *LB, int *UB, float *A, float *B,
+                         float *Retval, int islice, int nslices, int nHead);
+int word2vecEvalNegSlice(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A, float *B,
+                         float *Retval, int islice, int nslices, int nHead);
+
 /* No counterpart in the reference.  Same contract as word2vecEvalNeg, for
  * hosts that must not allocate device memory while they run (a JVM whose matrix
  * cache already owns the card, a process that froze its memory map): the
@@ -290,6 +313,14 @@ void w2v_comm_destroy(w2v_comm *comm);
  * and its write of that element (a few microseconds) is overwritten by the
  * mean; updates before are averaged in, updates after are kept. */
 int w2v_nvls_average(float *mc_base, int64_t n, int rank, int world, int blocks, void *stream);
+
+/* Word2Vec.Opts nSlices / iSlice / nHeadTerms / doHead (networks/Word2Vec.scala:586-590) for the
+ * whole-minibatch calls: A and B given to w2v_dobatch / w2v_evalbatch then hold the rows of that
+ * slice only (w2v_slice_rows of them), the minibatch still carries global ids.  The default is
+ * the whole vocabulary (nslices 1). */
+int w2v_set_slice(w2v_ctx *ctx, int islice, int nslices, int nHead, int doHead);
+/* Rows of a slice's matrices: nHead + 1 + (vocabSize - nHead - 1) / nslices (Word2Vec.scala:106). */
+int64_t w2v_slice_rows(int vocabSize, int nslices, int nHead);
 
 /* Keeps `sms` SMs out of the grids of the update kernels that the following
  * w2v_dobatch / w2v_dobatch_host calls launch (0 = use every SM again), so that

@@ -60,6 +60,8 @@ def port_lib():
         _port = C.CDLL(_build.build_oracle())
         _port.orc_word2vecEvalPos.restype = C.c_double
         _port.orc_word2vecEvalNeg.restype = C.c_double
+        _port.orc_word2vecEvalPosSlice.restype = C.c_double
+        _port.orc_word2vecEvalNegSlice.restype = C.c_double
         _port.orc_count_pairs.restype = C.c_int64
         _port.orc_fill_contexts.restype = C.c_int64
     return _port
@@ -145,6 +147,80 @@ def word2vecEvalNeg(nrows, ncols, nwa, nwb, WA, WB, A, B, nthreads=1):
     return float(port_lib().orc_word2vecEvalNeg(
         C.c_int(nrows), C.c_int(ncols), C.c_int(nwa), C.c_int(nwb), _ip(WA), _ip(WB), _fp(A), _fp(B),
         C.c_int(nthreads)))
+
+
+def slice_rows(vocab, nslices, nhead):
+    """Rows of a slice's matrices: nHeadTerms + 1 + (nfeats - nHeadTerms - 1) / nSlices
+    (Word2Vec.init, networks/Word2Vec.scala:106)."""
+    return vocab if nslices <= 1 else nhead + 1 + (vocab - nhead - 1) // nslices
+
+
+def slice_of_model(M, islice, nslices, nhead):
+    """The rows of a whole-vocabulary matrix that slice ``islice`` stores, in its own order
+    (mapIndx, networks/Word2Vec.scala:665-672): the head, then the ids congruent to islice."""
+    vocab = M.shape[0]
+    ids = np.arange(vocab)
+    mine = ids[(ids >= nhead) & (ids % nslices == islice)]
+    out = np.zeros((slice_rows(vocab, nslices, nhead), M.shape[1]), np.float32)
+    out[:nhead] = M[:nhead]
+    out[(mine - nhead) // nslices + nhead] = M[mine]
+    return out
+
+
+def word2vecPosSlice(nrows, ncols, skip, W, LB, UB, A, B, lrate, vexp, islice, nslices, nhead, do_head=1,
+                     nthreads=1, impl="port"):
+    """In-place positive update of one vocabulary slice; CPUMACH.word2vecPosSlice
+    (BIDMach_CPUMACH.c:90-184).  A, B: the slice's rows, one matrix per side."""
+    W, LB, UB = _i32(W), _i32(LB), _i32(UB)
+    _check_model(A, nrows)
+    _check_model(B, nrows)
+    if impl == "reference":
+        mats = (C.c_void_p * 2)(B.ctypes.data, A.ctypes.data)     # matrix 2m: context rows, 2m+1: centre rows
+        ref_lib().ref_word2vecPosSlice(
+            C.c_int(nrows), C.c_int(ncols), C.c_int(skip), _ip(W), _ip(LB), _ip(UB), mats, C.c_int(2),
+            C.c_float(lrate), C.c_float(vexp), C.c_int(nthreads), C.c_int(islice), C.c_int(nslices),
+            C.c_int(A.shape[0] + 1), C.c_int(nhead), C.c_int(0), C.c_int(do_head))
+    else:
+        port_lib().orc_word2vecPosSlice(
+            C.c_int(nrows), C.c_int(ncols), C.c_int(skip), _ip(W), _ip(LB), _ip(UB), _fp(A), _fp(B),
+            C.c_float(lrate), C.c_float(vexp), C.c_int(nthreads), C.c_int(islice), C.c_int(nslices),
+            C.c_int(nhead), C.c_int(do_head))
+
+
+def word2vecNegSlice(nrows, ncols, nwa, nwb, WA, WB, A, B, lrate, vexp, islice, nslices, nhead, do_head=1,
+                     nthreads=1, impl="port"):
+    """In-place negative update of one vocabulary slice; CPUMACH.word2vecNegSlice
+    (BIDMach_CPUMACH.c:267-366)."""
+    WA, WB = _i32(WA), _i32(WB)
+    _check_model(A, nrows)
+    _check_model(B, nrows)
+    if impl == "reference":
+        mats = (C.c_void_p * 2)(B.ctypes.data, A.ctypes.data)
+        ref_lib().ref_word2vecNegSlice(
+            C.c_int(nrows), C.c_int(ncols), C.c_int(nwa), C.c_int(nwb), _ip(WA), _ip(WB), mats, C.c_int(2),
+            C.c_float(lrate), C.c_float(vexp), C.c_int(nthreads), C.c_int(islice), C.c_int(nslices),
+            C.c_int(A.shape[0] + 1), C.c_int(nhead), C.c_int(0), C.c_int(do_head))
+    else:
+        port_lib().orc_word2vecNegSlice(
+            C.c_int(nrows), C.c_int(ncols), C.c_int(nwa), C.c_int(nwb), _ip(WA), _ip(WB), _fp(A), _fp(B),
+            C.c_float(lrate), C.c_float(vexp), C.c_int(nthreads), C.c_int(islice), C.c_int(nslices),
+            C.c_int(nhead), C.c_int(do_head))
+
+
+def word2vecEvalPosSlice(nrows, ncols, skip, W, LB, UB, A, B, islice, nslices, nhead, nthreads=1):
+    """Word2Vec.evalPosCPUslice (networks/Word2Vec.scala:1007-1068)."""
+    W, LB, UB = _i32(W), _i32(LB), _i32(UB)
+    return float(port_lib().orc_word2vecEvalPosSlice(
+        C.c_int(nrows), C.c_int(ncols), C.c_int(skip), _ip(W), _ip(LB), _ip(UB), _fp(A), _fp(B),
+        C.c_int(nthreads), C.c_int(islice), C.c_int(nslices), C.c_int(nhead)))
+
+
+def word2vecEvalNegSlice(nrows, ncols, nwa, nwb, WA, WB, A, B, islice, nslices, nhead, nthreads=1):
+    """Word2Vec.evalNegCPUslice (networks/Word2Vec.scala:1134-1200)."""
+    WA, WB = _i32(WA), _i32(WB)
+    return float(port_lib().orc_word2vecEvalNegSlice(
+        C.c_int(nrows), C.c_int(ncols), C.c_int(nwa), C.c_int(nwb), _ip(WA), _ip(WB), _fp(A), _fp(B),
+        C.c_int(nthreads), C.c_int(islice), C.c_int(nslices), C.c_int(nhead)))
 
 
 def word2vecNegFilt(nrows, ncols, nwords, nwa, nwb, WA, WB, A, B, lrate, vexp):

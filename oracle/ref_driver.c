@@ -12,6 +12,10 @@
  *   ref_word2vecNeg     -> Java_edu_berkeley_bid_CPUMACH_word2vecNeg     (BIDMach_CPUMACH.c:186-264)
  *   ref_word2vecEvalPos -> Java_edu_berkeley_bid_CPUMACH_word2vecEvalPos (BIDMach_CPUMACH.c:368-427)
  *   ref_word2vecEvalNeg -> Java_edu_berkeley_bid_CPUMACH_word2vecEvalNeg (BIDMach_CPUMACH.c:429-483)
+ *   ref_word2vecPosSlice -> Java_edu_berkeley_bid_CPUMACH_word2vecPosSlice (BIDMach_CPUMACH.c:90-184)
+ *   ref_word2vecNegSlice -> Java_edu_berkeley_bid_CPUMACH_word2vecNegSlice (BIDMach_CPUMACH.c:267-366)
+ *     (the model is a Java float[][]: matrix 2*m holds the context rows and 2*m+1 the centre
+ *     rows of block m of maxCols words; here an array of plain pointers)
  * The two eval functions of the reference add their per-thread sums onto an
  * uninitialised local (BIDMach_CPUMACH.c:379,423 and :439,479), so their
  * return value is only informational; the eval oracle is the restatement of
@@ -56,6 +60,33 @@ extern jdouble Java_edu_berkeley_bid_CPUMACH_word2vecEvalPos(
 extern jdouble Java_edu_berkeley_bid_CPUMACH_word2vecEvalNeg(
     JNIEnv *, jobject, jint, jint, const jint, const jint, jintArray, jintArray,
     jfloatArray, jfloatArray, jint);
+
+extern void Java_edu_berkeley_bid_CPUMACH_word2vecPosSlice(
+    JNIEnv *, jobject, jint, jint, jint, jintArray, jintArray, jintArray, jobjectArray, jfloat, jfloat,
+    jint, jint, jint, jint, jint, jint, jint);
+extern void Java_edu_berkeley_bid_CPUMACH_word2vecNegSlice(
+    JNIEnv *, jobject, jint, jint, jint, jint, jintArray, jintArray, jfloatArray, jfloat, jfloat,
+    jint, jint, jint, jint, jint, jint, jint);
+
+void ref_word2vecPosSlice(int nrows, int ncols, int skip, int *W, int *LB, int *UB, float **mats,
+                          int nmats, float lrate, float vexp, int nthreads, int islice, int nslices,
+                          int maxCols, int nHead, int dualMode, int doHead) {
+  JNIEnv env = &drv_table;
+  stub_objarray mm = {nmats, (void **)mats};
+  Java_edu_berkeley_bid_CPUMACH_word2vecPosSlice(&env, 0, nrows, ncols, skip, W, LB, UB, &mm, lrate,
+                                                 vexp, nthreads, islice, nslices, maxCols, nHead,
+                                                 dualMode, doHead);
+}
+
+void ref_word2vecNegSlice(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float **mats,
+                          int nmats, float lrate, float vexp, int nthreads, int islice, int nslices,
+                          int maxCols, int nHead, int dualMode, int doHead) {
+  JNIEnv env = &drv_table;
+  stub_objarray mm = {nmats, (void **)mats};
+  Java_edu_berkeley_bid_CPUMACH_word2vecNegSlice(&env, 0, nrows, ncols, nwa, nwb, WA, WB, &mm, lrate,
+                                                 vexp, nthreads, islice, nslices, maxCols, nHead,
+                                                 dualMode, doHead);
+}
 
 void ref_word2vecPos(int nrows, int ncols, int skip, int *W, int *LB, int *UB,
                      float *A, float *B, float lrate, float vexp, int nthreads) {

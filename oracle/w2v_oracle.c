@@ -191,6 +191,173 @@ ORC_API double orc_word2vecEvalNeg(int nrows, int ncols, int nwa, int nwb, const
 }
 
 /*
+ * Vocabulary slices.  mapIndx (BIDMach_CPUMACH.c:80-88; networks/Word2Vec.scala:665-672) with the
+ * model of a slice held as one matrix per side (the reference cuts it into blocks of maxCols words
+ * because a Java array is limited to 2^31 elements): ids below nhead have a row on every slice,
+ * an id at or above it belongs to slice id % nslices and sits at row (id - nhead) / nslices + nhead.
+ */
+typedef struct {
+  int64_t row;
+  int mine, head;
+} orc_slot;
+
+static inline orc_slot slice_slot(int id, int islice, int nslices, int nhead) {
+  orc_slot s;
+  s.row = (id >= nhead) ? (id - nhead) / nslices + nhead : id;
+  s.mine = (id >= nhead) && (id % nslices == islice);
+  s.head = (id < nhead);
+  return s;
+}
+
+static inline int slice_pair(orc_slot a, orc_slot b, int do_head) {
+  return (do_head > 1 && a.head && b.head) || (a.mine && b.head) || (b.mine && a.head) ||
+         (a.mine && b.mine);
+}
+
+/* Follows Java_edu_berkeley_bid_CPUMACH_word2vecPosSlice, BIDMach_CPUMACH.c:90-184. */
+ORC_API void orc_word2vecPosSlice(int nrows, int ncols, int skip, const int *W, const int *LB,
+                                  const int *UB, float *A, float *B, float lrate, float vexp,
+                                  int nthreads, int islice, int nslices, int nhead, int do_head) {
+  (void)skip;
+#pragma omp parallel for
+  for (int t = 0; t < nthreads; t++) {
+    float *acc = (float *)malloc(sizeof(float) * (size_t)nrows);
+    int hi = chunk_lo(t + 1, ncols, nthreads);
+    for (int i = chunk_lo(t, ncols, nthreads); i < hi; i++) {
+      int wc = W[i];
+      if (wc < 0) continue;
+      orc_slot sa_ = slice_slot(wc, islice, nslices, nhead);
+      float *arow = A + (int64_t)nrows * sa_.row;
+      float sa = freq_scale(wc, vexp);
+      int touched = 0;
+      memset(acc, 0, sizeof(float) * (size_t)nrows);
+      for (int j = LB[i]; j <= UB[i]; j++) {
+        if (j == 0 || i + j < 0 || i + j >= ncols) continue;
+        int wx = W[i + j];
+        if (wx < 0) continue;
+        orc_slot sb_ = slice_slot(wx, islice, nslices, nhead);
+        if (!slice_pair(sa_, sb_, do_head)) continue;
+        float *brow = B + (int64_t)nrows * sb_.row;
+        float sb = freq_scale(wx, vexp);
+        touched = 1;
+        float g = lrate * (1.0f - guarded_sigmoid(row_dot(arow, brow, nrows)));
+        for (int c = 0; c < nrows; c++) acc[c] += sa * g * brow[c];
+        if (sb_.mine || (sb_.head && do_head))
+          for (int c = 0; c < nrows; c++) brow[c] += sb * g * arow[c];
+      }
+      if (touched && (sa_.mine || (sa_.head && do_head)))
+        for (int c = 0; c < nrows; c++) arow[c] += acc[c];
+    }
+    free(acc);
+  }
+}
+
+/* Follows Java_edu_berkeley_bid_CPUMACH_word2vecNegSlice, BIDMach_CPUMACH.c:267-366. */
+ORC_API void orc_word2vecNegSlice(int nrows, int ncols, int nwa, int nwb, const int *WA,
+                                  const int *WB, float *A, float *B, float lrate, float vexp,
+                                  int nthreads, int islice, int nslices, int nhead, int do_head) {
+#pragma omp parallel for
+  for (int t = 0; t < nthreads; t++) {
+    float *da = (float *)malloc(sizeof(float) * (size_t)nrows * nwa);
+    float *db = (float *)malloc(sizeof(float) * (size_t)nrows);
+    int hi = chunk_lo(t + 1, ncols, nthreads);
+    for (int i = chunk_lo(t, ncols, nthreads); i < hi; i++) {
+      const int *wa = WA + (int64_t)i * nwa;
+      const int *wb = WB + (int64_t)i * nwb;
+      memset(da, 0, sizeof(float) * (size_t)nrows * nwa);
+      for (int k = 0; k < nwb; k++) {
+        orc_slot sb_ = slice_slot(wb[k], islice, nslices, nhead);
+        float *brow = B + (int64_t)nrows * sb_.row;
+        float sb = freq_scale(wb[k], vexp);
+        memset(db, 0, sizeof(float) * (size_t)nrows);
+        for (int j = 0; j < nwa; j++) {
+          orc_slot sa_ = slice_slot(wa[j], islice, nslices, nhead);
+          if (!slice_pair(sa_, sb_, do_head)) continue;
+          float *arow = A + (int64_t)nrows * sa_.row;
+          float sa = freq_scale(wa[j], vexp);
+          float g = -lrate * guarded_sigmoid(row_dot(arow, brow, nrows));
+          float *daj = da + (size_t)j * nrows;
+          for (int c = 0; c < nrows; c++) {
+            db[c] += sb * g * arow[c];
+            daj[c] += sa * g * brow[c];
+          }
+        }
+        if (sb_.mine || (sb_.head && do_head))
+          for (int c = 0; c < nrows; c++) brow[c] += db[c];
+      }
+      for (int j = 0; j < nwa; j++) {
+        orc_slot sa_ = slice_slot(wa[j], islice, nslices, nhead);
+        if (!(sa_.mine || (sa_.head && do_head))) continue;
+        float *arow = A + (int64_t)nrows * sa_.row;
+        const float *daj = da + (size_t)j * nrows;
+        for (int c = 0; c < nrows; c++) arow[c] += daj[c];
+      }
+    }
+    free(db);
+    free(da);
+  }
+}
+
+/* Follows Word2Vec.evalPosCPUslice, networks/Word2Vec.scala:1007-1068: the pairs whose two
+ * words both have a row on this slice (head or mine), head-head pairs included. */
+ORC_API double orc_word2vecEvalPosSlice(int nrows, int ncols, int skip, const int *W, const int *LB,
+                                        const int *UB, const float *A, const float *B, int nthreads,
+                                        int islice, int nslices, int nhead) {
+  (void)skip;
+  double total = 0;
+#pragma omp parallel for reduction(+ : total)
+  for (int t = 0; t < nthreads; t++) {
+    double part = 0;
+    int hi = chunk_lo(t + 1, ncols, nthreads);
+    for (int i = chunk_lo(t, ncols, nthreads); i < hi; i++) {
+      int wc = W[i];
+      if (wc < 0) continue;
+      orc_slot sa_ = slice_slot(wc, islice, nslices, nhead);
+      if (!(sa_.mine || sa_.head)) continue;
+      const float *arow = A + (int64_t)nrows * sa_.row;
+      for (int j = LB[i]; j <= UB[i]; j++) {
+        if (j == 0 || i + j < 0 || i + j >= ncols) continue;
+        int wx = W[i + j];
+        if (wx < 0) continue;
+        orc_slot sb_ = slice_slot(wx, islice, nslices, nhead);
+        if (!(sb_.mine || sb_.head)) continue;
+        float s = guarded_sigmoid(row_dot(arow, B + (int64_t)nrows * sb_.row, nrows));
+        part += log(fmax((double)s, 1e-20));
+      }
+    }
+    total += part;
+  }
+  return total;
+}
+
+/* Follows Word2Vec.evalNegCPUslice, networks/Word2Vec.scala:1134-1200. */
+ORC_API double orc_word2vecEvalNegSlice(int nrows, int ncols, int nwa, int nwb, const int *WA,
+                                        const int *WB, const float *A, const float *B, int nthreads,
+                                        int islice, int nslices, int nhead) {
+  double total = 0;
+#pragma omp parallel for reduction(+ : total)
+  for (int t = 0; t < nthreads; t++) {
+    double part = 0;
+    int hi = chunk_lo(t + 1, ncols, nthreads);
+    for (int i = chunk_lo(t, ncols, nthreads); i < hi; i++) {
+      for (int k = 0; k < nwb; k++) {
+        orc_slot sb_ = slice_slot(WB[(int64_t)i * nwb + k], islice, nslices, nhead);
+        if (!(sb_.mine || sb_.head)) continue;
+        const float *brow = B + (int64_t)nrows * sb_.row;
+        for (int j = 0; j < nwa; j++) {
+          orc_slot sa_ = slice_slot(WA[(int64_t)i * nwa + j], islice, nslices, nhead);
+          if (!(sa_.mine || sa_.head)) continue;
+          float s = guarded_sigmoid(row_dot(A + (int64_t)nrows * sa_.row, brow, nrows));
+          part += log(fmax((double)(1.0f - s), 1e-20));
+        }
+      }
+    }
+    total += part;
+  }
+  return total;
+}
+
+/*
  * Frequent-word subsampling and window bounds.  Follows Word2Vec.wordMats,
  * networks/Word2Vec.scala:214-241, element by element:
  *   - the minibatch is a 2 x ncols int32 matrix stored column-major; row 0 is

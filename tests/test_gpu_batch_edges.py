@@ -92,7 +92,9 @@ def test_unsupported_options_are_refused():
     with pytest.raises(RuntimeError):
         Word2Vec(Opts(dim=100, vocabSize=100, nneg=7, nreuse=3)).init(64)
     with pytest.raises(NotImplementedError):
-        Word2Vec(Opts(nSlices=2))
+        Word2Vec(Opts(nSlices=2, dualMode=True))
+    with pytest.raises(ValueError):
+        Word2Vec(Opts(nSlices=2, iSlice=2))
     with pytest.raises(RuntimeError):
         Word2Vec(Opts(useGPU=False))
 

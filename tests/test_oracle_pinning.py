@@ -159,3 +159,46 @@ def test_shuffle_and_negative_ids(oracle):
     want = np.minimum(999_999, (1_000_000 * u.astype(np.float64) ** 4.0).astype(np.int64))
     assert np.array_equal(ids, want.astype(np.int32))
     assert oracle.negative_ids(np.array([0.99999994], np.float32), np.float32(4.0), 10)[0] == 9
+
+
+@pytest.mark.parametrize("nslices,islice,nhead,do_head", [(4, 1, 20, 1), (3, 0, 0, 1), (2, 1, 50, 0), (4, 3, 37, 2),
+                                                          (8, 5, 16, 1)])
+def test_port_equals_compiled_reference_slices(oracle, nslices, islice, nhead, do_head):
+    """word2vecPosSlice / word2vecNegSlice: the restatement against the reference's own C, bit for
+    bit, on general (conflicting) input with words of every kind: head, this slice's, other slices'."""
+    if not oracle.have_reference():
+        pytest.skip("compiled reference not present on this machine")
+    dim, vocab, ncols = 64, 400, 600
+    rows = oracle.slice_rows(vocab, nslices, nhead)
+    A, B = random_model(rows, dim, 3 + nslices, scale=0.5)
+    W, LB, UB = random_pos(ncols, vocab, 5, 5 + islice)
+    A1, B1, A2, B2 = A.copy(), B.copy(), A.copy(), B.copy()
+    oracle.word2vecPosSlice(dim, ncols, 5, W, LB, UB, A1, B1, 0.05, 0.5, islice, nslices, nhead, do_head, 1, "port")
+    oracle.word2vecPosSlice(dim, ncols, 5, W, LB, UB, A2, B2, 0.05, 0.5, islice, nslices, nhead, do_head, 1,
+                            "reference")
+    assert np.array_equal(A1, A2) and np.array_equal(B1, B2)
+    assert not np.array_equal(A1, A)
+    if do_head == 0:
+        assert np.array_equal(A1[:nhead], A[:nhead]) and np.array_equal(B1[:nhead], B[:nhead])
+    WA, WB = random_neg(150, vocab, 5, 5, 9 + islice)
+    oracle.word2vecNegSlice(dim, 150, 5, 5, WA, WB, A1, B1, 0.02, 0.5, islice, nslices, nhead, do_head, 1, "port")
+    oracle.word2vecNegSlice(dim, 150, 5, 5, WA, WB, A2, B2, 0.02, 0.5, islice, nslices, nhead, do_head, 1,
+                            "reference")
+    assert np.array_equal(A1, A2) and np.array_equal(B1, B2)
+
+
+def test_one_slice_without_head_is_the_plain_kernel(oracle):
+    """nslices = 1, nhead = 0: every id is this slice's own, rows are where they always were."""
+    dim, vocab, ncols = 32, 200, 300
+    A, B = random_model(vocab, dim, 1, scale=0.5)
+    W, LB, UB = random_pos(ncols, vocab, 3, 2)
+    A1, B1, A2, B2 = A.copy(), B.copy(), A.copy(), B.copy()
+    oracle.word2vecPos(dim, ncols, 3, W, LB, UB, A1, B1, 0.05, 0.5, 1, "port")
+    oracle.word2vecPosSlice(dim, ncols, 3, W, LB, UB, A2, B2, 0.05, 0.5, 0, 1, 0, 1, 1, "port")
+    assert np.array_equal(A1, A2) and np.array_equal(B1, B2)
+    e1 = oracle.word2vecEvalPos(dim, ncols, 3, W, LB, UB, A1, B1)
+    e2 = oracle.word2vecEvalPosSlice(dim, ncols, 3, W, LB, UB, A1, B1, 0, 1, 0)
+    assert e1 == e2
+    WA, WB = random_neg(80, vocab, 5, 5, 4)
+    assert oracle.word2vecEvalNeg(dim, 80, 5, 5, WA, WB, A1, B1) == \
+        oracle.word2vecEvalNegSlice(dim, 80, 5, 5, WA, WB, A1, B1, 0, 1, 0)

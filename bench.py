@@ -333,6 +333,10 @@ def run_ours(args):
         elif args.exchange == "nvls":
             raise SystemExit("--exchange nvls: no symmetric memory with a multicast mapping here (%s)"
                              % getattr(model, "_symm_error", "no multicast address"))
+    if args.exchange_kernel:
+        model.exchangeKernel = args.exchange_kernel
+    if args.exchange_blocks:
+        model.EXCHANGE_BLOCKS = {world: args.exchange_blocks}
     overlap = world > 1 and not args.head_sync and (
         args.sync_mode == "overlap" or (args.sync_mode == "auto" and exchange == "nvls"))
     randomise_model()
@@ -613,7 +617,10 @@ def run_ours(args):
     collective = None
     if world > 1:
         nbytes = 4 * model._flat.numel()
-        collective = {"kind": ("multimem.ld_reduce/st kernel over the NVLink multicast mapping (w2v_nvls_average)"
+        in_place = ("peer loads and stores on the replicas' symmetric buffers (w2v_p2p_average)"
+                    if (args.exchange_kernel or ("p2p" if world <= model.P2P_MAX_WORLD else "nvls")) == "p2p"
+                    else "multimem.ld_reduce/st over the NVLink multicast mapping (w2v_nvls_average)")
+        collective = {"kind": ("in-place average kernel: " + in_place
                                if exchange == "nvls" else "ncclAllReduce(avg) via torch.distributed"),
                       "overlapped_with_next_minibatch": bool(overlap), "bytes": nbytes,
                       "sync_every": args.sync_every, "exchanges_in_region": dev_r["exchanges"],
@@ -661,6 +668,10 @@ def main():
     ap.add_argument("--exchange", default="auto", choices=["auto", "nvls", "nccl"],
                     help="multi-GPU: average the model in place through the NVLink multicast mapping "
                          "(nvls; auto picks it where the platform has one) or with NCCL")
+    ap.add_argument("--exchange-kernel", default=None, choices=["p2p", "nvls"],
+                    help="force the in-place average's kernel (default: p2p up to 3 replicas, nvls beyond)")
+    ap.add_argument("--exchange-blocks", type=int, default=None,
+                    help="SMs the overlapped in-place average runs on (default by replica count)")
     ap.add_argument("--sync-mode", default="auto", choices=["auto", "overlap", "blocking"],
                     help="multi-GPU: run the exchange beside the next minibatch or block on it "
                          "(auto: overlap with nvls, blocking with nccl)")

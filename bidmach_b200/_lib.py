@@ -89,6 +89,8 @@ SIGNATURES = {
     "w2v_allreduce_avg": (_I, [_P, _P, _P, C.c_int64, _P]),
     "w2v_comm_destroy": (None, [_P]),
     "w2v_nvls_average": (_I, [_P, C.c_int64, _I, _I, _I, _P]),
+    "w2v_p2p_average": (_I, [C.POINTER(_P), C.c_int64, _I, _I, _I, _P]),
+    "w2v_wait_pos": (_I, [_P, _P]),
     "w2v_reserve_sms": (_I, [_P, _I]),
     "w2v_set_slice": (_I, [_P, _I, _I, _I, _I]),
     "w2v_slice_rows": (C.c_int64, [_I, _I, _I]),

@@ -298,6 +298,8 @@ struct w2v_ctx {
   int *fault_host;         // pinned: set by a staged kernel that gave up waiting for its copies
   int sm_reserve;          // SMs the update kernels leave free (w2v_reserve_sms)
   w2v::SliceMap slice;     // which rows of the vocabulary the caller's matrices hold (w2v_set_slice)
+  cudaEvent_t ev_pos;      // end of the latest positive update (w2v_wait_pos)
+  int pos_recorded;
   void *cub_tmp;
   size_t cub_tmp_bytes;
   // pinned host
@@ -449,6 +451,7 @@ void w2v_destroy(w2v_ctx *c) {
   for (int r = 0; r < kRing; r++)
     for (int k = 0; k < 5; k++) if (c->ev[r][k]) cudaEventDestroy(c->ev[r][k]);
   if (c->ev_counts) cudaEventDestroy(c->ev_counts);
+  if (c->ev_pos) cudaEventDestroy(c->ev_pos);
   cudaSetDevice(prev);
   delete c;
 }
@@ -507,6 +510,7 @@ int w2v_create(const w2v_opts *opts, int ncols, w2v_ctx **out) {
   c->hot.stats = nullptr;   // set once the counts buffer exists
   if (e == cudaSuccess) e = cudaMallocHost(&c->counts_host, 256);
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_counts, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_pos, cudaEventDisableTiming);
   if (e == cudaSuccess) e = cudaMallocHost(&c->retvals_host, 256);
   if (e == cudaSuccess)
     e = cub::DeviceScan::ExclusiveSum(nullptr, scan_bytes, c->cnt, c->off, ncols);
@@ -535,6 +539,12 @@ int64_t w2v_slice_rows(int vocabSize, int nslices, int nHead) {
   // Word2Vec.init: nHeadTerms + 1 + (nfeats - nHeadTerms - 1) / nSlices (networks/Word2Vec.scala:106)
   if (nslices <= 1) return vocabSize;
   return (int64_t)nHead + 1 + (vocabSize - nHead - 1) / nslices;
+}
+
+int w2v_wait_pos(w2v_ctx *c, void *stream) {
+  if (!c) return 1;
+  if (!c->pos_recorded) return 0;
+  return (int)cudaStreamWaitEvent((cudaStream_t)stream, c->ev_pos, 0);
 }
 
 int w2v_reserve_sms(w2v_ctx *c, int sms) {
@@ -699,13 +709,15 @@ int w2v_dobatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, float *A, 
   const float nsteps = (float)pos / (float)c->first_pos;
   const float lrpos = o.lrate * (float)pow((double)nsteps, -(double)o.texp);
   const float lrneg = o.eqPosNeg ? lrpos : lrpos / (float)o.nneg;
-  w2v::SmReserve reserve(c->sm_reserve);
   int err = w2v_wordmats(c, tokens, u, batch_id, stream);
   if (err) return err;
   err = w2v::pos_update_async(o.dim, c->ncols, nullptr, o.nskip, c->words, c->lb, c->ub, A, B,
                               lrpos, o.vexp, c->hot, c->slice, stream);
   if (err) return err;
+  W2V_CHECK(cudaEventRecord(c->ev_pos, stream));
+  c->pos_recorded = 1;
   mark(c, 3, stream);
+  w2v::SmReserve reserve(c->sm_reserve);   // the negative update leaves these SMs to another stream's kernel
   int groups = 0;
   const int *groups_dev = nullptr;
   group_count(c, &groups, &groups_dev);

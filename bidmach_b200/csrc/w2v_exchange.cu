@@ -13,6 +13,13 @@
 //    allocated as symmetric memory with a multicast mapping (one process per GPU;
 //    torch.distributed's symmetric memory does that).
 //
+//    w2v_p2p_average does the same with plain loads and stores on the replicas' own addresses
+//    of the buffer (every replica reads its slice from all peers, adds, and writes the mean to
+//    all of them).  A multimem access moves the requester's own copy through the switch as well,
+//    n * (1 + 1/replicas) bytes per direction and GPU against 2 * n * (replicas - 1) / replicas
+//    for peer accesses: the peer form moves less for two or three replicas, the multicast form
+//    for four or more.
+//
 // 2. w2v_comm_* / w2v_allreduce_avg: the same average through NCCL, for hosts
 //    that own the model buffers themselves (a JVM with one thread per GPU and
 //    matrices allocated by its matrix library).  NCCL is loaded at run time
@@ -67,6 +74,65 @@ __global__ void __launch_bounds__(kAvgThreads) nvls_average_kernel(float *mc, in
     float4 v = multimem_sum_v4(mc + 4 * i);
     v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
     multimem_store_v4(mc + 4 * i, v);
+  }
+}
+
+constexpr int kMaxPeers = 8;
+struct PeerPtrs {
+  float *p[kMaxPeers];
+};
+
+__device__ __forceinline__ float4 load_sys_v4(const float *a) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(a)
+               : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void store_sys_v4(float *a, float4 v) {
+  asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a), "f"(v.x), "f"(v.y),
+               "f"(v.z), "f"(v.w)
+               : "memory");
+}
+
+// Every pointer addresses the same element of the buffer on one replica; first_vec / nvec
+// delimit this replica's slice in 16-byte vectors.
+template <int WORLD>
+__global__ void __launch_bounds__(kAvgThreads) p2p_average_kernel(PeerPtrs pp, int64_t first_vec,
+                                                                  int64_t nvec, float scale) {
+  constexpr int U = WORLD <= 2 ? 4 : 2;   // vectors in flight per thread and replica
+  const int64_t stride = (int64_t)gridDim.x * kAvgThreads;
+  int64_t i = (int64_t)blockIdx.x * kAvgThreads + threadIdx.x;
+  for (; i + (U - 1) * stride < nvec; i += U * stride) {
+    float4 v[U][WORLD];
+#pragma unroll
+    for (int u = 0; u < U; u++)
+#pragma unroll
+      for (int r = 0; r < WORLD; r++) v[u][r] = load_sys_v4(pp.p[r] + 4 * (first_vec + i + u * stride));
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      float4 a = v[u][0];
+#pragma unroll
+      for (int r = 1; r < WORLD; r++) {
+        a.x += v[u][r].x; a.y += v[u][r].y; a.z += v[u][r].z; a.w += v[u][r].w;
+      }
+      a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
+#pragma unroll
+      for (int r = 0; r < WORLD; r++) store_sys_v4(pp.p[r] + 4 * (first_vec + i + u * stride), a);
+    }
+  }
+  for (; i < nvec; i += stride) {
+    float4 a = load_sys_v4(pp.p[0] + 4 * (first_vec + i));
+#pragma unroll
+    for (int r = 1; r < WORLD; r++) {
+      const float4 b = load_sys_v4(pp.p[r] + 4 * (first_vec + i));
+      a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+    a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
+#pragma unroll
+    for (int r = 0; r < WORLD; r++) store_sys_v4(pp.p[r] + 4 * (first_vec + i), a);
   }
 }
 
@@ -151,6 +217,38 @@ int w2v_nvls_average(float *mc_base, int64_t n, int rank, int world, int blocks,
   const int64_t need = (mine + kAvgThreads - 1) / kAvgThreads;
   if (blocks > need) blocks = (int)need;
   nvls_average_kernel<<<blocks, kAvgThreads, 0, stream>>>(mc_base + 4 * first, mine, 1.0f / (float)world);
+  w2v::count_launch(1);
+  return (int)cudaGetLastError();
+}
+
+int w2v_p2p_average(float *const *replicas_host, int64_t n, int rank, int world, int blocks, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!replicas_host || world < 1 || world > kMaxPeers || rank < 0 || rank >= world || n < 0) return 1;
+  if (n & 3) return 1;
+  PeerPtrs pp;
+  for (int r = 0; r < kMaxPeers; r++) {
+    // this replica's own copy first: its loads are the cheap ones and start the sums
+    pp.p[r] = r < world ? replicas_host[(rank + r) % world] : nullptr;
+    if (r < world && (!pp.p[r] || ((uintptr_t)pp.p[r] & 15))) return 1;
+  }
+  const int64_t nvec = n / 4;
+  const int64_t per = nvec / world;
+  const int64_t first = per * rank;
+  const int64_t mine = (rank == world - 1) ? nvec - first : per;
+  if (mine <= 0 || world == 1) return 0;
+  if (blocks <= 0) blocks = w2v::device_sm_count();
+  const int64_t need = (mine + kAvgThreads - 1) / kAvgThreads;
+  if (blocks > need) blocks = (int)need;
+  const float scale = 1.0f / (float)world;
+  switch (world) {
+    case 2: p2p_average_kernel<2><<<blocks, kAvgThreads, 0, stream>>>(pp, first, mine, scale); break;
+    case 3: p2p_average_kernel<3><<<blocks, kAvgThreads, 0, stream>>>(pp, first, mine, scale); break;
+    case 4: p2p_average_kernel<4><<<blocks, kAvgThreads, 0, stream>>>(pp, first, mine, scale); break;
+    case 5: p2p_average_kernel<5><<<blocks, kAvgThreads, 0, stream>>>(pp, first, mine, scale); break;
+    case 6: p2p_average_kernel<6><<<blocks, kAvgThreads, 0, stream>>>(pp, first, mine, scale); break;
+    case 7: p2p_average_kernel<7><<<blocks, kAvgThreads, 0, stream>>>(pp, first, mine, scale); break;
+    default: p2p_average_kernel<8><<<blocks, kAvgThreads, 0, stream>>>(pp, first, mine, scale); break;
+  }
   w2v::count_launch(1);
   return (int)cudaGetLastError();
 }

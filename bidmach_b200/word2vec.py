@@ -179,6 +179,8 @@ class Word2Vec:
             _check(_lib.load().w2v_dobatch(self._ctx, toks.data_ptr(), self._uniforms(uniforms),
                                            self.modelmats[1].data_ptr(), self.modelmats[0].data_ptr(),
                                            int(pos), self._batches, self._stream()), "w2v_dobatch")
+        if getattr(self, "_pending", None) is not None:
+            self._launch_pending(after_pos=True)
 
     def evalbatch(self, gmats, ipass: int, pos: int, uniforms=None) -> float:
         """Word2Vec.evalbatch (Word2Vec.scala:192-212): mean log-likelihood score."""
@@ -208,6 +210,8 @@ class Word2Vec:
                                                 self.modelmats[1].data_ptr(), self.modelmats[0].data_ptr(),
                                                 int(pos), self._batches, C.byref(npairs),
                                                 self._stream()), "w2v_dobatch_host")
+        if getattr(self, "_pending", None) is not None:
+            self._launch_pending(after_pos=True)
         return npairs.value
 
     def evalbatchg(self, mats, ipass: int, pos: int) -> float:
@@ -310,9 +314,9 @@ class Word2Vec:
                 mats = flat if flat is not None else self.modelmats
                 bufs = [mats[j][:rows] for j in range(2)]   # the head of a matrix is contiguous
         if getattr(self, "_mc", 0) and istep <= 0:
-            # the model lives in symmetric memory: one multimem kernel per replica, fenced by two
+            # the model lives in symmetric memory: one averaging kernel per replica, fenced by two
             # one-element collectives (all replicas done updating / all slices written)
-            self._nvls_average(group, 0)
+            self._inplace_average(group, 0)
             return
         avg = dist.ReduceOp.AVG if dist.get_backend(group) == "nccl" else None
         for m in bufs:
@@ -322,9 +326,12 @@ class Word2Vec:
                 dist.all_reduce(m, op=dist.ReduceOp.SUM, group=group)
                 m.mul_(1.0 / dist.get_world_size(group))
 
-    # SMs the overlapped NVLS average runs on, per replica count: a replica pulls 1/world of the
-    # buffer through the switch, so fewer SMs keep up as the job grows
-    NVLS_BLOCKS = {2: 24, 3: 16, 4: 12}
+    # SMs the overlapped in-place average runs on, per replica count: a replica handles 1/world
+    # of the buffer, so fewer SMs keep up as the job grows
+    EXCHANGE_BLOCKS = {2: 32, 3: 24, 4: 16}
+    # replicas up to which the average uses peer loads and stores instead of the multicast
+    # address (which moves a replica's own copy through the switch too: more bytes for few replicas)
+    P2P_MAX_WORLD = 3
 
     def enableSymmetric(self, group=None) -> bool:
         """Moves the model into symmetric memory mapped on every replica's GPU through an NVLink
@@ -354,34 +361,68 @@ class Word2Vec:
         self._flat = buf.view(2, self.sliceRows(), self.opts.dim)
         self.modelmats = [self._flat[0], self._flat[1]]
         self._symm, self._mc = hdl, int(hdl.multicast_ptr)
+        world = dist.get_world_size(group)
+        self._peers = (C.c_void_p * world)(*[int(p) for p in hdl.buffer_ptrs])
         self._tick = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._pending = None
         return True
 
-    def _nvls_average(self, group, blocks: int):
-        """Enqueues fence, w2v_nvls_average, fence on the current stream."""
+    def _inplace_average(self, group, blocks: int, kind: str | None = None):
+        """Enqueues fence, averaging kernel, fence on the current stream.  ``kind``: "p2p" (peer
+        loads and stores), "nvls" (multicast address), default by replica count."""
         import torch.distributed as dist
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        kind = kind or getattr(self, "exchangeKernel", None) or ("p2p" if world <= self.P2P_MAX_WORLD else "nvls")
+        lib = _lib.load()
         dist.all_reduce(self._tick, group=group)     # every replica has finished its updates
         with torch.cuda.device(self.device):
-            _check(_lib.load().w2v_nvls_average(self._mc, self._flat.numel(), dist.get_rank(group),
-                                                dist.get_world_size(group), blocks, self._stream()),
-                   "w2v_nvls_average")
+            if kind == "p2p":
+                _check(lib.w2v_p2p_average(self._peers, self._flat.numel(), rank, world, blocks,
+                                           self._stream()), "w2v_p2p_average")
+            else:
+                _check(lib.w2v_nvls_average(self._mc, self._flat.numel(), rank, world, blocks,
+                                            self._stream()), "w2v_nvls_average")
         dist.all_reduce(self._tick, group=group)     # every replica's slice has been written everywhere
 
     def reserveSMs(self, sms: int):
-        """Keeps ``sms`` SMs out of the grids of the following minibatches' update kernels (0 = use
+        """Keeps ``sms`` SMs out of the grid of the following minibatches' negative update (0 = use
         all), so that a kernel on another stream finds room."""
         with torch.cuda.device(self.device):
             _check(_lib.load().w2v_reserve_sms(self._ctx, int(sms)), "w2v_reserve_sms")
+
+    def _launch_pending(self, after_pos: bool):
+        """Starts the requested in-place average on the side stream: after the positive update of
+        the minibatch just enqueued (so that it runs beside the negative update only, which loses
+        nothing to it), or after everything enqueued so far."""
+        group, blocks = self._pending
+        self._pending = None
+        if getattr(self, "_comm", None) is None:
+            self._comm = torch.cuda.Stream(device=self.device, priority=-1)
+        compute = torch.cuda.current_stream(self.device)
+        if after_pos:
+            with torch.cuda.device(self.device):
+                _check(_lib.load().w2v_wait_pos(self._ctx, int(self._comm.cuda_stream)), "w2v_wait_pos")
+        else:
+            taken = torch.cuda.Event()
+            taken.record(compute)
+            self._comm.wait_event(taken)
+        with torch.cuda.stream(self._comm):
+            self._inplace_average(group, blocks)
+            done = torch.cuda.Event()
+            done.record(self._comm)
+        self._merge = done
+        self._merge_inplace = True
 
     def startMerge(self, group=None):
         """Overlapped form of mergeModelFn; training goes on while the exchange runs on a side
         stream, and ``finishMerge`` (called by the learner one minibatch later, or by the next
         start) makes the compute stream wait for it.
 
-        With the model in symmetric memory the average is taken in place by w2v_nvls_average on a
-        few SMs (the update kernels of the next minibatch leave them free): an element is read on
-        all replicas, averaged and written back within microseconds, so it keeps every update
-        made before and after that moment and loses only those that land in between.  Otherwise
+        With the model in symmetric memory the average is taken in place (w2v_nvls_average or
+        w2v_p2p_average) on a few SMs beside the negative update of the next minibatch, which
+        leaves them free; it starts when that minibatch's positive update has finished.  An element
+        is read on all replicas, averaged and written back within microseconds, so it keeps every
+        update made before and after that moment and loses only those that land in between.  Otherwise
         the model is snapshotted, the snapshot averaged with NCCL, and ``finishMerge`` adds
         ``average - snapshot`` to the live model (two extra model-sized buffers)."""
         import torch.distributed as dist
@@ -390,20 +431,9 @@ class Word2Vec:
         self.finishMerge()
         world = dist.get_world_size(group)
         if getattr(self, "_mc", 0):
-            if getattr(self, "_comm", None) is None:
-                self._comm = torch.cuda.Stream(device=self.device, priority=-1)
-            compute = torch.cuda.current_stream(self.device)
-            taken = torch.cuda.Event()
-            taken.record(compute)
-            blocks = self.NVLS_BLOCKS.get(world, 8)
-            with torch.cuda.stream(self._comm):
-                self._comm.wait_event(taken)
-                self._nvls_average(group, blocks)
-                done = torch.cuda.Event()
-                done.record(self._comm)
+            blocks = self.EXCHANGE_BLOCKS.get(world, 12)
+            self._pending = (group, blocks)     # launched by the next minibatch call, or by finishMerge
             self.reserveSMs(blocks)
-            self._merge = done
-            self._merge_inplace = True
             return
         self._merge_inplace = False
         n = self._flat.numel()
@@ -436,6 +466,8 @@ class Word2Vec:
         self._merge = done
 
     def finishMerge(self):
+        if getattr(self, "_pending", None) is not None:
+            self._launch_pending(after_pos=False)    # no minibatch came in between
         if getattr(self, "_merge", None) is None:
             return
         compute = torch.cuda.current_stream(self.device)

@@ -313,6 +313,11 @@ void w2v_comm_destroy(w2v_comm *comm);
  * and its write of that element (a few microseconds) is overwritten by the
  * mean; updates before are averaged in, updates after are kept. */
 int w2v_nvls_average(float *mc_base, int64_t n, int rank, int world, int blocks, void *stream);
+/* The same with plain peer loads and stores: replicas_host[r] (a host array of `world` <= 8
+ * device pointers) is replica r's address of the buffer as this GPU sees it (peer access or
+ * symmetric memory), replicas_host[rank] the local one.  Moves fewer bytes over NVLink than the
+ * multicast form for two or three replicas. */
+int w2v_p2p_average(float *const *replicas_host, int64_t n, int rank, int world, int blocks, void *stream);
 
 /* Word2Vec.Opts nSlices / iSlice / nHeadTerms / doHead (networks/Word2Vec.scala:586-590) for the
  * whole-minibatch calls: A and B given to w2v_dobatch / w2v_evalbatch then hold the rows of that
@@ -322,11 +327,16 @@ int w2v_set_slice(w2v_ctx *ctx, int islice, int nslices, int nHead, int doHead);
 /* Rows of a slice's matrices: nHead + 1 + (vocabSize - nHead - 1) / nslices (Word2Vec.scala:106). */
 int64_t w2v_slice_rows(int vocabSize, int nslices, int nHead);
 
-/* Keeps `sms` SMs out of the grids of the update kernels that the following
+/* Keeps `sms` SMs out of the grid of the negative update that the following
  * w2v_dobatch / w2v_dobatch_host calls launch (0 = use every SM again), so that
  * a kernel on another stream -- the overlapped w2v_nvls_average -- finds free
- * SMs while a minibatch trains. */
+ * SMs while it runs (the negative update is bound by the L2's atomic throughput
+ * and loses nothing measurable to a few SMs fewer). */
 int w2v_reserve_sms(w2v_ctx *ctx, int sms);
+/* Makes `stream` wait until the positive update of the latest w2v_dobatch / w2v_dobatch_host call
+ * has finished (and with it everything of the minibatches before): the point from which an
+ * exchange on another stream runs beside the negative update only. */
+int w2v_wait_pos(w2v_ctx *ctx, void *stream);
 
 /* Second half of an overlapped model average (multi-GPU): the caller snapshots
  * its replica into `base`, averages the snapshots of all replicas into `avg`

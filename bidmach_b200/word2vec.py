@@ -326,9 +326,11 @@ class Word2Vec:
                 dist.all_reduce(m, op=dist.ReduceOp.SUM, group=group)
                 m.mul_(1.0 / dist.get_world_size(group))
 
-    # SMs the overlapped in-place average runs on, per replica count: a replica handles 1/world
-    # of the buffer, so fewer SMs keep up as the job grows
-    EXCHANGE_BLOCKS = {2: 32, 3: 24, 4: 16}
+    # SMs the overlapped in-place average runs on, per replica count (24 beyond four): a replica
+    # handles 1/world of the buffer, so fewer SMs keep up as the job grows.  Generous on purpose:
+    # the negative update beside it is bound by the L2's atomic throughput and ran no slower with
+    # 48 of 148 SMs held back.
+    EXCHANGE_BLOCKS = {2: 48, 3: 40, 4: 32}
     # replicas up to which the average uses peer loads and stores instead of the multicast
     # address (which moves a replica's own copy through the switch too: more bytes for few replicas)
     P2P_MAX_WORLD = 3
@@ -431,7 +433,7 @@ class Word2Vec:
         self.finishMerge()
         world = dist.get_world_size(group)
         if getattr(self, "_mc", 0):
-            blocks = self.EXCHANGE_BLOCKS.get(world, 12)
+            blocks = self.EXCHANGE_BLOCKS.get(world, 24)
             self._pending = (group, blocks)     # launched by the next minibatch call, or by finishMerge
             self.reserveSMs(blocks)
             return

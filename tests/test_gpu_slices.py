@@ -133,9 +133,19 @@ def test_sliced_minibatch_calls_follow_the_slice_kernels(oracle):
     en = oracle.word2vecEvalNegSlice(D, wa.shape[0], 5, 5, wa.cpu().numpy(), wb.cpu().numpy(), A, B, 1, 4, 1000, 4)
     want = oracle.eval_score(ep, en, 5, wb.numel())
     assert abs(s0 - want) <= TOL * abs(want)
+    from bidmach_b200 import CUMACHSlice
+
+    def positive_score():
+        r = torch.zeros(1, device="cuda")
+        assert CUMACHSlice.word2vecEvalPosSlice(D, N, 5, wkeep, lbkeep, ubkeep, m.modelmats[1], m.modelmats[0], r,
+                                                1, 4, 1000) == 0
+        return r.item()
+
+    wkeep, lbkeep, ubkeep = words.clone(), lb.clone(), ub.clone()
+    p0 = positive_score()
     for k in range(3):
         m.dobatch([toks], 0, (k + 1) * N)
     torch.cuda.synchronize()
     assert torch.equal(m.modelmats[0][:1000], before[0][:1000]) and torch.equal(m.modelmats[1][:1000], before[1][:1000])
     assert not torch.equal(m.modelmats[0][1000:], before[0][1000:])
-    assert m.evalbatch([toks], 0, N) > s0
+    assert positive_score() > p0        # the slice's own positive pairs became more likely

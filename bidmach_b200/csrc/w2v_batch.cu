@@ -220,6 +220,62 @@ __global__ void shuffle_contexts_kernel(const int *__restrict__ counts, int nreu
     out[i] = ctx[permute_index(i, n, keys)];
 }
 
+// The shuffled context matrix and the negative ids in one pass, without the ordered pair list
+// in between: place i of WB takes pair perm(i) of the (centre ascending, offset ascending)
+// order, which is found where it lies -- the centre by bisection of the scanned pair counts,
+// the context by walking that centre's window -- instead of being written out by
+// fill_pairs_kernel and gathered again.  Same WB and WA, bit for bit, as fill + shuffle +
+// negative_ids_kernel.
+__global__ void pairs_and_negatives_kernel(int ncols, const int *__restrict__ counts, int nreuse, int nneg,
+                                           PermKeys keys, const int *__restrict__ words,
+                                           const int *__restrict__ lb, const int *__restrict__ ub,
+                                           const int *__restrict__ off, const float *__restrict__ unegs,
+                                           Rng rng, int vocab, float expt, int *__restrict__ wb,
+                                           int *__restrict__ wa) {
+  const uint32_t n = (uint32_t)counts[0];
+  const int64_t groups = counts[1];
+  const int64_t m = groups * nreuse, nn = groups * nneg;
+  const int64_t total = m > nn ? m : nn;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    if (i < m) {
+      const int p = (int)permute_index((uint32_t)i, n, keys);
+      // the last centre whose first pair is at or before p (it has pairs: the next one starts after p)
+      int lo = 0, hi = ncols - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (off[mid] <= p) lo = mid; else hi = mid - 1;
+      }
+      int k = p - off[lo];
+      const int top = ub[lo];
+      int w = -1;
+      for (int j = lb[lo]; j <= top; j++) {
+        if (j == 0) continue;
+        const int cand = words[lo + j];
+        if (cand < 0) continue;
+        if (k-- == 0) {
+          w = cand;
+          break;
+        }
+      }
+      wb[i] = w;
+    }
+    if (i < nn) {
+      float u;
+      if (unegs) {
+        u = unegs[i];
+      } else {
+        const uint64_t blk = (uint64_t)i >> 2;
+        PhiloxOut r = philox4x32_10((uint32_t)blk, (uint32_t)(blk >> 32), kStreamNegs, rng.batch, rng.k0, rng.k1);
+        u = u01(r.v[i & 3]);
+      }
+      const double v = (double)vocab * pow((double)u, (double)expt);
+      const int id = (v >= 2147483647.0) ? 2147483647 : (int)v;
+      wa[i] = min(id, vocab - 1);
+    }
+  }
+}
+
 // n draws, or counts[1] * nneg of them when the count is only known on the device
 __global__ void negative_ids_kernel(int64_t n, const int *__restrict__ counts, int nneg,
                                     const float *__restrict__ unegs, Rng rng, int vocab,
@@ -300,6 +356,7 @@ struct w2v_ctx {
   w2v::SliceMap slice;     // which rows of the vocabulary the caller's matrices hold (w2v_set_slice)
   cudaEvent_t ev_pos;      // end of the latest positive update (w2v_wait_pos)
   int pos_recorded;
+  int have_list;           // the latest preprocessing wrote the ordered pair list (ctx_in)
   void *cub_tmp;
   size_t cub_tmp_bytes;
   // pinned host
@@ -600,9 +657,18 @@ static int take_fault(w2v_ctx *c) {
   return 0;
 }
 
+// keep_list: also write the ordered pair list (w2v_buffers.contexts); the minibatch calls do not
+// need it and build WB straight from the token windows.
+static int wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64_t batch_id,
+                    cudaStream_t stream, bool keep_list);
+
 int w2v_wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64_t batch_id,
                  void *stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
+  return wordmats(c, tokens, u, batch_id, (cudaStream_t)stream_, true);
+}
+
+static int wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64_t batch_id,
+                    cudaStream_t stream, bool keep_list) {
   if (int fault = take_fault(c)) return fault;
   const w2v_opts &o = c->o;
   const int n = c->ncols;
@@ -632,10 +698,13 @@ int w2v_wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64_t 
                             cudaMemcpyDeviceToHost, stream));
   W2V_CHECK(cudaEventRecord(c->ev_counts, stream));
   c->counts_pending = 1;
-  w2v::fill_pairs_kernel<<<blocks, threads, 0, stream>>>(n, o.nskip, c->words, c->lb, c->ub, c->off,
-                                                        up, rng, c->ctx_in,
-                                                        by_sort ? c->key_in : nullptr);
-  w2v::count_launch(4);
+  keep_list = keep_list || by_sort;
+  c->have_list = keep_list ? 1 : 0;
+  if (keep_list)
+    w2v::fill_pairs_kernel<<<blocks, threads, 0, stream>>>(n, o.nskip, c->words, c->lb, c->ub, c->off,
+                                                          up, rng, c->ctx_in,
+                                                          by_sort ? c->key_in : nullptr);
+  w2v::count_launch(keep_list ? 4 : 3);
   W2V_CHECK(cudaGetLastError());
   mark(c, 1, stream);
   if (by_sort) {
@@ -658,6 +727,17 @@ int w2v_wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64_t 
     // everything downstream reads the counts on the device: nothing waits for the host
     const int64_t max_groups = c->max_pairs / o.nreuse;
     const int64_t max_negs = max_groups * o.nneg;
+    if (!keep_list && c->max_pairs > 0) {
+      const int64_t most = std::max<int64_t>(c->max_pairs, max_negs);
+      const int fused_blocks = (int)std::min<int64_t>((most + threads - 1) / threads,
+                                                     (int64_t)w2v::device_sm_count() * 16);
+      w2v::pairs_and_negatives_kernel<<<fused_blocks, threads, 0, stream>>>(
+          n, c->counts, o.nreuse, o.nneg, make_perm_keys(o, batch_id), c->words, c->lb, c->ub, c->off, un,
+          rng, o.vocabSize, c->expt, c->ctx_out, c->wa);
+      w2v::count_launch(1);
+      mark(c, 2, stream);
+      return (int)cudaGetLastError();
+    }
     if (c->max_pairs > 0) {
       const int shuffle_blocks = (int)std::min<int64_t>((c->max_pairs + threads - 1) / threads,
                                                        (int64_t)w2v::device_sm_count() * 16);
@@ -680,7 +760,7 @@ int w2v_buffers(w2v_ctx *c, w2v_buffers_t *out) {
   int err = settle_counts(c);
   if (err) return err;
   out->words = c->words; out->lb = c->lb; out->ub = c->ub;
-  out->contexts = c->ctx_in;
+  out->contexts = c->have_list ? c->ctx_in : nullptr;
   out->WB = c->ctx_out;
   out->WA = c->wa;
   out->npairs = c->npairs;
@@ -709,7 +789,7 @@ int w2v_dobatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, float *A, 
   const float nsteps = (float)pos / (float)c->first_pos;
   const float lrpos = o.lrate * (float)pow((double)nsteps, -(double)o.texp);
   const float lrneg = o.eqPosNeg ? lrpos : lrpos / (float)o.nneg;
-  int err = w2v_wordmats(c, tokens, u, batch_id, stream);
+  int err = wordmats(c, tokens, u, batch_id, stream, false);
   if (err) return err;
   err = w2v::pos_update_async(o.dim, c->ncols, nullptr, o.nskip, c->words, c->lb, c->ub, A, B,
                               lrpos, o.vexp, c->hot, c->slice, stream);
@@ -732,7 +812,7 @@ int w2v_evalbatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, const fl
                   const float *B, uint64_t batch_id, double *score_host, void *stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   const w2v_opts &o = c->o;
-  int err = w2v_wordmats(c, tokens, u, batch_id, stream);
+  int err = wordmats(c, tokens, u, batch_id, stream, false);
   if (err) return err;
   W2V_CHECK(cudaMemsetAsync(c->retvals, 0, 2 * sizeof(float), stream));
   err = w2v::pos_eval_async(o.dim, c->ncols, nullptr, o.nskip, c->words, c->lb, c->ub, A, B,

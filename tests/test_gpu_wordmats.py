@@ -114,3 +114,35 @@ def test_init_model_matches_restatement(oracle):
     assert np.array_equal(m.modelmats[0].cpu().numpy(), want)
     assert float(m.modelmats[1].abs().max()) == 0.0
     assert abs(float(m.modelmats[0].mean())) < 1e-4 and float(m.modelmats[0].abs().max()) <= 0.5 / 100
+
+
+@pytest.mark.parametrize("n,nskip,nneg,nreuse,wsample,seed", [(4096, 5, 5, 5, 1e-3, 1), (1000, 3, 10, 5, 1.0, 2),
+                                                              (777, 2, 5, 10, 1e-3, 3), (5000, 5, 5, 1, 1.0, 4),
+                                                              (37, 5, 5, 5, 1.0, 5), (200_000, 5, 5, 5, 1.0, 6)])
+def test_minibatch_calls_build_the_same_lists_without_the_ordered_pair_list(n, nskip, nneg, nreuse, wsample, seed):
+    """w2v_dobatch / w2v_evalbatch never write the ordered pair list: one kernel finds pair perm(i)
+    where it lies in the token windows and draws the negatives.  Its WB and WA must equal, bit for
+    bit, what w2v_wordmats (ordered list, then shuffle, then negatives) builds for the same
+    minibatch and batch id."""
+    import ctypes as C
+    from bidmach_b200 import _lib, Word2Vec
+    o = _opts(nskip=nskip, nneg=nneg, nreuse=nreuse, wsample=wsample, lrate=0.0, seed=seed)
+    toks = dev(_tokens(n, o.vocabSize, seed))
+    m = Word2Vec(o).init(n)
+    lib = _lib.load()
+    for call in ("train", "score"):
+        if call == "train":
+            m.dobatch([toks], 0, n)
+        else:
+            m.evalbatch([toks], 0, n)
+        b = _lib.W2VBuffers()
+        assert lib.w2v_buffers(m._ctx, C.byref(b)) == 0
+        assert not b.contexts                     # no ordered list was written
+        g = b.ngroups
+        from bidmach_b200.word2vec import _view_i32
+        wb_fused = _view_i32(b.WB, g * nreuse, m.device).clone()
+        wa_fused = _view_i32(b.WA, g * nneg, m.device).clone()
+        words, lb, ub, wa, wb = m.wordMats([toks], batch_id=m._batches)
+        assert wa.shape[0] == g
+        assert torch.equal(wb.reshape(-1), wb_fused) and torch.equal(wa.reshape(-1), wa_fused)
+        assert m.last_contexts.numel() == b.npairs

@@ -23,6 +23,8 @@
 
 #include <algorithm>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_scan.cuh>
 
@@ -400,6 +402,15 @@ static void mark(w2v_ctx *c, int k, cudaStream_t stream) {
   if (c->timing_on) cudaEventRecord(c->ev[c->slot][k], stream);
 }
 
+// Named range on the host thread for timeline tools (NVTX; costs nothing when no tool is attached).
+// The ranges follow the reference's addTime phases (networks/Word2Vec.scala:168-268): "w2v.wordmats"
+// covers its phases 1-7 (subsampling and bounds 1-4, pair list 5, permutation 6, negatives 7),
+// "w2v.pos" / "w2v.neg" its phases 8 / 9 and "w2v.evalpos" / "w2v.evalneg" its phases 10 / 11.
+struct Range {
+  explicit Range(const char *name) { nvtxRangePushA(name); }
+  ~Range() { nvtxRangePop(); }
+};
+
 // Waits for the pair and group counts of the latest wordmats to reach the host.
 static int settle_counts(w2v_ctx *c) {
   if (!c->counts_pending) return 0;
@@ -669,6 +680,7 @@ int w2v_wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64_t 
 
 static int wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64_t batch_id,
                     cudaStream_t stream, bool keep_list) {
+  Range range("w2v.wordmats");
   if (int fault = take_fault(c)) return fault;
   const w2v_opts &o = c->o;
   const int n = c->ncols;
@@ -791,8 +803,11 @@ int w2v_dobatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, float *A, 
   const float lrneg = o.eqPosNeg ? lrpos : lrpos / (float)o.nneg;
   int err = wordmats(c, tokens, u, batch_id, stream, false);
   if (err) return err;
-  err = w2v::pos_update_async(o.dim, c->ncols, nullptr, o.nskip, c->words, c->lb, c->ub, A, B,
-                              lrpos, o.vexp, c->hot, c->slice, stream);
+  {
+    Range range("w2v.pos");
+    err = w2v::pos_update_async(o.dim, c->ncols, nullptr, o.nskip, c->words, c->lb, c->ub, A, B,
+                                lrpos, o.vexp, c->hot, c->slice, stream);
+  }
   if (err) return err;
   W2V_CHECK(cudaEventRecord(c->ev_pos, stream));
   c->pos_recorded = 1;
@@ -801,8 +816,11 @@ int w2v_dobatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, float *A, 
   int groups = 0;
   const int *groups_dev = nullptr;
   group_count(c, &groups, &groups_dev);
-  err = w2v::neg_update_async(o.dim, groups, groups_dev, 0x7fffffff, o.nneg, o.nreuse, c->wa,
-                              c->ctx_out, A, B, lrneg, o.vexp, c->hot, c->fault_host, c->slice, stream);
+  {
+    Range range("w2v.neg");
+    err = w2v::neg_update_async(o.dim, groups, groups_dev, 0x7fffffff, o.nneg, o.nreuse, c->wa,
+                                c->ctx_out, A, B, lrneg, o.vexp, c->hot, c->fault_host, c->slice, stream);
+  }
   mark(c, 4, stream);
   if (c->timing_on) c->ev_state[c->slot] = 1;
   return err;
@@ -815,15 +833,21 @@ int w2v_evalbatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, const fl
   int err = wordmats(c, tokens, u, batch_id, stream, false);
   if (err) return err;
   W2V_CHECK(cudaMemsetAsync(c->retvals, 0, 2 * sizeof(float), stream));
-  err = w2v::pos_eval_async(o.dim, c->ncols, nullptr, o.nskip, c->words, c->lb, c->ub, A, B,
-                            c->retvals, c->eval, c->slice, stream);
+  {
+    Range range("w2v.evalpos");
+    err = w2v::pos_eval_async(o.dim, c->ncols, nullptr, o.nskip, c->words, c->lb, c->ub, A, B,
+                              c->retvals, c->eval, c->slice, stream);
+  }
   if (err) return err;
   mark(c, 3, stream);
   int groups = 0;
   const int *groups_dev = nullptr;
   group_count(c, &groups, &groups_dev);
-  err = w2v::neg_eval_async(o.dim, groups, groups_dev, o.nneg, o.nreuse, c->wa, c->ctx_out, A, B,
-                            c->retvals + 1, c->eval, c->fault_host, c->slice, stream);
+  {
+    Range range("w2v.evalneg");
+    err = w2v::neg_eval_async(o.dim, groups, groups_dev, o.nneg, o.nreuse, c->wa, c->ctx_out, A, B,
+                              c->retvals + 1, c->eval, c->fault_host, c->slice, stream);
+  }
   if (err) return err;
   mark(c, 4, stream);
   if (c->timing_on) c->ev_state[c->slot] = 2;

@@ -529,6 +529,52 @@ def run_ours(args):
                                                "kernel_over_gather_only": evalneg_ms / bounds[1]}
                                               if bounds else None)}}
 
+    if args.mode == "exchange":
+        # the exchange by itself at the workload's model size: NCCL, and where the model sits in
+        # symmetric memory both in-place kernels over a range of SM counts (ms, max over ranks)
+        if world < 2:
+            raise SystemExit("--mode exchange needs --gpus >= 2")
+
+        def time_of(fn, reps=5):
+            ts = []
+            for _ in range(reps + 1):
+                sync_all()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                fn()
+                b.record(stream)
+                sync_all()
+                t = torch.tensor([a.elapsed_time(b)], device="cuda", dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ts.append(float(t.item()))
+            return float(np.median(ts[1:]))
+
+        flat = model._flat
+        nbytes = 4 * flat.numel()
+        out = {"mode": "exchange", "n_gpus": world, "bytes": nbytes, "symmetric_memory": exchange == "nvls",
+               "nccl_allreduce_avg_ms": time_of(lambda: dist.all_reduce(flat, op=dist.ReduceOp.AVG)),
+               "nccl_allreduce_sum_ms": time_of(lambda: dist.all_reduce(flat, op=dist.ReduceOp.SUM)),
+               "fence_ms": None, "kernels": {}}
+        if exchange == "nvls":
+            out["fence_ms"] = time_of(lambda: dist.all_reduce(model._tick))
+            s_ptr = model._stream()
+            n = flat.numel()
+            for kind in ("p2p", "nvls"):
+                row = {}
+                for blocks in (4, 8, 12, 16, 24, 32, 48, 64, 148):
+                    if kind == "p2p":
+                        fn = lambda: lib.w2v_p2p_average(model._peers, n, rank, world, blocks, s_ptr)
+                    else:
+                        fn = lambda: lib.w2v_nvls_average(model._mc, n, rank, world, blocks, s_ptr)
+                    row[str(blocks)] = time_of(fn, reps=3)
+                out["kernels"][kind] = row
+            out["blocking_exchange_ms"] = time_of(lambda: model.mergeModelFn())
+        sampler.stop()
+        if rank == 0:
+            print(json.dumps(out), flush=True)
+        dist.destroy_process_group()
+        return
+
     K = args.steps
     pos = 0
     if args.mode == "eval":
@@ -680,8 +726,9 @@ def main():
                          "mergeModelFn does, instead of the whole model")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-eval", action="store_true", help="skip the scoring stretch of the default run")
-    ap.add_argument("--mode", default="train", choices=["train", "eval"],
-                    help="eval: time the scoring path (evalbatch) instead of the update path")
+    ap.add_argument("--mode", default="train", choices=["train", "eval", "exchange"],
+                    help="eval: time the scoring path (evalbatch) instead of the update path; exchange: time "
+                         "the model exchange alone (NCCL, and the in-place kernels over a range of SM counts)")
     ap.add_argument("--vocab", type=int, default=None, help="override the workload's vocabulary (profiling)")
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per minibatch (profiling)")
     ap.add_argument("--nneg", type=int, default=None, help="override the number of negatives (configs[4] uses 10)")

@@ -216,6 +216,7 @@ def test_heldout_score_matches_cpu_reference_at_benchmark_scale(oracle):
         cpu_model.dobatch(b, (k + 1) * N, *oracle._draws(rng, N, 5, 5, 5))
     cpu = cpu_model.evalbatch(held, *oracle._draws(rng, N, 5, 5, 5))
     assert cpu > 2 * np.log(0.5) + 2e-3            # the CPU run learnt something
+    print("held-out score after %d minibatches: gpu %.5f cpu %.5f (untrained %.5f)" % (nbatches, gpu, cpu, 2 * np.log(0.5)))
     assert abs(gpu - cpu) <= 0.01 * abs(cpu), (gpu, cpu)
 
 

@@ -38,6 +38,18 @@ def _run_pair(oracle, vocab, dim, ntrain, ntest, batch, corpus, seed=11, lrate=1
     return gpu_ll, cpu_ll, learner.reslist, cpu_eval
 
 
+def _same_gain(gpu_ll, cpu_ll, within=0.10):
+    """The 1 % bar on the score alone would let a path pass that learnt a sixth less: what training
+    adds to the untrained score 2*log(1/2) is only a few times that tolerance.  So the gains are
+    compared too: the GPU path's within 10 % of the CPU path's (the two runs draw different random
+    numbers; on these corpora they differ by about 1 % of the gain)."""
+    untrained = 2 * np.log(0.5)
+    print("held-out score: gpu %.5f cpu %.5f, gain gpu %.5f cpu %.5f" % (gpu_ll, cpu_ll, gpu_ll - untrained,
+                                                                        cpu_ll - untrained))
+    assert cpu_ll - untrained >= 5 * 0.01 * abs(cpu_ll)
+    assert abs((gpu_ll - untrained) - (cpu_ll - untrained)) <= within * (cpu_ll - untrained), (gpu_ll, cpu_ll)
+
+
 def test_config1_zipf_heldout_ll_within_one_percent(oracle):
     """BASELINE configs[0] at a fifth of its length: vocab 10k, dim 100, Zipf(1.0)
     tokens, window 5, 5 negatives, 100k-token minibatches, one pass."""
@@ -51,6 +63,7 @@ def test_config1_zipf_heldout_ll_within_one_percent(oracle):
     assert abs(gpu_ll - cpu_ll) <= 0.01 * abs(cpu_ll), (gpu_ll, cpu_ll)
     # the untrained model scores 2*log(1/2) per pair; training must have moved away from it
     assert gpu_ll > 2 * np.log(0.5) + 0.03
+    _same_gain(gpu_ll, cpu_ll)
 
 
 def test_topic_corpus_heldout_ll_within_one_percent(oracle):
@@ -64,3 +77,4 @@ def test_topic_corpus_heldout_ll_within_one_percent(oracle):
         lambda n, s: tc.tokens(s * 100_000, n // 1000), lrate=0.002)
     assert abs(gpu_ll - cpu_ll) <= 0.01 * abs(cpu_ll), (gpu_ll, cpu_ll)
     assert gpu_ll > 2 * np.log(0.5) + 0.1
+    _same_gain(gpu_ll, cpu_ll)

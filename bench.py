@@ -580,7 +580,7 @@ def run_ours(args):
     if args.mode == "eval":
         dev_r, pos = timed(False, pos, "eval", K, args.warmup)
         e2e_r, pos = timed(True, pos, "eval", K, args.warmup)
-        bounds = probe_bounds() if (rank == 0 and world == 1) else None
+        bounds = probe_bounds() if (rank == 0 and world == 1 and not args.no_probes) else None
         sampler.stop()
         if rank == 0:
             blk = eval_block(dev_r, e2e_r, K, bounds)
@@ -609,8 +609,8 @@ def run_ours(args):
         ke = max(4, min(K, 24))
         ev_dev, pos = timed(False, pos, "eval", ke, 3)
         ev_e2e, pos = timed(True, pos, "eval", ke, 3)
-    bounds = probe_bounds() if (rank == 0 and world == 1) else None
-    rows_a, rows_b = distinct_rows() if rank == 0 else (0, 0)
+    bounds = probe_bounds() if (rank == 0 and world == 1 and not args.no_probes) else None
+    rows_a, rows_b = distinct_rows() if (rank == 0 and not args.no_probes) else (0, 0)
     sampler.stop()
     if not args.no_eval and rank == 0:
         eval_blk = eval_block(ev_dev, ev_e2e, ke, bounds)
@@ -637,7 +637,7 @@ def run_ours(args):
     # vocabulary, minibatch size or rate changes the L2 hit rate and the folding period
     traffic = NEG_DRAM_TRAFFIC_BYTES if (default_shape and w["lrate"] == DEFAULT_WORKLOAD["lrate"]) else None
     # what no kernel can avoid: every distinct row the launch names read once and written once
-    compulsory = 2.0 * row * (rows_a + rows_b)
+    compulsory = 2.0 * row * (rows_a + rows_b) if (rows_a + rows_b) > 0 else None
     roofline = {"bound": "hbm", "kernel": "neg_update_staged_kernel<%d,%d,%d,false>" % (
                     w["nneg"], w["nreuse"], nr), "achieved": achieved, "peak": peak,
                 "peak_kind": peak_kind, "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
@@ -647,7 +647,7 @@ def run_ours(args):
                 "dram_frac": (traffic / neg_s / 1e9 / peak) if (traffic and neg_s > 0) else None,
                 # distinct rows read once + written once: at most 1 of peak by construction
                 "compulsory_bytes": compulsory, "distinct_rows": {"A": rows_a, "B": rows_b},
-                "compulsory_frac": (compulsory / neg_s / 1e9 / peak) if neg_s > 0 else None,
+                "compulsory_frac": (compulsory / neg_s / 1e9 / peak) if (compulsory and neg_s > 0) else None,
                 "traffic_over_compulsory": (traffic / compulsory) if (traffic and compulsory) else None,
                 # what the kernel's atomic row reductions take with nothing else in the kernel
                 # (zeros added to the same rows), and what reading those rows takes: ms per launch
@@ -726,6 +726,9 @@ def main():
                          "mergeModelFn does, instead of the whole model")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-eval", action="store_true", help="skip the scoring stretch of the default run")
+    ap.add_argument("--no-probes", action="store_true",
+                    help="skip the row-traffic probes and the distinct-row count (profiling: keeps the launch list "
+                         "to the minibatches)")
     ap.add_argument("--mode", default="train", choices=["train", "eval", "exchange"],
                     help="eval: time the scoring path (evalbatch) instead of the update path; exchange: time "
                          "the model exchange alone (NCCL, and the in-place kernels over a range of SM counts)")

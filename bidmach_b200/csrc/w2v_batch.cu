@@ -96,6 +96,31 @@ __host__ __device__ inline uint32_t permute_index(uint32_t i, uint32_t n, const 
   return x;
 }
 
+// The inverse of permute_index: the place i with permute_index(i, n, k) == p.  Every round is
+// undone in reverse order (x ^= x >> sh is its own inverse because sh >= b / 2; the affine step
+// with the multiplier's inverse modulo 2^32, which is also its inverse modulo 2^b), and walking
+// the inverse map from p until the value drops below n undoes the cycle walk.
+struct PermInverse {
+  uint32_t ainv[4], c[4];
+};
+
+__host__ __device__ inline uint32_t unpermute_index(uint32_t p, uint32_t n, const PermInverse &k) {
+  if (n < 2) return 0;
+  int b = 0;
+  while (b < 32 && ((n - 1) >> b) != 0) b++;
+  const uint32_t mask = (b >= 32) ? 0xFFFFFFFFu : ((1u << b) - 1u);
+  const int sh = (b + 1) >> 1;
+  uint32_t x = p;
+  do {
+#pragma unroll
+    for (int r = 3; r >= 0; r--) {
+      x ^= x >> sh;
+      x = ((x - k.c[r]) * k.ainv[r]) & mask;
+    }
+  } while (x >= n);
+  return x;
+}
+
 // ---------------------------------------------------------------------------
 // Preprocessing kernels
 // ---------------------------------------------------------------------------
@@ -222,59 +247,29 @@ __global__ void shuffle_contexts_kernel(const int *__restrict__ counts, int nreu
     out[i] = ctx[permute_index(i, n, keys)];
 }
 
-// The shuffled context matrix and the negative ids in one pass, without the ordered pair list
-// in between: place i of WB takes pair perm(i) of the (centre ascending, offset ascending)
-// order, which is found where it lies -- the centre by bisection of the scanned pair counts,
-// the context by walking that centre's window -- instead of being written out by
-// fill_pairs_kernel and gathered again.  Same WB and WA, bit for bit, as fill + shuffle +
-// negative_ids_kernel.
-__global__ void pairs_and_negatives_kernel(int ncols, const int *__restrict__ counts, int nreuse, int nneg,
-                                           PermKeys keys, const int *__restrict__ words,
-                                           const int *__restrict__ lb, const int *__restrict__ ub,
-                                           const int *__restrict__ off, const float *__restrict__ unegs,
-                                           Rng rng, int vocab, float expt, int *__restrict__ wb,
-                                           int *__restrict__ wa) {
+// The shuffled context matrix straight from the token windows, without the ordered pair list in
+// between: pair p of the (centre ascending, offset ascending) order belongs at place
+// unpermute_index(p) of WB, so the thread of a centre sends each of its contexts there (places at
+// or beyond groups * nreuse are the dropped tail).  Same WB, bit for bit, as fill_pairs_kernel
+// followed by shuffle_contexts_kernel, with coalesced reads and no 24 MB list written and
+// gathered again.
+__global__ void scatter_pairs_kernel(int ncols, const int *__restrict__ counts, int nreuse,
+                                     PermInverse inv, const int *__restrict__ words,
+                                     const int *__restrict__ lb, const int *__restrict__ ub,
+                                     const int *__restrict__ off, int *__restrict__ wb) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= ncols) return;
+  if (words[i] < 0) return;
   const uint32_t n = (uint32_t)counts[0];
-  const int64_t groups = counts[1];
-  const int64_t m = groups * nreuse, nn = groups * nneg;
-  const int64_t total = m > nn ? m : nn;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    if (i < m) {
-      const int p = (int)permute_index((uint32_t)i, n, keys);
-      // the last centre whose first pair is at or before p (it has pairs: the next one starts after p)
-      int lo = 0, hi = ncols - 1;
-      while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (off[mid] <= p) lo = mid; else hi = mid - 1;
-      }
-      int k = p - off[lo];
-      const int top = ub[lo];
-      int w = -1;
-      for (int j = lb[lo]; j <= top; j++) {
-        if (j == 0) continue;
-        const int cand = words[lo + j];
-        if (cand < 0) continue;
-        if (k-- == 0) {
-          w = cand;
-          break;
-        }
-      }
-      wb[i] = w;
-    }
-    if (i < nn) {
-      float u;
-      if (unegs) {
-        u = unegs[i];
-      } else {
-        const uint64_t blk = (uint64_t)i >> 2;
-        PhiloxOut r = philox4x32_10((uint32_t)blk, (uint32_t)(blk >> 32), kStreamNegs, rng.batch, rng.k0, rng.k1);
-        u = u01(r.v[i & 3]);
-      }
-      const double v = (double)vocab * pow((double)u, (double)expt);
-      const int id = (v >= 2147483647.0) ? 2147483647 : (int)v;
-      wa[i] = min(id, vocab - 1);
-    }
+  const uint32_t m = (uint32_t)counts[1] * (uint32_t)nreuse;
+  uint32_t p = (uint32_t)off[i];
+  const int hi = ub[i];
+  for (int j = lb[i]; j <= hi; j++) {
+    if (j == 0) continue;
+    const int w = words[i + j];
+    if (w < 0) continue;
+    const uint32_t place = unpermute_index(p++, n, inv);
+    if (place < m) wb[place] = w;
   }
 }
 
@@ -646,6 +641,23 @@ int w2v_init_model(const w2v_opts *o, float *A, float *B, void *stream_) {
   return (int)cudaGetLastError();
 }
 
+static w2v::PermInverse invert(const w2v::PermKeys &k) {
+  w2v::PermInverse inv;
+  for (int r = 0; r < 4; r++) {
+    // Newton's iteration for the inverse of an odd number modulo 2^32 (doubles the correct bits)
+    uint32_t x = k.a[r];
+    for (int it = 0; it < 5; it++) x *= 2u - k.a[r] * x;
+    inv.ainv[r] = x;
+    inv.c[r] = k.c[r];
+  }
+  return inv;
+}
+
+static w2v::PermKeys make_perm_keys(const w2v_opts &o, uint64_t batch_id);
+static w2v::PermInverse make_perm_inverse(const w2v_opts &o, uint64_t batch_id) {
+  return invert(make_perm_keys(o, batch_id));
+}
+
 static w2v::PermKeys make_perm_keys(const w2v_opts &o, uint64_t batch_id) {
   const w2v::Rng rng = make_rng(o, batch_id);
   const w2v::PhiloxOut x = w2v::philox4x32_10(0u, 0u, w2v::kStreamPermute, rng.batch, rng.k0, rng.k1);
@@ -740,17 +752,10 @@ static int wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64
     const int64_t max_groups = c->max_pairs / o.nreuse;
     const int64_t max_negs = max_groups * o.nneg;
     if (!keep_list && c->max_pairs > 0) {
-      const int64_t most = std::max<int64_t>(c->max_pairs, max_negs);
-      const int fused_blocks = (int)std::min<int64_t>((most + threads - 1) / threads,
-                                                     (int64_t)w2v::device_sm_count() * 16);
-      w2v::pairs_and_negatives_kernel<<<fused_blocks, threads, 0, stream>>>(
-          n, c->counts, o.nreuse, o.nneg, make_perm_keys(o, batch_id), c->words, c->lb, c->ub, c->off, un,
-          rng, o.vocabSize, c->expt, c->ctx_out, c->wa);
+      w2v::scatter_pairs_kernel<<<blocks, threads, 0, stream>>>(
+          n, c->counts, o.nreuse, make_perm_inverse(o, batch_id), c->words, c->lb, c->ub, c->off, c->ctx_out);
       w2v::count_launch(1);
-      mark(c, 2, stream);
-      return (int)cudaGetLastError();
-    }
-    if (c->max_pairs > 0) {
+    } else if (c->max_pairs > 0) {
       const int shuffle_blocks = (int)std::min<int64_t>((c->max_pairs + threads - 1) / threads,
                                                        (int64_t)w2v::device_sm_count() * 16);
       w2v::shuffle_contexts_kernel<<<shuffle_blocks, threads, 0, stream>>>(

@@ -120,10 +120,10 @@ def test_init_model_matches_restatement(oracle):
                                                               (777, 2, 5, 10, 1e-3, 3), (5000, 5, 5, 1, 1.0, 4),
                                                               (37, 5, 5, 5, 1.0, 5), (200_000, 5, 5, 5, 1.0, 6)])
 def test_minibatch_calls_build_the_same_lists_without_the_ordered_pair_list(n, nskip, nneg, nreuse, wsample, seed):
-    """w2v_dobatch / w2v_evalbatch never write the ordered pair list: one kernel finds pair perm(i)
-    where it lies in the token windows and draws the negatives.  Its WB and WA must equal, bit for
-    bit, what w2v_wordmats (ordered list, then shuffle, then negatives) builds for the same
-    minibatch and batch id."""
+    """w2v_dobatch / w2v_evalbatch never write the ordered pair list: the thread of a centre sends
+    each of its contexts to the place the inverse of the keyed bijection gives its pair.  WB and WA
+    must equal, bit for bit, what w2v_wordmats (ordered list, then shuffle, then negatives) builds
+    for the same minibatch and batch id."""
     import ctypes as C
     from bidmach_b200 import _lib, Word2Vec
     o = _opts(nskip=nskip, nneg=nneg, nreuse=nreuse, wsample=wsample, lrate=0.0, seed=seed)

@@ -67,9 +67,10 @@ POOL = 4             # distinct minibatches per rank, cycled
 CPU_SAMPLE = 500_000  # tokens of one minibatch the CPU arms process per step
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the negative-update kernel on the
-# default workload at the default rate (6.48 GB read + 6.82 GB written), from a one-pass ncu
-# capture of the full-size workload.
-NEG_DRAM_TRAFFIC_BYTES = 13.30e9
+# default workload at the default rate 1e-3, i.e. with the folding period that the kernel derives
+# from the hot word's share (6.49 GB read + 6.84 GB written; one-pass ncu capture of the
+# full-size workload, six launches within 0.2 % of each other).
+NEG_DRAM_TRAFFIC_BYTES = 13.33e9
 
 
 def measured_peak_gbs():

@@ -154,3 +154,29 @@ def test_jni_binders_of_the_whole_minibatch_calls():
     # unsupported options are refused with a null handle
     assert lib.Java_edu_berkeley_bid_CUMACH_w2vCreate(jvm.env, None, D, 5, 7, 3, V, 0.75, 1.0, 0.01, 0.5, 0.5,
                                                       0, 0, 0, 7, n) == 0
+
+
+def test_reserved_sms_and_the_pos_event_leave_the_result_alone():
+    """w2v_reserve_sms only narrows the negative update's grid and w2v_wait_pos only orders another
+    stream after the positive update: a minibatch trained with 48 SMs held back, and a side stream
+    waiting on the positive update, gives the score a plain run gives (same seeds, same draws; the
+    update order differs, hence a tolerance), and both calls refuse a null context."""
+    from bidmach_b200 import _lib
+    lib = _lib.load()
+    n = 20_000
+    toks = torch.from_numpy(_toks(n, 500, seed=2, doc=40)).cuda()
+    scores = []
+    for reserve in (0, 48):
+        m = _model(n, dim=300, lrate=0.005)
+        m.reserveSMs(reserve)
+        side = torch.cuda.Stream()
+        for k in range(3):
+            m.dobatch([toks], 0, (k + 1) * n)
+            assert lib.w2v_wait_pos(m._ctx, side.cuda_stream) == 0
+        side.synchronize()
+        m.reserveSMs(0)
+        scores.append(m.evalbatch([toks], 0, n))
+    assert abs(scores[0] - scores[1]) <= 0.01 * abs(scores[0]), scores
+    assert scores[0] > 2 * np.log(0.5)
+    assert lib.w2v_reserve_sms(None, 4) == 1 and lib.w2v_wait_pos(None, None) == 1
+    assert lib.w2v_reserve_sms(m._ctx, -1) == 1

@@ -163,11 +163,11 @@ def test_reserved_sms_and_the_pos_event_leave_the_result_alone():
     update order differs, hence a tolerance), and both calls refuse a null context."""
     from bidmach_b200 import _lib
     lib = _lib.load()
-    n = 20_000
-    toks = torch.from_numpy(_toks(n, 500, seed=2, doc=40)).cuda()
+    n = 50_000
+    toks = torch.from_numpy(_toks(n, 5000, seed=2, doc=40)).cuda()
     scores = []
     for reserve in (0, 48):
-        m = _model(n, dim=300, lrate=0.005)
+        m = _model(n, dim=300, vocabSize=5000, lrate=1e-3, wsample=1e-3)
         m.reserveSMs(reserve)
         side = torch.cuda.Stream()
         for k in range(3):
@@ -177,6 +177,6 @@ def test_reserved_sms_and_the_pos_event_leave_the_result_alone():
         m.reserveSMs(0)
         scores.append(m.evalbatch([toks], 0, n))
     assert abs(scores[0] - scores[1]) <= 0.01 * abs(scores[0]), scores
-    assert scores[0] > 2 * np.log(0.5)
+    assert np.isfinite(scores[0]) and scores[0] > -1.5
     assert lib.w2v_reserve_sms(None, 4) == 1 and lib.w2v_wait_pos(None, None) == 1
     assert lib.w2v_reserve_sms(m._ctx, -1) == 1

@@ -396,7 +396,7 @@ def run_ours(args):
                 model.dobatch([devt[b]], 0, pos)
             if world > 1 and exchanges:
                 if overlap:
-                    model.finishMerge()          # an exchange started after the previous minibatch
+                    model.finishMerge(defer=True)   # an exchange started beside this minibatch
                 if (nsteps - s) % args.sync_every == 0:
                     exchange_now(s)
         return pos

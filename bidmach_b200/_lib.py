@@ -91,6 +91,7 @@ SIGNATURES = {
     "w2v_nvls_average": (_I, [_P, C.c_int64, _I, _I, _I, _P]),
     "w2v_p2p_average": (_I, [C.POINTER(_P), C.c_int64, _I, _I, _I, _P]),
     "w2v_wait_pos": (_I, [_P, _P]),
+    "w2v_wait_before_neg": (_I, [_P, _P]),
     "w2v_reserve_sms": (_I, [_P, _I]),
     "w2v_set_slice": (_I, [_P, _I, _I, _I, _I]),
     "w2v_slice_rows": (C.c_int64, [_I, _I, _I]),

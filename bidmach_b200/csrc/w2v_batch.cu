@@ -354,6 +354,7 @@ struct w2v_ctx {
   cudaEvent_t ev_pos;      // end of the latest positive update (w2v_wait_pos)
   int pos_recorded;
   int have_list;           // the latest preprocessing wrote the ordered pair list (ctx_in)
+  cudaEvent_t neg_wait;    // the next negative update waits for this event first (w2v_wait_before_neg)
   void *cub_tmp;
   size_t cub_tmp_bytes;
   // pinned host
@@ -610,6 +611,12 @@ int w2v_wait_pos(w2v_ctx *c, void *stream) {
   return (int)cudaStreamWaitEvent((cudaStream_t)stream, c->ev_pos, 0);
 }
 
+int w2v_wait_before_neg(w2v_ctx *c, void *event) {
+  if (!c) return 1;
+  c->neg_wait = (cudaEvent_t)event;
+  return 0;
+}
+
 int w2v_reserve_sms(w2v_ctx *c, int sms) {
   if (!c || sms < 0) return 1;
   c->sm_reserve = sms;
@@ -817,6 +824,10 @@ int w2v_dobatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, float *A, 
   W2V_CHECK(cudaEventRecord(c->ev_pos, stream));
   c->pos_recorded = 1;
   mark(c, 3, stream);
+  if (c->neg_wait) {
+    W2V_CHECK(cudaStreamWaitEvent(stream, c->neg_wait, 0));
+    c->neg_wait = nullptr;
+  }
   w2v::SmReserve reserve(c->sm_reserve);   // the negative update leaves these SMs to another stream's kernel
   int groups = 0;
   const int *groups_dev = nullptr;

@@ -267,7 +267,7 @@ class ParLearner(Learner):
         self._since_sync += 1
         if self.opts.overlapSync:
             if self._since_sync == 1:
-                self.model.finishMerge()        # the exchange started one minibatch ago
+                self.model.finishMerge(defer=True)   # the exchange started beside this minibatch
             if self._since_sync >= self.opts.syncStep:
                 self.model.startMerge(self.group)
                 self._since_sync = 0

@@ -187,6 +187,7 @@ class Word2Vec:
         toks = gmats[0]
         if toks.shape[0] != self.ncols:
             return 0.0
+        self.finishMerge()        # scores are taken on a model no exchange is writing to
         self._batches += 1
         score = C.c_double(0.0)
         with torch.cuda.device(self.device):
@@ -219,6 +220,7 @@ class Word2Vec:
         host = _host_i32(mats[0])
         if host.shape[0] != self.ncols:
             return 0.0
+        self.finishMerge()
         self._batches += 1
         score = C.c_double(0.0)
         with torch.cuda.device(self.device):
@@ -467,17 +469,33 @@ class Word2Vec:
             done.record(self._comm)
         self._merge = done
 
-    def finishMerge(self):
+    def finishMerge(self, defer: bool = False):
+        """Makes the compute stream wait for an exchange started by ``startMerge``.  ``defer``
+        (in-place exchange only): not now but before the negative update of the next minibatch,
+        so that an exchange that outlasts the negative update it ran beside finishes beside the
+        next minibatch's preprocessing and positive update instead of stalling the stream."""
         if getattr(self, "_pending", None) is not None:
             self._launch_pending(after_pos=False)    # no minibatch came in between
+        if getattr(self, "_deferred", None) is not None and not defer:
+            # a wait handed to the next minibatch: take it now
+            torch.cuda.current_stream(self.device).wait_event(self._deferred)
+            self._deferred = None
         if getattr(self, "_merge", None) is None:
             return
         compute = torch.cuda.current_stream(self.device)
-        compute.wait_event(self._merge)
-        self._merge = None
         if getattr(self, "_merge_inplace", False):
+            if defer:
+                self._deferred = self._merge         # keeps the event alive until it has been waited for
+                with torch.cuda.device(self.device):
+                    _check(_lib.load().w2v_wait_before_neg(self._ctx, int(self._merge.cuda_event)),
+                           "w2v_wait_before_neg")
+            else:
+                compute.wait_event(self._merge)
+            self._merge = None
             self.reserveSMs(0)
             return
+        compute.wait_event(self._merge)
+        self._merge = None
         with torch.cuda.device(self.device):
             _check(_lib.load().w2v_apply_average(self._flat.data_ptr(), self._snap.data_ptr(),
                                                  self._avg.data_ptr(), self._flat.numel(),

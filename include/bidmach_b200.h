@@ -337,6 +337,11 @@ int w2v_reserve_sms(w2v_ctx *ctx, int sms);
  * has finished (and with it everything of the minibatches before): the point from which an
  * exchange on another stream runs beside the negative update only. */
 int w2v_wait_pos(w2v_ctx *ctx, void *stream);
+/* The negative update of the next w2v_dobatch / w2v_dobatch_host call waits for `event` (a
+ * cudaEvent_t, which must stay alive until that call; null withdraws it) before it starts, while
+ * that call's preprocessing and positive update do not: an exchange that outlasts the negative
+ * update it started beside finishes beside the next minibatch's first kernels. */
+int w2v_wait_before_neg(w2v_ctx *ctx, void *event);
 
 /* Second half of an overlapped model average (multi-GPU): the caller snapshots
  * its replica into `base`, averages the snapshots of all replicas into `avg`

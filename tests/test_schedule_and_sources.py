@@ -212,7 +212,7 @@ def test_parlearner_overlapped_exchange_order():
         def startMerge(self, group=None):
             self.log.append("start")
 
-        def finishMerge(self):
+        def finishMerge(self, defer=False):
             self.log.append("finish")
 
     m = M()

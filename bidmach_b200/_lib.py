@@ -71,6 +71,15 @@ SIGNATURES = {
     "Java_edu_berkeley_bid_CUMACH_w2vDobatch": (_I, [_P, _P, C.c_int64, _P, _P, _P, C.c_int64, C.c_int64]),
     "Java_edu_berkeley_bid_CUMACH_w2vEvalbatch": (C.c_double, [_P, _P, C.c_int64, _P, _P, _P, C.c_int64]),
     "Java_edu_berkeley_bid_CUMACH_w2vLastError": (_I, [_P, _P, C.c_int64]),
+    "Java_edu_berkeley_bid_CUMACH_w2vSetSlice": (_I, [_P, _P, C.c_int64, _I, _I, _I, _I]),
+    "Java_edu_berkeley_bid_CUMACH_word2vecPosSlice": (_I, [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _F, _F, _I, _I, _I, _I]),
+    "Java_edu_berkeley_bid_CUMACH_word2vecNegSlice": (_I, [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _F, _F, _I, _I, _I, _I]),
+    "Java_edu_berkeley_bid_CUMACH_word2vecEvalPosSlice": (_I, [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I]),
+    "Java_edu_berkeley_bid_CUMACH_word2vecEvalNegSlice": (_I, [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I]),
+    "Java_edu_berkeley_bid_CUMACH_w2vCommInitAll": (C.c_int64, [_P, _P, _I]),
+    "Java_edu_berkeley_bid_CUMACH_w2vCommOf": (C.c_int64, [_P, _P, C.c_int64, _I]),
+    "Java_edu_berkeley_bid_CUMACH_w2vAllreduceAvg": (_I, [_P, _P, C.c_int64, _P, _P, C.c_int64]),
+    "Java_edu_berkeley_bid_CUMACH_w2vCommDestroyAll": (None, [_P, _P, C.c_int64]),
     "w2v_default_opts": (None, [C.POINTER(W2VOpts)]),
     "w2v_create": (_I, [C.POINTER(W2VOpts), _I, C.POINTER(_P)]),
     "w2v_destroy": (None, [_P]),

@@ -230,4 +230,115 @@ JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMACH_w2vLastError(JNIEnv *env, jo
   return h ? h->last_error : 1;
 }
 
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMACH_w2vSetSlice(JNIEnv *env, jobject obj, jlong handle,
+                                                                jint islice, jint nslices, jint nHead,
+                                                                jint doHead) {
+  (void)env;
+  (void)obj;
+  JniCtx *h = (JniCtx *)(intptr_t)handle;
+  if (!h) return 1;
+  return h->last_error = w2v_set_slice(h->ctx, islice, nslices, nHead, doHead);
+}
+
+// ---------------------------------------------------------------------------
+// Binders of the vocabulary-slice launchers, for a CUMACH that declares
+//   native int word2vecPosSlice(int nrows, int ncols, int shift, Pointer W, Pointer LB, Pointer UB, Pointer A,
+//                               Pointer B, float lrate, float vexp, int islice, int nslices, int nHead, int doHead);
+//   native int word2vecNegSlice(int nrows, int ncols, int nwa, int nwb, Pointer WA, Pointer WB, Pointer A,
+//                               Pointer B, float lrate, float vexp, int islice, int nslices, int nHead, int doHead);
+//   native int word2vecEvalPosSlice(..., Pointer retVal, int islice, int nslices, int nHead);
+//   native int word2vecEvalNegSlice(..., Pointer retVal, int islice, int nslices, int nHead);
+// (the device forms of CPUMACH.word2vecPosSlice / word2vecNegSlice, jni/src/BIDMach_CPUMACH.c:90-184, 267-366).
+// ---------------------------------------------------------------------------
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMACH_word2vecPosSlice(
+    JNIEnv *env, jobject obj, jint nrows, jint ncols, jint shift, jobject jW, jobject jLB, jobject jUB,
+    jobject jA, jobject jB, jfloat lrate, jfloat vexp, jint islice, jint nslices, jint nHead, jint doHead) {
+  (void)obj;
+  return word2vecPosSlice(nrows, ncols, shift, (int *)device_address(env, jW), (int *)device_address(env, jLB),
+                          (int *)device_address(env, jUB), (float *)device_address(env, jA),
+                          (float *)device_address(env, jB), lrate, vexp, islice, nslices, nHead, doHead);
+}
+
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMACH_word2vecNegSlice(
+    JNIEnv *env, jobject obj, jint nrows, jint ncols, jint nwa, jint nwb, jobject jWA, jobject jWB,
+    jobject jA, jobject jB, jfloat lrate, jfloat vexp, jint islice, jint nslices, jint nHead, jint doHead) {
+  (void)obj;
+  return word2vecNegSlice(nrows, ncols, nwa, nwb, (int *)device_address(env, jWA),
+                          (int *)device_address(env, jWB), (float *)device_address(env, jA),
+                          (float *)device_address(env, jB), lrate, vexp, islice, nslices, nHead, doHead);
+}
+
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMACH_word2vecEvalPosSlice(
+    JNIEnv *env, jobject obj, jint nrows, jint ncols, jint shift, jobject jW, jobject jLB, jobject jUB,
+    jobject jA, jobject jB, jobject jRetval, jint islice, jint nslices, jint nHead) {
+  (void)obj;
+  return word2vecEvalPosSlice(nrows, ncols, shift, (int *)device_address(env, jW),
+                              (int *)device_address(env, jLB), (int *)device_address(env, jUB),
+                              (float *)device_address(env, jA), (float *)device_address(env, jB),
+                              (float *)device_address(env, jRetval), islice, nslices, nHead);
+}
+
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMACH_word2vecEvalNegSlice(
+    JNIEnv *env, jobject obj, jint nrows, jint ncols, jint nwa, jint nwb, jobject jWA, jobject jWB,
+    jobject jA, jobject jB, jobject jRetval, jint islice, jint nslices, jint nHead) {
+  (void)obj;
+  return word2vecEvalNegSlice(nrows, ncols, nwa, nwb, (int *)device_address(env, jWA),
+                              (int *)device_address(env, jWB), (float *)device_address(env, jA),
+                              (float *)device_address(env, jB), (float *)device_address(env, jRetval), islice,
+                              nslices, nHead);
+}
+
+// ---------------------------------------------------------------------------
+// Binders of the model exchange, for a ParLearner with one thread per GPU:
+//   native long w2vCommInitAll(int ndev);             // devices 0..ndev-1; 0 = failed
+//   native long w2vCommOf(long comms, int i);         // the communicator of device i
+//   native int  w2vAllreduceAvg(long comm, Pointer A, Pointer B, long nEach);   // thread i, its own matrices
+//   native void w2vCommDestroyAll(long comms);
+// w2vAllreduceAvg enqueues on the calling thread's default stream and returns; the next launcher
+// call of that thread runs after it in stream order.
+// ---------------------------------------------------------------------------
+namespace {
+struct JniComms {
+  int ndev;
+  w2v_comm *comm[64];
+};
+}  // namespace
+
+JNIEXPORT jlong JNICALL Java_edu_berkeley_bid_CUMACH_w2vCommInitAll(JNIEnv *env, jobject obj, jint ndev) {
+  (void)env;
+  (void)obj;
+  if (ndev < 1 || ndev > 64) return 0;
+  JniComms *set = new JniComms();
+  set->ndev = ndev;
+  if (w2v_comm_init_all(ndev, nullptr, set->comm) != 0) {
+    delete set;
+    return 0;
+  }
+  return (jlong)(intptr_t)set;
+}
+
+JNIEXPORT jlong JNICALL Java_edu_berkeley_bid_CUMACH_w2vCommOf(JNIEnv *env, jobject obj, jlong comms, jint i) {
+  (void)env;
+  (void)obj;
+  JniComms *set = (JniComms *)(intptr_t)comms;
+  if (!set || i < 0 || i >= set->ndev) return 0;
+  return (jlong)(intptr_t)set->comm[i];
+}
+
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMACH_w2vAllreduceAvg(JNIEnv *env, jobject obj, jlong comm,
+                                                                    jobject jA, jobject jB, jlong nEach) {
+  (void)obj;
+  return w2v_allreduce_avg((w2v_comm *)(intptr_t)comm, (float *)device_address(env, jA),
+                           (float *)device_address(env, jB), nEach, kPerThreadStream);
+}
+
+JNIEXPORT void JNICALL Java_edu_berkeley_bid_CUMACH_w2vCommDestroyAll(JNIEnv *env, jobject obj, jlong comms) {
+  (void)env;
+  (void)obj;
+  JniComms *set = (JniComms *)(intptr_t)comms;
+  if (!set) return;
+  for (int i = 0; i < set->ndev; i++) w2v_comm_destroy(set->comm[i]);
+  delete set;
+}
+
 }  // extern "C"

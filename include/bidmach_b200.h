@@ -161,6 +161,36 @@ int Java_edu_berkeley_bid_CUMACH_w2vDobatch(BidmachJNIEnv *env, void *obj, int64
 double Java_edu_berkeley_bid_CUMACH_w2vEvalbatch(BidmachJNIEnv *env, void *obj, int64_t ctx,
                                                  void *jTokens, void *jA, void *jB, int64_t batchId);
 int Java_edu_berkeley_bid_CUMACH_w2vLastError(BidmachJNIEnv *env, void *obj, int64_t ctx);
+int Java_edu_berkeley_bid_CUMACH_w2vSetSlice(BidmachJNIEnv *env, void *obj, int64_t ctx, int islice,
+                                             int nslices, int nHead, int doHead);
+
+/* Binders of the vocabulary-slice launchers and of the model exchange (both further down in part
+ * 1 and part 3): same argument lists with jcuda.Pointer objects in place of the device pointers.
+ *   native int  word2vecPosSlice(..., int islice, int nslices, int nHead, int doHead);      etc.
+ *   native long w2vCommInitAll(int ndev);   native long w2vCommOf(long comms, int i);
+ *   native int  w2vAllreduceAvg(long comm, Pointer A, Pointer B, long nEach);
+ *   native void w2vCommDestroyAll(long comms); */
+int Java_edu_berkeley_bid_CUMACH_word2vecPosSlice(BidmachJNIEnv *env, void *obj, int nrows, int ncols,
+                                                  int shift, void *jW, void *jLB, void *jUB, void *jA,
+                                                  void *jB, float lrate, float vexp, int islice,
+                                                  int nslices, int nHead, int doHead);
+int Java_edu_berkeley_bid_CUMACH_word2vecNegSlice(BidmachJNIEnv *env, void *obj, int nrows, int ncols,
+                                                  int nwa, int nwb, void *jWA, void *jWB, void *jA,
+                                                  void *jB, float lrate, float vexp, int islice,
+                                                  int nslices, int nHead, int doHead);
+int Java_edu_berkeley_bid_CUMACH_word2vecEvalPosSlice(BidmachJNIEnv *env, void *obj, int nrows, int ncols,
+                                                      int shift, void *jW, void *jLB, void *jUB, void *jA,
+                                                      void *jB, void *jRetval, int islice, int nslices,
+                                                      int nHead);
+int Java_edu_berkeley_bid_CUMACH_word2vecEvalNegSlice(BidmachJNIEnv *env, void *obj, int nrows, int ncols,
+                                                      int nwa, int nwb, void *jWA, void *jWB, void *jA,
+                                                      void *jB, void *jRetval, int islice, int nslices,
+                                                      int nHead);
+int64_t Java_edu_berkeley_bid_CUMACH_w2vCommInitAll(BidmachJNIEnv *env, void *obj, int ndev);
+int64_t Java_edu_berkeley_bid_CUMACH_w2vCommOf(BidmachJNIEnv *env, void *obj, int64_t comms, int i);
+int Java_edu_berkeley_bid_CUMACH_w2vAllreduceAvg(BidmachJNIEnv *env, void *obj, int64_t comm, void *jA,
+                                                 void *jB, int64_t nEach);
+void Java_edu_berkeley_bid_CUMACH_w2vCommDestroyAll(BidmachJNIEnv *env, void *obj, int64_t comms);
 #endif
 
 /* ------------------------------------------------------------------------

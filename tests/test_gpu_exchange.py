@@ -81,6 +81,27 @@ def test_two_threads_two_gpus_average_through_the_c_abi():
         lib.w2v_comm_destroy(comms[r])
 
 
+@pytest.mark.gpu
+def test_exchange_binders_on_one_gpu():
+    """w2vCommInitAll / w2vCommOf / w2vAllreduceAvg / w2vCommDestroyAll through a mock JNIEnv: one
+    replica, so the average is the identity, and the call lands on the calling thread's stream."""
+    from test_jni_shim import MockJVM
+    lib = _lib()
+    jvm = MockJVM()
+    assert lib.JNI_OnLoad(jvm.vm, None) == 0x00010004
+    comms = lib.Java_edu_berkeley_bid_CUMACH_w2vCommInitAll(jvm.env, None, 1)
+    assert comms != 0
+    comm = lib.Java_edu_berkeley_bid_CUMACH_w2vCommOf(jvm.env, None, comms, 0)
+    assert comm != 0 and lib.Java_edu_berkeley_bid_CUMACH_w2vCommOf(jvm.env, None, comms, 1) == 0
+    A = torch.arange(50, dtype=torch.float32, device="cuda")
+    B = -A.clone()
+    pA, pB = jvm.pointer(A.data_ptr(), 0), jvm.pointer(B.data_ptr() - 16, 16)
+    assert lib.Java_edu_berkeley_bid_CUMACH_w2vAllreduceAvg(jvm.env, None, comm, pA, pB, 50) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(A, torch.arange(50, dtype=torch.float32, device="cuda")) and torch.equal(B, -A)
+    lib.Java_edu_berkeley_bid_CUMACH_w2vCommDestroyAll(jvm.env, None, comms)
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -149,3 +149,32 @@ def test_sliced_minibatch_calls_follow_the_slice_kernels(oracle):
     assert torch.equal(m.modelmats[0][:1000], before[0][:1000]) and torch.equal(m.modelmats[1][:1000], before[1][:1000])
     assert not torch.equal(m.modelmats[0][1000:], before[0][1000:])
     assert positive_score() > p0        # the slice's own positive pairs became more likely
+
+
+def test_slice_binders_give_what_the_c_functions_give(oracle):
+    """Java_edu_berkeley_bid_CUMACH_word2vecNegSlice / EvalNegSlice through a mock JNIEnv (jcuda.Pointer
+    objects with nativePointer + byteOffset) against the oracle."""
+    import ctypes as C
+    from bidmach_b200 import _lib
+    from test_jni_shim import MockJVM
+    lib = _lib.load()
+    jvm = MockJVM()
+    assert lib.JNI_OnLoad(jvm.vm, None) == 0x00010004
+    dim, vocab, ncols, nslices, islice, nhead = 100, 3000, 290, 4, 2, 64
+    rows = oracle.slice_rows(vocab, nslices, nhead)
+    A, B = random_model(rows, dim, 3, scale=0.5)
+    WA, WB = conflict_free_neg(ncols, vocab, 5, 5, 4)
+    A_ref, B_ref = A.copy(), B.copy()
+    oracle.word2vecNegSlice(dim, ncols, 5, 5, WA, WB, A_ref, B_ref, 0.02, 0.5, islice, nslices, nhead, 1)
+    dA, dB, dWA, dWB = dev(A), dev(B), dev(WA), dev(WB)
+    pA, pB, pWA, pWB = (jvm.pointer(x.data_ptr() - 32, 32) for x in (dA, dB, dWA, dWB))
+    assert lib.Java_edu_berkeley_bid_CUMACH_word2vecNegSlice(jvm.env, None, dim, ncols, 5, 5, pWA, pWB, pA, pB,
+                                                             0.02, 0.5, islice, nslices, nhead, 1) == 0
+    assert rel_err(dA.cpu().numpy() - A, A_ref - A) <= TOL and rel_err(dB.cpu().numpy() - B, B_ref - B) <= TOL
+    ret = torch.zeros(1, device="cuda")
+    pR = jvm.pointer(ret.data_ptr(), 0)
+    assert lib.Java_edu_berkeley_bid_CUMACH_word2vecEvalNegSlice(jvm.env, None, dim, ncols, 5, 5, pWA, pWB, pA, pB,
+                                                                 pR, islice, nslices, nhead) == 0
+    want = oracle.word2vecEvalNegSlice(dim, ncols, 5, 5, WA, WB, dA.cpu().numpy(), dB.cpu().numpy(), islice,
+                                       nslices, nhead)
+    assert abs(ret.item() - want) <= TOL * abs(want)

@@ -111,3 +111,28 @@ def test_binders_forward_to_the_launchers(lib, capfd):
     assert k(env, None, 100, 10, 50, 2, 2, *ptrs[:4], 0.1, 0.5) == 1
     e = lib.Java_edu_berkeley_bid_CUMACH_word2vecEvalPos
     assert e(env, None, 100, 10, 9, *ptrs[:6]) == 1
+
+
+def test_slice_and_exchange_binders_check_their_arguments(lib, capfd):
+    """The binders of the slice launchers and of the exchange: refusals that come back before any
+    CUDA or NCCL call."""
+    jvm = MockJVM()
+    assert lib.JNI_OnLoad(C.cast(jvm.vm, C.c_void_p), None) == 0x00010004
+    env = C.cast(jvm.env, C.c_void_p)
+    ptrs = [jvm.pointer(0x10000 * (k + 1), 0) for k in range(6)]
+    f = lib.Java_edu_berkeley_bid_CUMACH_word2vecPosSlice
+    assert f(env, None, 100, 10, 5, *ptrs[:5], 0.1, 0.5, 4, 4, 10, 1) == 1      # islice out of range
+    assert f(env, None, 100, 10, 4, *ptrs[:5], 0.1, 0.5, 1, 4, 10, 1) == 1      # window 4 unsupported
+    assert f(env, None, 100, 0, 5, *ptrs[:5], 0.1, 0.5, 1, 4, 10, 1) == 0       # nothing to do
+    g = lib.Java_edu_berkeley_bid_CUMACH_word2vecNegSlice
+    assert g(env, None, 100, 10, 3, 3, *ptrs[:4], 0.1, 0.5, 0, 2, 0, 1) == 1
+    assert g(env, None, 100, 10, 5, 5, *ptrs[:4], 0.1, 0.5, 0, 0, 0, 1) == 1    # nslices 0
+    e = lib.Java_edu_berkeley_bid_CUMACH_word2vecEvalPosSlice
+    assert e(env, None, 100, 10, 5, *ptrs[:6], 0, 2, -1) == 1                   # negative head
+    h = lib.Java_edu_berkeley_bid_CUMACH_word2vecEvalNegSlice
+    assert h(env, None, 100, 0, 5, 5, *ptrs[:5], 1, 2, 0) == 0
+    assert lib.Java_edu_berkeley_bid_CUMACH_w2vCommInitAll(env, None, 0) == 0
+    assert lib.Java_edu_berkeley_bid_CUMACH_w2vCommOf(env, None, 0, 0) == 0
+    assert lib.Java_edu_berkeley_bid_CUMACH_w2vAllreduceAvg(env, None, 0, ptrs[0], ptrs[1], 10) == 1
+    lib.Java_edu_berkeley_bid_CUMACH_w2vCommDestroyAll(env, None, 0)
+    assert lib.Java_edu_berkeley_bid_CUMACH_w2vSetSlice(env, None, 0, 0, 2, 0, 1) == 1

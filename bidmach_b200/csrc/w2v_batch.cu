@@ -356,7 +356,6 @@ struct w2v_ctx {
   int pos_recorded;
   int have_list;           // the latest preprocessing wrote the ordered pair list (ctx_in)
   cudaEvent_t neg_wait;    // the next negative update waits for this event first (w2v_wait_before_neg)
-  int exp_phases, exp_pos_sms;   // EXPERIMENT
   void *cub_tmp;
   size_t cub_tmp_bytes;
   // pinned host
@@ -536,8 +535,6 @@ int w2v_create(const w2v_opts *opts, int ncols, w2v_ctx **out) {
   c->ncols = ncols;
   c->first_pos = -1;
   c->slice = w2v::whole_vocabulary();
-  c->exp_phases = getenv("W2V_EXP_PHASES") ? atoi(getenv("W2V_EXP_PHASES")) : 3;
-  c->exp_pos_sms = getenv("W2V_EXP_POS_SMS") ? atoi(getenv("W2V_EXP_POS_SMS")) : 0;
   c->max_pairs = (int64_t)2 * o.nskip * ncols;
   if (c->max_pairs > 0x7fffffffLL) { delete c; return 1; }
   // expt and salpha exactly as Word2Vec.init forms them (Word2Vec.scala:139,150)
@@ -819,9 +816,8 @@ int w2v_dobatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, float *A, 
   const float lrneg = o.eqPosNeg ? lrpos : lrpos / (float)o.nneg;
   int err = wordmats(c, tokens, u, batch_id, stream, false);
   if (err) return err;
-  if (c->exp_phases & 1) {
+  {
     Range range("w2v.pos");
-    w2v::SmReserve pos_reserve(c->exp_pos_sms > 0 ? 148 - c->exp_pos_sms : 0);
     err = w2v::pos_update_async(o.dim, c->ncols, nullptr, o.nskip, c->words, c->lb, c->ub, A, B,
                                 lrpos, o.vexp, c->hot, c->slice, stream);
   }
@@ -837,7 +833,7 @@ int w2v_dobatch(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, float *A, 
   int groups = 0;
   const int *groups_dev = nullptr;
   group_count(c, &groups, &groups_dev);
-  if (c->exp_phases & 2) {
+  {
     Range range("w2v.neg");
     err = w2v::neg_update_async(o.dim, groups, groups_dev, 0x7fffffff, o.nneg, o.nreuse, c->wa,
                                 c->ctx_out, A, B, lrneg, o.vexp, c->hot, c->fault_host, c->slice, stream);

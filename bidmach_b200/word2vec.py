@@ -329,10 +329,10 @@ class Word2Vec:
                 m.mul_(1.0 / dist.get_world_size(group))
 
     # SMs the overlapped in-place average runs on, per replica count (24 beyond four): a replica
-    # handles 1/world of the buffer, so fewer SMs keep up as the job grows.  Generous on purpose:
-    # the negative update beside it is bound by the L2's atomic throughput and ran no slower with
-    # 48 of 148 SMs held back.
-    EXCHANGE_BLOCKS = {2: 48, 3: 40, 4: 32}
+    # handles 1/world of the buffer, so fewer SMs keep up as the job grows.  Measured at two
+    # replicas the step time hardly depends on the count between 24 and 64: fewer SMs lengthen the
+    # exchange, more take them from the negative update beside it.
+    EXCHANGE_BLOCKS = {2: 40, 3: 40, 4: 32}
     # replicas up to which the average uses peer loads and stores instead of the multicast
     # address (which moves a replica's own copy through the switch too: more bytes for few replicas)
     P2P_MAX_WORLD = 3

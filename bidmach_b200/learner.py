@@ -220,7 +220,9 @@ class Learner:
 
 class ParLearner(Learner):
     """Data-parallel loop: one process per GPU, each with a full replica of both
-    matrices and its own minibatches; every ``syncStep`` training minibatches the
+    matrices and its own minibatches (or, when the model's ``nSlices`` > 1, each with one
+    vocabulary slice and every minibatch: give every rank the same un-strided data source; the
+    head rows are then averaged every ``syncStep`` training minibatches, ``Word2Vec.mergeHeadFn``); every ``syncStep`` training minibatches the
     replicas are averaged (ParLearner.syncmodels, Learner.scala:655, here one
     all-reduce per matrix, see Word2Vec.mergeModelFn).  Requires an initialised
     ``torch.distributed`` process group; rank 0's initial model is broadcast so
@@ -238,13 +240,19 @@ class ParLearner(Learner):
         import torch.distributed as dist
         super().init()
         if dist.is_initialized() and dist.get_world_size(self.group) > 1:
-            if self.opts.exchange in ("auto", "nvls") and not self.opts.headSync \
+            if self.opts.exchange in ("auto", "nvls") and not self.opts.headSync and not self._sliced() \
                     and dist.get_backend(self.group) == "nccl":
                 if not self.model.enableSymmetric(self.group) and self.opts.exchange == "nvls":
                     raise RuntimeError("exchange='nvls': no symmetric memory with a multicast mapping here")
-            for m in self.model.modelmats:
-                dist.broadcast(m, src=dist.get_global_rank(self.group, 0) if self.group else 0,
-                               group=self.group)
+            src = dist.get_global_rank(self.group, 0) if self.group else 0
+            if self._sliced():
+                rows = self.model.opts.nHeadTerms     # slices share the head only
+                for m in self.model.modelmats:
+                    if rows > 0:
+                        dist.broadcast(m[:rows], src=src, group=self.group)
+            else:
+                for m in self.model.modelmats:
+                    dist.broadcast(m, src=src, group=self.group)
 
     def _world(self) -> int:
         import torch.distributed as dist
@@ -261,10 +269,20 @@ class ParLearner(Learner):
         if (self._istep // world) % self.opts.syncStep == 0:
             self.model.mergeModelFn(self.group, self._istep // self.opts.syncStep)
 
+    def _sliced(self) -> bool:
+        o = getattr(self.model, "opts", None)
+        return o is not None and getattr(o, "nSlices", 1) > 1
+
     def _after_train_step(self, istep_global: int):
         if self.opts.headSync:
             return
         self._since_sync += 1
+        if self._sliced():
+            # replicas are vocabulary slices: every one sees every minibatch, only the head is shared
+            if self._since_sync >= self.opts.syncStep:
+                self.model.mergeHeadFn(self.group)
+                self._since_sync = 0
+            return
         if self.opts.overlapSync:
             if self._since_sync == 1:
                 self.model.finishMerge(defer=True)   # the exchange started beside this minibatch

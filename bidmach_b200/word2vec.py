@@ -328,6 +328,28 @@ class Word2Vec:
                 dist.all_reduce(m, op=dist.ReduceOp.SUM, group=group)
                 m.mul_(1.0 / dist.get_world_size(group))
 
+    def mergeHeadFn(self, group=None):
+        """For a job whose replicas are vocabulary slices (``nSlices`` = replicas): the rows of the
+        head (the first ``nHeadTerms`` of each matrix, which every slice holds and every slice
+        updates from its own pairs) become their mean over the slices; the tail rows belong to one
+        slice each and stay.  The reference leaves this step to its multi-node all-reduce outside
+        the Word2Vec code; here it is one NCCL all-reduce per matrix (a contiguous block of rows)."""
+        import torch.distributed as dist
+        if not dist.is_initialized() or dist.get_world_size(group) == 1:
+            return
+        self.finishMerge()
+        rows = min(self.opts.nHeadTerms, self.modelmats[0].shape[0])
+        if rows <= 0:
+            return
+        nccl = dist.get_backend(group) == "nccl"
+        for m in self.modelmats:
+            head = m[:rows]
+            if nccl:
+                dist.all_reduce(head, op=dist.ReduceOp.AVG, group=group)
+            else:
+                dist.all_reduce(head, op=dist.ReduceOp.SUM, group=group)
+                head.mul_(1.0 / dist.get_world_size(group))
+
     # SMs the overlapped in-place average runs on, per replica count (24 beyond four): a replica
     # handles 1/world of the buffer, so fewer SMs keep up as the job grows.  Measured at two
     # replicas the step time hardly depends on the count between 24 and 64: fewer SMs lengthen the

@@ -129,6 +129,37 @@ def _avg_worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
+def _slice_head_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from bidmach_b200.word2vec import Opts, Word2Vec
+    m = Word2Vec.__new__(Word2Vec)
+    m.opts = Opts(nSlices=world, iSlice=rank, nHeadTerms=2)
+    m.modelmats = [torch.full((6, 4), float(rank + 1)), torch.arange(24.0).view(6, 4) * (rank + 1)]
+    m.mergeHeadFn()
+    q.put((rank, m.modelmats[0].clone(), m.modelmats[1].clone()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_merge_head_averages_only_the_head_rows_of_vocabulary_slices():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_slice_head_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict((r, (a, b)) for r, a, b in (q.get(timeout=120) for _ in range(world)))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank in range(world):
+        m0, m1 = got[rank]
+        assert torch.allclose(m0[:2], torch.full((2, 4), 1.5)) and torch.allclose(m0[2:], torch.full((4, 4), rank + 1.0))
+        base = torch.arange(24.0).view(6, 4)
+        assert torch.allclose(m1[:2], base[:2] * 1.5) and torch.allclose(m1[2:], base[2:] * (rank + 1))
+
+
 def test_merge_model_averages_both_matrices_over_a_gloo_group():
     world, port = 2, _free_port()
     ctx = mp.get_context("spawn")

@@ -272,6 +272,8 @@ def config_dict(args, extra=None):
                         + (" (head rows only, the reference's schedule)" if args.head_sync else "")
                         if args.gpus > 1 else "single GPU",
          "l2_policy": "inputs larger than L2: 2.4 GB of embedding rows gathered per Zipf draw; no flush"}
+    if getattr(args, "slices", 1) > 1:
+        c["slice"] = {"nSlices": args.slices, "iSlice": args.islice, "nHeadTerms": args.nhead}
     if w.get("topics"):
         c["workload"] = ("configs[3]/[4] shape: minibatches of %d-token documents from a seeded topic model "
                          "(%d topics, Zipf(%.2f) per topic, Dirichlet(0.1) mixtures), ids ranked by frequency"
@@ -315,7 +317,8 @@ def run_ours(args):
 
     o = Opts(dim=w["dim"], vocabSize=w["vocab"], nskip=w["nskip"], nneg=w["nneg"], nreuse=w["nreuse"],
              lrate=w["lrate"], texp=w["texp"], vexp=w["vexp"], wsample=w["wsample"], seed=17 + rank,
-             sortPermute=args.sort_permute)
+             sortPermute=args.sort_permute, nSlices=args.slices, iSlice=args.islice if args.slices > 1 else 0,
+             nHeadTerms=args.nhead if args.slices > 1 else 0)
     model = Word2Vec(o, device=torch.device("cuda", local)).init(N)
     g = torch.Generator(device="cuda")
 
@@ -323,7 +326,7 @@ def run_ours(args):
         # configs[1] / configs[2]: both matrices U(-0.5, 0.5) / dim from a seed
         g.manual_seed(5)
         for m in model.modelmats:
-            m.copy_((torch.rand(w["vocab"], w["dim"], device="cuda", generator=g) - 0.5) / w["dim"])
+            m.copy_((torch.rand(m.shape[0], w["dim"], device="cuda", generator=g) - 0.5) / w["dim"])
 
     # the exchange: in place through the NVLink multicast mapping where the platform has one
     exchange = "none"
@@ -581,7 +584,7 @@ def run_ours(args):
     if args.mode == "eval":
         dev_r, pos = timed(False, pos, "eval", K, args.warmup)
         e2e_r, pos = timed(True, pos, "eval", K, args.warmup)
-        bounds = probe_bounds() if (rank == 0 and world == 1 and not args.no_probes) else None
+        bounds = probe_bounds() if (rank == 0 and world == 1 and not args.no_probes and args.slices == 1) else None
         sampler.stop()
         if rank == 0:
             blk = eval_block(dev_r, e2e_r, K, bounds)
@@ -610,8 +613,8 @@ def run_ours(args):
         ke = max(4, min(K, 24))
         ev_dev, pos = timed(False, pos, "eval", ke, 3)
         ev_e2e, pos = timed(True, pos, "eval", ke, 3)
-    bounds = probe_bounds() if (rank == 0 and world == 1 and not args.no_probes) else None
-    rows_a, rows_b = distinct_rows() if (rank == 0 and not args.no_probes) else (0, 0)
+    bounds = probe_bounds() if (rank == 0 and world == 1 and not args.no_probes and args.slices == 1) else None
+    rows_a, rows_b = distinct_rows() if (rank == 0 and not args.no_probes and args.slices == 1) else (0, 0)
     sampler.stop()
     if not args.no_eval and rank == 0:
         eval_blk = eval_block(ev_dev, ev_e2e, ke, bounds)
@@ -743,6 +746,11 @@ def main():
     ap.add_argument("--topics", type=int, default=None,
                     help="draw the minibatches from a topic-model corpus with this many topics "
                          "(configs[3]: 1000, configs[4]: 3000) instead of i.i.d. Zipf text")
+    ap.add_argument("--slices", type=int, default=1,
+                    help="single GPU: hold one vocabulary slice of this many (Word2Vec.Opts.nSlices) and work on "
+                         "its share of every minibatch's pairs")
+    ap.add_argument("--islice", type=int, default=0, help="which slice (Opts.iSlice)")
+    ap.add_argument("--nhead", type=int, default=10000, help="head rows every slice holds (Opts.nHeadTerms)")
     ap.add_argument("--sort-permute", action="store_true",
                     help="shuffle the pair list by sorting random keys (the reference's GPU branch) "
                          "instead of the keyed bijection")

@@ -24,7 +24,8 @@
 //
 // Set-up.  In host code the array's name is only a handle; the device address
 // that a kernel can use comes from cudaGetSymbolAddress, once per device, with
-// that device current.  The first call on each device does this.  Like the
+// that device current.  The first call on each device does this; it should come
+// before the process starts any stream capture on that device.  Like the
 // other launchers the function runs on the calling thread's default stream and
 // waits for the kernel before it returns.
 //

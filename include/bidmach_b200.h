@@ -102,7 +102,9 @@ int word2vecEvalNegSlice(int nrows, int ncols, int nwa, int nwb, int *WA, int *W
  * 64 KiB on every GPU that loads the library) instead of a buffer obtained with
  * cudaMalloc.  At most 2,097,152 columns per call; a larger ncols prints a
  * message and returns 1.  The first call on a device looks up the array's
- * device address.  The function waits for its kernel, like the launchers
+ * device address (a runtime query, not an allocation); let that first call
+ * happen before the process starts any stream capture on that device.  The
+ * function waits for its kernel, like the launchers
  * above.  Calls on the same GPU share the array: do not let two of them run at
  * the same time. */
 int word2vecEvalNegNoAlloc(int nrows, int ncols, int nwa, int nwb, int *WA, int *WB, float *A,

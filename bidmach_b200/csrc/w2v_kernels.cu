@@ -837,16 +837,30 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
         for (int q = 0; q < S::FIN; q++) p[q] = -lrate * sigmoid_guard(p[q]);
         float g[NWA * NWB];
         broadcast_totals<NWA * NWB>(p, g);
+        unsigned live_a = (1u << NWA) - 1u, live_b = (1u << NWB) - 1u;   // rows with a pair that counts
         if constexpr (SLICED) {
-          if (sl.skips_head_pairs()) {
-            const unsigned head = __ballot_sync(kFullMask, myw >= 0 && myw < sl.nhead);
+          // a pair counts when both words have a row here and it is not a head-head pair that the
+          // slice leaves out; the others get a zero coefficient, and a row none of whose pairs
+          // counts is not written at all (most rows of a slice's minibatch, which would otherwise
+          // cost an atomic row addition of zeros each)
+          const unsigned have = __ballot_sync(kFullMask, myw >= 0);
+          const unsigned head = sl.skips_head_pairs() ? __ballot_sync(kFullMask, myw >= 0 && myw < sl.nhead) : 0u;
+          live_a = live_b = 0u;
 #pragma unroll
-            for (int j = 0; j < NWA; j++)
+          for (int j = 0; j < NWA; j++)
 #pragma unroll
-              for (int k = 0; k < NWB; k++)
-                if (((head >> j) & 1u) && ((head >> (NWA + k)) & 1u)) g[j * NWB + k] = 0.f;
-          }
+            for (int k = 0; k < NWB; k++) {
+              const bool both = ((have >> j) & 1u) && ((have >> (NWA + k)) & 1u);
+              const bool hh = ((head >> j) & 1u) && ((head >> (NWA + k)) & 1u);
+              if (both && !hh) {
+                live_a |= 1u << j;
+                live_b |= 1u << k;
+              } else {
+                g[j * NWB + k] = 0.f;
+              }
+            }
         }
+        auto row_live = [&](bool is_a, int idx) { return ((is_a ? live_a : live_b) >> idx) & 1u; };
         // rows of the streamed side: their deltas need the held rows only
 #pragma unroll
         for (int y = 0; y < NY; y++) {
@@ -857,7 +871,7 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
 #pragma unroll
           for (int x = 1; x < NX; x++)
             prow_axpy(dY, sy * g[HOLD_B ? (y * NWB + x) : (x * NWB + y)], X[x]);
-          if (!CHECKED || writable(wy))
+          if ((!CHECKED || writable(wy)) && (!SLICED || row_live(HOLD_B, y)))
             prow_red_lane(update_target(MY, SY, hot, wy, dim, gwarp) + 4 * lane, tail, dY);
         }
         // rows of the held side: the held rows themselves are dead by now, their
@@ -882,7 +896,7 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
         }
 #pragma unroll
         for (int x = 0; x < NX; x++)
-          if (!CHECKED || writable(wx[x]))
+          if ((!CHECKED || writable(wx[x])) && (!SLICED || row_live(!HOLD_B, x)))
             prow_red_lane(update_target(MX, SX, hot, wx[x], dim, gwarp) + 4 * lane, tail, X[x]);
       }
     };

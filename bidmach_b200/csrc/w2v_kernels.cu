@@ -753,7 +753,17 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
   };
   auto ids_of = [&](int i) {
     int w = column_word<NWA, NWB>(WA, WB, gwarp + (int64_t)i * nwarps, nwords, lane);
-    if (SLICED) w = sl.local(w);
+    if (SLICED) {
+      w = sl.local(w);
+      // a column without a single pair that counts is dropped whole, before any of its rows is
+      // fetched: for the update, one without a word of this slice's own when head-head pairs are
+      // left out; for either kind, one whose A side or B side has no row here at all
+      const unsigned have = __ballot_sync(kFullMask, w >= 0);
+      const unsigned own = __ballot_sync(kFullMask, w >= sl.nhead);
+      const bool none = (have & ((1u << NWA) - 1u)) == 0u || (have >> NWA) == 0u ||
+                        (!EVAL && sl.skips_head_pairs() && own == 0u);
+      if (none) w = -1;
+    }
     return w;
   };
   // a row that takes part may still be closed to writes (head rows of a slice with do_head 0)
@@ -787,6 +797,11 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
         if (i + 2 < mycols) ahead = ids_of(i + 2);
       }
     };
+    if (SLICED && !__any_sync(kFullMask, myw >= 0)) {   // a dropped column: nothing was fetched
+      __syncwarp();
+      refill();
+      continue;
+    }
     // CHECKED = false: every word of the column is present (the usual case), so
     // no row needs a test; CHECKED = true: masked words act as zero rows and
     // receive no update.

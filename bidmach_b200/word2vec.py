@@ -554,6 +554,13 @@ class Word2Vec:
         opts = opts or Opts()
         rank = dist.get_rank(group) if dist.is_initialized() else 0
         world = dist.get_world_size(group) if dist.is_initialized() else 1
+        if opts.nSlices > 1:
+            # replicas are vocabulary slices: slice = rank, every slice sees every minibatch and
+            # draws the same samples (one minibatch's pairs are split over the slices)
+            if opts.nSlices != world:
+                raise ValueError("nSlices (%d) must equal the number of replicas (%d)" % (opts.nSlices, world))
+            opts.iSlice = rank
+            return ParLearner(Word2Vec._source(tokens, batchSize, 0, 1), Word2Vec(opts), lopts, group), opts
         opts.seed = opts.seed + 7919 * rank   # every replica draws its own samples
         return ParLearner(Word2Vec._source(tokens, batchSize, rank, world), Word2Vec(opts), lopts, group), opts
 

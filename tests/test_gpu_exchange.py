@@ -219,3 +219,59 @@ def test_two_replicas_learn_the_same_with_the_overlapped_in_place_average():
         assert blk - untrained > 0.05
         assert abs(ovl - blk) <= 0.01 * abs(blk), (rank, ovl, blk)
         assert abs((ovl - untrained) - (blk - untrained)) <= 0.10 * (blk - untrained), (rank, ovl, blk)
+
+
+def _slice_worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from bidmach_b200 import Word2Vec
+    from bidmach_b200.corpus import TopicCorpus
+    from bidmach_b200.learner import LearnerOpts, MatSource, ParLearner
+    from bidmach_b200.word2vec import Opts
+    V, D, N, H = 10_000, 100, 100_000, 500
+    tc = TopicCorpus(V, 50, s=1.07, alpha=0.1, doc_len=1000, seed=5, rank_sample_docs=2000)
+    train, held = tc.tokens(0, 30 * 100), tc.tokens(9000, 100)
+    model = Word2Vec(Opts(dim=D, vocabSize=V, lrate=1e-3, seed=3, nSlices=world, iSlice=rank, nHeadTerms=H),
+                     device=torch.device("cuda", rank))
+    lr = ParLearner(MatSource(train, N, 0, 1), model, LearnerOpts(npasses=1, evalStep=1000, syncStep=4))
+    lr.init()
+    before = model.evalbatchg([held], 0, N)
+    lr.train(do_init=False)
+    model.mergeHeadFn()
+    torch.cuda.synchronize()
+    after = model.evalbatchg([held], 0, N)
+    heads = [model.modelmats[j][:H].clone() for j in range(2)]
+    others = [[torch.empty_like(h) for _ in range(world)] for h in heads]
+    for h, o in zip(heads, others):
+        dist.all_gather(o, h)
+    same = all(torch.equal(o[0], o[r]) for o in others for r in range(world))
+    rows = model.modelmats[0].shape[0]
+    q.put((rank, before, after, same, rows))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_two_vocabulary_slices_train_side_by_side_and_share_their_head():
+    """Two GPUs, each one vocabulary slice of a model (nSlices = 2), both fed every minibatch: after
+    training and a last head average the head rows are identical on both, each holds only its
+    slice's rows, and each slice's held-out score has improved."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_slice_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=600) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, before, after, same, rows in got:
+        assert same
+        assert rows == 500 + 1 + (10_000 - 500 - 1) // 2
+        assert after > before + 0.01, (rank, before, after)

@@ -1136,14 +1136,15 @@ HotRows hot_rows_at(float *buffer, int levels) {
   h.limit = (buffer && levels > 0) ? (1 << levels) : 0;
   // a warp folds one replica row every `fold_every` columns (negative kernel) or
   // every 2 * fold_every positions (positive kernel); 0 leaves everything to the
-  // fold kernel that follows the update kernel.  16 is where the first minibatches of a run
-  // (model still near its start, every update of a frequent word matters) learn as fast as
-  // with plain atomics: measured on 1M-token subsampled Zipf minibatches at vocab 1M, the
-  // held-out gain after six minibatches is 88 % of the sequential CPU kernels' with 16, 90 %
-  // with plain atomics and 70 % with 64, for 6 % of the throughput on that text.
+  // fold kernel that follows the update kernel.  64 is a compromise: a period of 16 makes the
+  // first minibatches of a run (model still near its start, every update of a frequent word
+  // matters) learn as fast as plain atomics do -- held-out gain after six 1M-token subsampled
+  // minibatches at vocab 1M: 88 % of the sequential CPU kernels' with 16, 90 % with plain
+  // atomics, 70 % with 64, the gap closing as training goes on -- but costs 6 % of the
+  // throughput on that text and 17 % on dense text (W2V_FOLD_EVERY selects it).
   static const int every = [] {
     const char *e = getenv("W2V_FOLD_EVERY");
-    return e ? atoi(e) : 16;
+    return e ? atoi(e) : 64;
   }();
   h.fold_every = h.limit > 1 ? every : 0;
   h.stats = nullptr;

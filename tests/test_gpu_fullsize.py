@@ -219,10 +219,11 @@ def test_heldout_score_matches_cpu_reference_at_benchmark_scale(oracle):
     print("held-out score after %d minibatches: gpu %.5f cpu %.5f (untrained %.5f)" % (nbatches, gpu, cpu, 2 * np.log(0.5)))
     assert abs(gpu - cpu) <= 0.01 * abs(cpu), (gpu, cpu)
     # so early in a run the score has moved by only three times that tolerance, so the gains are
-    # compared as well: thousands of columns in flight read rows that 16 sequential threads would
-    # already have updated, which costs about a tenth of the gain at this point (nothing later on)
+    # compared as well.  Thousands of columns in flight read rows that 16 sequential threads would
+    # already have updated, and updates of the most frequent words wait in replica rows for the next
+    # fold: at this point that costs 30 % of the gain (10 % with plain atomics), nothing later on.
     untrained = 2 * np.log(0.5)
-    assert gpu - untrained >= 0.8 * (cpu - untrained), (gpu, cpu)
+    assert gpu - untrained >= 0.6 * (cpu - untrained), (gpu, cpu)
 
 
 def test_dense_text_at_the_script_rate_stays_bounded():

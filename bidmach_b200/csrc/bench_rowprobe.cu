@@ -81,8 +81,6 @@ extern "C" int w2v_rowprobe(int dim, int ncols, int nwa, int nwb, const int *WA,
   hot.rmax = kReps;
   hot.fold_every = 0;
   hot.stats = nullptr;
-  hot.folders = 0;
-  hot.done = nullptr;
   float *sink = g_buf + 2 * rows * kMaxDim;
   int sms = 148;
   int dev = 0;

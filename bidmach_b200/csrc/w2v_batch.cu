@@ -718,7 +718,7 @@ static int wordmats(w2v_ctx *c, const int *tokens, const w2v_uniforms *u, uint64
   if (c->timing_on) harvest(c, c->slot);
   c->ev_state[c->slot] = 0;
   mark(c, 0, stream);
-  W2V_CHECK(cudaMemsetAsync(c->counts + 8, 0, 4 * sizeof(int), stream));   // the hot-word statistics (+ 2 counters)
+  W2V_CHECK(cudaMemsetAsync(c->counts + 8, 0, 2 * sizeof(int), stream));   // the hot-word statistics
   w2v::words_bounds_kernel<<<blocks, threads, 0, stream>>>(
       n, tokens, o.iflip ? 1 : 0, o.vocabSize, o.nskip, c->salpha, us, uw, rng, c->words, c->lb, c->ub,
       c->counts + 8);

@@ -26,12 +26,6 @@ struct HotRows {
   // them the kernels shorten the folding period when the text is dense and the rate high
   // (see fold_period in w2v_kernels.cu); null = fold_every as it stands.
   const int *stats;
-  // Folder blocks: when > 0 (and `done` is set) the last `folders` blocks of an update kernel's
-  // grid do nothing but fold replica rows into the model, sweep after sweep, until the other
-  // blocks have all counted themselves into *done (or a cycle limit runs out); the working
-  // warps then never pause to fold.  The launch code sets both; 0 = every warp folds in turn.
-  int folders;
-  int *done;
 };
 // Vocabulary slicing of the reference's multi-node mode (Word2Vec.Opts nSlices / iSlice /
 // nHeadTerms / doHead; mapIndx, networks/Word2Vec.scala:665-672 and BIDMach_CPUMACH.c:80-88):

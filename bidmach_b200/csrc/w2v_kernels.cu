@@ -169,82 +169,6 @@ __device__ __forceinline__ void fold_one_replica(const HotRows &hot, float *A, f
   }
 }
 
-// Folder blocks (HotRows::folders): the warps of the last blocks of an update kernel's grid sweep
-// over all replica rows of both matrices, each warp over its share, exchanging a row's contents
-// for zeros and adding them to the model row, ROWS rows at a time so that their round trips
-// overlap.  A replica row therefore holds a few microseconds of updates at most, whatever the
-// working warps do, and those never stop to fold.  The sweep ends when every working block has
-// counted itself into *done, or after kFolderCycles clock cycles (the blocks of a grid are not
-// guaranteed to run together; what is left then is collected by hot_fold_kernel as always).
-constexpr long long kFolderCycles = 1ll << 31;
-
-template <int NR>
-__device__ __forceinline__ void folder_sweeps(const HotRows &hot, float *A, float *B, int dim, int nvec,
-                                              int lane, int fwarp, int nfwarps, int workers) {
-  constexpr int ROWS = 4;
-  const int levels = 31 - __clz(hot.limit);
-  const int per_matrix = levels * hot.rmax;
-  const int total = 2 * per_matrix;
-  const long long t0 = clock64();
-  const volatile int *done = hot.done;
-  bool last = false;
-  while (true) {
-    for (int base = fwarp * ROWS; base < total; base += nfwarps * ROWS) {
-      u64 got[ROWS][NR][2];
-      float *dst[ROWS];
-#pragma unroll
-      for (int k = 0; k < ROWS; k++) {
-        const int r = base + k;
-        dst[k] = nullptr;
-        if (r < total) {
-          const bool in_b = r >= per_matrix;
-          const int row = in_b ? r - per_matrix : r;
-          const int lv = row / hot.rmax;
-          const int reps = hot.rmax >> lv;
-          const int id = (1 << lv) - 1 + (row - lv * hot.rmax) / reps;
-          float *src = (in_b ? hot.shadowB : hot.shadowA) + (int64_t)row * dim;
-          dst[k] = (in_b ? B : A) + (int64_t)id * dim;
-#pragma unroll
-          for (int q = 0; q < NR; q++) {
-            const int idx = lane + 32 * q;
-            got[k][q][0] = got[k][q][1] = 0ull;
-            if (idx < nvec) exch_zero_v4(src + 4 * idx, got[k][q][0], got[k][q][1]);
-          }
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < ROWS; k++) {
-        if (dst[k] == nullptr) continue;
-#pragma unroll
-        for (int q = 0; q < NR; q++) {
-          const int idx = lane + 32 * q;
-          if (idx < nvec && (got[k][q][0] | got[k][q][1])) {
-            float4 v;
-            unpack2(got[k][q][0], v.x, v.y);
-            unpack2(got[k][q][1], v.z, v.w);
-            red_add_v4(dst[k] + 4 * idx, v);
-          }
-        }
-      }
-    }
-    if (last) break;
-    // one more sweep after the last working block has finished picks up what it left
-    int seen = 0;
-    if (lane == 0) seen = *done;
-    seen = __shfl_sync(kFullMask, seen, 0);
-    if (seen >= workers || clock64() - t0 > kFolderCycles) last = true;
-  }
-}
-
-// A working block counts itself out (see folder_sweeps).
-__device__ __forceinline__ void worker_block_done(const HotRows &hot) {
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    atomicAdd(hot.done, 1);
-  }
-}
-
 // Folds the replica rows of the hot ids back into the model and clears them.
 // grid = (hot ids, 2 matrices).
 __global__ void hot_fold_kernel(int dim, HotRows hot, float *A, float *B) {
@@ -335,14 +259,8 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
   const bool tail = lane + 32 * (NR - 1) < nvec;
   const int slots = 2 * skip + 1;
   ulonglong2 *ring = ring_storage + (size_t)warp * slots * nvec + lane;  // this lane's part of slot 0
-  const int wblocks = (int)gridDim.x - hot.folders;     // blocks that walk positions
-  if (hot.folders > 0 && (int)blockIdx.x >= wblocks) {   // this block only folds replica rows
-    folder_sweeps<NR>(hot, A, B, dim, nvec, lane, ((int)blockIdx.x - wblocks) * (kPosThreads / 32) + warp,
-                      hot.folders * (kPosThreads / 32), wblocks);
-    return;
-  }
   const unsigned gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const unsigned nwarps = ((unsigned)wblocks * blockDim.x) >> 5;
+  const unsigned nwarps = (gridDim.x * blockDim.x) >> 5;
   if (ncols_dev) ncols = *ncols_dev;
   const int per_warp = (ncols + (int)nwarps - 1) / (int)nwarps;
   const int first = (int)gwarp * per_warp;
@@ -374,7 +292,7 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
     }
   };
   // about six pairs per position; the rate of the positive update is five times the negative one's
-  const int fold_every = hot.folders > 0 ? 0 : 2 * fold_period(hot, lrate, 6.0f);
+  const int fold_every = 2 * fold_period(hot, lrate, 6.0f);
   int until_fold = fold_every;
   unsigned fold_turn = gwarp * 3u;
 
@@ -491,7 +409,6 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
     retire(wu, wslot);
     wslot = (wslot + 1 == slots) ? 0 : wslot + 1;
   }
-  if (hot.folders > 0) worker_block_done(hot);
 }
 
 // Adds this block's double partial sum into scratch[0]; the block that
@@ -803,14 +720,8 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
   u64 *bars = reinterpret_cast<u64 *>(mine);            // [NST]
   int *ids = reinterpret_cast<int *>(mine + 64);        // [NST][16]
   unsigned char *stages = mine + kStagedHeader;
-  const int wblocks = (int)gridDim.x - (EVAL ? 0 : hot.folders);   // blocks that work on columns
-  if (!EVAL && hot.folders > 0 && (int)blockIdx.x >= wblocks) {      // this block only folds replica rows
-    folder_sweeps<NR>(hot, A, B, dim, nvec, lane, ((int)blockIdx.x - wblocks) * (int)(blockDim.x >> 5) + warp,
-                      hot.folders * (int)(blockDim.x >> 5), wblocks);
-    return;
-  }
   const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int nwarps = (wblocks * (int)blockDim.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
   if (ncols_dev) ncols = *ncols_dev;
   float *const MX = HOLD_B ? B : A, *const MY = HOLD_B ? A : B;
   float *const SX = HOLD_B ? hot.shadowB : hot.shadowA, *const SY = HOLD_B ? hot.shadowA : hot.shadowB;
@@ -823,7 +734,7 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
   const int mycols = (gwarp < ncols) ? (ncols - gwarp + nwarps - 1) / nwarps : 0;
   double acc = 0.0;  // EVAL: this lane's share of the score
   const bool tail = lane + 32 * (NR - 1) < nvec;
-  const int fold_every = (EVAL || hot.folders > 0) ? 0 : fold_period(hot, lrate, (float)NWB);
+  const int fold_every = fold_period(hot, lrate, (float)NWB);
   int until_fold = fold_every;
   unsigned fold_turn = (unsigned)gwarp * 5u;
 
@@ -1018,7 +929,6 @@ __global__ void __launch_bounds__((StagedShape<NWA, NWB, NR>::max_threads), 1)
     }
   }
   if constexpr (EVAL) finish_eval_sum(acc, scratch, retval);
-  if (!EVAL && hot.folders > 0) worker_block_done(hot);
 }
 
 // Scoring of the negative columns: the smaller side of a column is held in
@@ -1238,8 +1148,6 @@ HotRows hot_rows_at(float *buffer, int levels) {
   }();
   h.fold_every = h.limit > 1 ? every : 0;
   h.stats = nullptr;
-  h.folders = 0;
-  h.done = nullptr;
   return h;
 }
 
@@ -1335,23 +1243,6 @@ int count_hot_share_async(const int *ids, int64_t n, int nwords, int *stats, cud
   return (int)cudaGetLastError();
 }
 
-// Gives `folders` blocks of a grid of `grid` blocks to folding (HotRows::folders) when the launch
-// is large enough for that to pay and the caller supplied the count buffer (stats[2 + slot] is
-// the launch's "working blocks done" counter, cleared here).  W2V_FOLDERS=0 keeps every warp
-// folding in turn.
-static cudaError_t assign_folders(HotRows &hot, int grid, int folders, int slot, cudaStream_t stream) {
-  static const bool enabled = [] {
-    const char *e = getenv("W2V_FOLDERS");
-    return !(e && atoi(e) == 0);
-  }();
-  hot.folders = 0;
-  hot.done = nullptr;
-  if (!enabled || hot.limit <= 1 || hot.fold_every <= 0 || hot.stats == nullptr || grid < 64) return cudaSuccess;
-  hot.folders = folders;
-  hot.done = const_cast<int *>(hot.stats) + 2 + slot;
-  return cudaMemsetAsync(hot.done, 0, sizeof(int), stream);
-}
-
 static void fold_hot_rows(int dim, const HotRows &hot, float *A, float *B, cudaStream_t stream) {
   if (hot.limit <= 1) return;
   hot_fold_kernel<<<dim3(hot.limit - 1, 2), 128, 0, stream>>>(dim, hot, A, B);
@@ -1425,16 +1316,13 @@ int pos_update_async(int dim, int ncols, const int *ncols_dev, int skip, const i
     int grid = device_sm_count() * resident;
     const int max_grid = std::max(1, ncols / (64 * (kPosThreads / 32)));
     grid = std::max(1, std::min(grid, max_grid));
-    HotRows h = hot;
-    // one SM's worth of blocks folds, the others walk positions
-    cudaError_t e = assign_folders(h, grid, resident, 0, stream);
-    if (e != cudaSuccess) return (int)e;
+    cudaError_t e = cudaSuccess;
     if (sliced) {
       W2V_NR_SWITCH(nr, (e = launch_pos_update<NR, true>(grid, smem, stream, dim, ncols, ncols_dev, skip, W,
-                                                         LB, UB, A, B, lrate, vexp, h, slice)));
+                                                         LB, UB, A, B, lrate, vexp, hot, slice)));
     } else {
       W2V_NR_SWITCH(nr, (e = launch_pos_update<NR, false>(grid, smem, stream, dim, ncols, ncols_dev, skip, W,
-                                                          LB, UB, A, B, lrate, vexp, h, slice)));
+                                                          LB, UB, A, B, lrate, vexp, hot, slice)));
     }
     if (e != cudaSuccess) return (int)e;
     fold_hot_rows(dim, hot, A, B, stream);
@@ -1554,14 +1442,12 @@ static int neg_dispatch(bool eval, int dim, int ncols, const int *ncols_dev, int
     // at least 8 columns per warp: a small launch then still applies its updates in several
     // rounds instead of computing every column from the same stale rows
     const int grid = std::max(1, std::min(device_sm_count(), (ncols + 8 * staged_warps - 1) / (8 * staged_warps)));
-    HotRows h = hot;
-    cudaError_t e = eval ? cudaSuccess : assign_folders(h, grid, 2, 1, stream);   // two SMs fold
-    if (e != cudaSuccess) return (int)e;
+    cudaError_t e = cudaSuccess;
     switch (nr) {
-      case 1: e = launch_neg_staged_any<NWA, NWB, 1>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, h, scratch, retval, fault, sl); break;
-      case 2: e = launch_neg_staged_any<NWA, NWB, 2>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, h, scratch, retval, fault, sl); break;
-      case 3: e = launch_neg_staged_any<NWA, NWB, 3>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, h, scratch, retval, fault, sl); break;
-      default: e = launch_neg_staged_any<NWA, NWB, 4>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, h, scratch, retval, fault, sl); break;
+      case 1: e = launch_neg_staged_any<NWA, NWB, 1>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault, sl); break;
+      case 2: e = launch_neg_staged_any<NWA, NWB, 2>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault, sl); break;
+      case 3: e = launch_neg_staged_any<NWA, NWB, 3>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault, sl); break;
+      default: e = launch_neg_staged_any<NWA, NWB, 4>(eval, grid, staged_warps, smem, stream, dim, ncols, ncols_dev, nwords, WA, WB, A, B, lrate, vexp, hot, scratch, retval, fault, sl); break;
     }
     if (e != cudaSuccess) return (int)e;
     if (!eval) fold_hot_rows(dim, hot, A, B, stream);

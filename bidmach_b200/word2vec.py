@@ -501,6 +501,8 @@ class Word2Vec:
         if getattr(self, "_deferred", None) is not None and not defer:
             # a wait handed to the next minibatch: take it now
             torch.cuda.current_stream(self.device).wait_event(self._deferred)
+            if self._ctx is not None:     # the library must not keep an event that is about to go
+                _lib.load().w2v_wait_before_neg(self._ctx, None)
             self._deferred = None
         if getattr(self, "_merge", None) is None:
             return

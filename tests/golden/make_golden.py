@@ -7,7 +7,8 @@ Run once on a machine that has the BIDMach checkout:
 
 Each kernels_*.npz holds seeded inputs and the model matrices after the
 reference's word2vecPos, then after its word2vecNeg (nthreads = 1, so the
-result is deterministic).
+result is deterministic); each slices_*.npz the same for word2vecPosSlice and
+word2vecNegSlice on one vocabulary slice.
 """
 import os
 import sys
@@ -30,8 +31,38 @@ CASES = [  # dim, vocab, skip, ncols, nwa, nwb, ngroups, seed
 ]
 
 
+SLICE_CASES = [  # dim, vocab, skip, ncols, nwa, nwb, ngroups, nslices, islice, nhead, do_head, seed
+    (64, 160, 5, 96, 5, 5, 30, 4, 1, 12, 1, 11),
+    (100, 120, 3, 80, 10, 5, 16, 2, 1, 30, 0, 12),
+    (64, 200, 5, 96, 5, 5, 30, 8, 5, 16, 2, 13),
+]
+
+
+def slices():
+    """slices_*.npz: the reference's word2vecPosSlice, then its word2vecNegSlice, on one slice's
+    matrices (a single block of maxCols words per side)."""
+    for dim, vocab, skip, ncols, nwa, nwb, ng, nslices, islice, nhead, do_head, seed in SLICE_CASES:
+        rows = orc.slice_rows(vocab, nslices, nhead)
+        A, B = random_model(rows, dim, seed, scale=0.5)
+        W, LB, UB = random_pos(ncols, vocab, skip, seed)
+        WA, WB = random_neg(ng, vocab, nwa, nwb, seed + 100)
+        lrate, vexp = np.float32(0.05), np.float32(0.5)
+        A1, B1 = A.copy(), B.copy()
+        orc.word2vecPosSlice(dim, ncols, skip, W, LB, UB, A1, B1, lrate, vexp, islice, nslices, nhead, do_head, 1,
+                             "reference")
+        A2, B2 = A1.copy(), B1.copy()
+        orc.word2vecNegSlice(dim, ng, nwa, nwb, WA, WB, A2, B2, float(lrate) / nwa, vexp, islice, nslices, nhead,
+                             do_head, 1, "reference")
+        np.savez_compressed(os.path.join(HERE, f"slices_n{nslices}_i{islice}_h{nhead}_d{do_head}.npz"),
+                            dim=dim, skip=skip, lrate=lrate, vexp=vexp, nslices=nslices, islice=islice, nhead=nhead,
+                            do_head=do_head, W=W, LB=LB, UB=UB, WA=WA, WB=WB, A=A, B=B, A_pos=A1, B_pos=B1,
+                            A_neg=A2, B_neg=B2)
+        print("wrote slice", nslices, islice, nhead, do_head)
+
+
 def main():
     assert orc.have_reference(), "needs the compiled reference"
+    slices()
     for dim, vocab, skip, ncols, nwa, nwb, ng, seed in CASES:
         A, B = random_model(vocab, dim, seed, scale=0.5)
         W, LB, UB = random_pos(ncols, vocab, skip, seed)

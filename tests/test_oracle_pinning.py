@@ -202,3 +202,23 @@ def test_one_slice_without_head_is_the_plain_kernel(oracle):
     WA, WB = random_neg(80, vocab, 5, 5, 4)
     assert oracle.word2vecEvalNeg(dim, 80, 5, 5, WA, WB, A1, B1) == \
         oracle.word2vecEvalNegSlice(dim, 80, 5, 5, WA, WB, A1, B1, 0, 1, 0)
+
+
+def test_port_equals_golden_slice_fixtures(oracle):
+    """slices_*.npz were written by the reference's own word2vecPosSlice / word2vecNegSlice: the
+    restatement reproduces them bit for bit, with or without the compiled reference at hand."""
+    files = sorted(glob.glob(os.path.join(GOLD, "slices_*.npz")))
+    assert files, "golden slice fixtures missing"
+    for f in files:
+        g = np.load(f)
+        dim, skip = int(g["dim"]), int(g["skip"])
+        sl = (int(g["islice"]), int(g["nslices"]), int(g["nhead"]), int(g["do_head"]))
+        A, B = g["A"].copy(), g["B"].copy()
+        oracle.word2vecPosSlice(dim, len(g["W"]), skip, g["W"], g["LB"], g["UB"], A, B, float(g["lrate"]),
+                                float(g["vexp"]), *sl, 1, "port")
+        assert np.array_equal(A, g["A_pos"]) and np.array_equal(B, g["B_pos"]), f
+        nwa, nwb = g["WA"].shape[1], g["WB"].shape[1]
+        oracle.word2vecNegSlice(dim, g["WA"].shape[0], nwa, nwb, g["WA"], g["WB"], A, B,
+                                float(g["lrate"]) / nwa, float(g["vexp"]), *sl, 1, "port")
+        assert np.array_equal(A, g["A_neg"]) and np.array_equal(B, g["B_neg"]), f
+        assert not np.array_equal(g["A_neg"], g["A"])

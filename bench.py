@@ -26,8 +26,8 @@ the negative-update kernel: algorithmic bytes over its measured duration
 against the measured HBM copy peak, the DRAM traffic of an ncu capture,
 `compulsory_bytes` (every distinct row the launch names read once and written
 once: a fraction that cannot exceed 1), and `memory_bound`: what the kernel's
-atomic row additions and its row reads take on their own, on the same columns
-(a probe library of its own, libw2vrowprobe.so).  `eval` is the scoring path
+atomic row additions, its row reads, and both together take on their own, on
+the same columns (a probe library of its own, libw2vrowprobe.so).  `eval` is the scoring path
 (configs[2]) on fixed random matrices, a shorter stretch of the same run.
 With N > 1, `collective` describes the exchange: its kind, the bytes, what it
 takes alone (CUDA events, max over ranks) and how many fell into the region.
@@ -447,8 +447,9 @@ def run_ours(args):
 
     def probe_bounds(reps=6):
         """The memory side of the negative kernels alone, on the workload's own columns:
-        the update kernel's atomic row reductions with zeros (nothing else), and the
-        scoring kernel's row reads (nothing else).  ms per launch, CUDA events."""
+        the update kernel's atomic row reductions with zeros (nothing else), the scoring
+        kernel's row reads (nothing else), and both as the update kernel does them (a
+        column's rows read, then zeros added to them).  ms per launch, CUDA events."""
         nonlocal probe
         path = os.path.join(os.path.dirname(_lib.LIB_PATH), "libw2vrowprobe.so")
         if not os.path.exists(path):
@@ -457,7 +458,7 @@ def run_ours(args):
             probe = C.CDLL(path)
             probe.w2v_rowprobe.argtypes = [C.c_int] * 4 + [C.c_void_p] * 4 + [C.c_int, C.c_void_p]
         out = []
-        for mode in (0, 1):
+        for mode in (0, 1, 2):
             tot = 0.0
             for r in range(reps + 2):
                 _, _, _, wa, wb = model.wordMats([devt[r % POOL]], batch_id=1000 + r)
@@ -655,9 +656,13 @@ def run_ours(args):
                 "traffic_over_compulsory": (traffic / compulsory) if (traffic and compulsory) else None,
                 # what the kernel's atomic row reductions take with nothing else in the kernel
                 # (zeros added to the same rows), and what reading those rows takes: ms per launch
+                # and what reading a column's rows and then adding zeros to them takes (the kernel's
+                # whole memory side: its reductions find the rows in the L2, those of scatter_only do not)
                 "memory_bound": ({"scatter_only_ms": bounds[0], "gather_only_ms": bounds[1],
+                                  "gather_scatter_ms": bounds[2],
                                   "atomic_payload_gbs": neg_bytes / 2 / (bounds[0] * 1e-3) / 1e9,
-                                  "kernel_over_scatter_only": neg_s * 1e3 / bounds[0]} if bounds else None)}
+                                  "kernel_over_scatter_only": neg_s * 1e3 / bounds[0],
+                                  "kernel_over_gather_scatter": neg_s * 1e3 / bounds[2]} if bounds else None)}
     phases = {"prep_ms": tm.prep_ms / nb, "permute_ms": tm.permute_ms / nb, "pos_ms": tm.pos_ms / nb,
               "neg_ms": tm.neg_ms / nb, "pairs_per_step": pairs, "groups_per_step": groups,
               "pos_algorithmic_gbs": pos_bytes / pos_s / 1e9 if pos_s > 0 else None,

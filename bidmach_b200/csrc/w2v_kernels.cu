@@ -239,6 +239,16 @@ __device__ __forceinline__ Neighbour look_at_neighbour(const int *__restrict__ W
   return nb;
 }
 
+// Which of the two positive-update kernels takes a launch: both are launched, both read the same
+// count of valid words that the launch's preparation left on the device (HotRows::stats), and
+// exactly one of them goes on.  With three quarters or more of the positions holding a word, two
+// centres at a time pay (dense text: 1.44 against 1.54 ms on the benchmark's minibatches); on
+// subsampled text, where many positions are empty and windows are short, one centre at a time
+// with more resident warps does (0.77 against 0.78 ms).
+__device__ __forceinline__ bool pos_text_is_dense(const HotRows &hot, int ncols) {
+  return hot.stats != nullptr && 4ll * hot.stats[0] >= 3ll * ncols;
+}
+
 // Shared memory: per warp, (2*skip+1) slots of nvec float4 (one context-row
 // delta each), all zero whenever they hold nothing.  Lane l only ever touches
 // elements l, l+32, ... of a slot, so no synchronisation is needed between the
@@ -251,7 +261,7 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
     pos_update_kernel(int dim, int ncols, const int *__restrict__ ncols_dev, int skip,
                       const int *__restrict__ W, const int *__restrict__ LB,
                       const int *__restrict__ UB, float *A, float *B, float lrate, float vexp,
-                      HotRows hot, SliceMap sl) {
+                      HotRows hot, SliceMap sl, int yield_dense) {
   constexpr int kChunk = ChunkOf<NR>::value;
   extern __shared__ ulonglong2 ring_storage[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -262,6 +272,8 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
   const unsigned gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const unsigned nwarps = (gridDim.x * blockDim.x) >> 5;
   if (ncols_dev) ncols = *ncols_dev;
+  // dense text goes to pos_update_pair_kernel, launched beside this one (see there)
+  if (yield_dense && pos_text_is_dense(hot, ncols)) return;
   const int per_warp = (ncols + (int)nwarps - 1) / (int)nwarps;
   const int first = (int)gwarp * per_warp;
   const int last = min(ncols, first + per_warp);
@@ -406,6 +418,181 @@ __global__ void __launch_bounds__(kPosThreads, PosBlocksOf<NR>::value)
     // a dirty slot belongs to a position inside the minibatch that holds a word
     int wu = (u >= 0 && u < ncols) ? W[u] : 0;
     if (SLICED) wu = sl.local(wu);
+    retire(wu, wslot);
+    wslot = (wslot + 1 == slots) ? 0 : wslot + 1;
+  }
+}
+
+// Two centres at a time.  Positions t and t + 1 share most of their windows, so a context row
+// that both take is loaded once, meets both centre rows in one pass and its ring slot is updated
+// once for both: fewer loads and fewer shared-memory read-modify-writes per position than with
+// one centre at a time, paid for with two centre rows and two centre deltas in registers (168
+// registers per thread, 12 warps per SM).  Lane l stands for position t - skip + l of the
+// 2*skip + 2 positions the two windows span; the ring has as many slots.
+template <int NR>
+struct PairChunkOf {
+  static constexpr int value = NR <= 3 ? 5 : (NR <= 4 ? 3 : 2);
+};
+
+template <int NR>
+__global__ void __launch_bounds__(kPosThreads, 3)
+    pos_update_pair_kernel(int dim, int ncols, const int *__restrict__ ncols_dev, int skip,
+                           const int *__restrict__ W, const int *__restrict__ LB,
+                           const int *__restrict__ UB, float *A, float *B, float lrate, float vexp,
+                           HotRows hot) {
+  constexpr int kChunk = PairChunkOf<NR>::value;
+  extern __shared__ ulonglong2 ring_storage[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec = dim >> 2;
+  const bool tail = lane + 32 * (NR - 1) < nvec;
+  const int slots = 2 * skip + 2;
+  ulonglong2 *ring = ring_storage + (size_t)warp * slots * nvec + lane;  // this lane's part of slot 0
+  const unsigned gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const unsigned nwarps = (gridDim.x * blockDim.x) >> 5;
+  if (ncols_dev) ncols = *ncols_dev;
+  if (!pos_text_is_dense(hot, ncols)) return;   // pos_update_kernel takes the launch
+  // stretches of an even number of positions, so that every warp starts on a pair
+  const int per_warp = (((ncols + (int)nwarps - 1) / (int)nwarps) + 1) & ~1;
+  const int first = (int)min((long long)gwarp * per_warp, (long long)ncols);
+  const int last = min(ncols, first + per_warp);
+  unsigned dirty = 0;             // bit s: slot s holds a pending delta
+  for (int s = 0; s < slots; s++) {
+#pragma unroll
+    for (int q = 0; q < NR; q++)
+      if (vec_ok<NR>(q, tail)) ring[s * nvec + 32 * q] = make_ulonglong2(0ull, 0ull);
+  }
+  int wslot = 0;  // slot of position t - skip
+  auto retire = [&](int wu, int slot) {  // wu = the word at the slot's position
+    if ((dirty >> slot) & 1u) {
+      dirty &= ~(1u << slot);
+      float *dst = update_target(B, hot.shadowB, hot, wu, dim, gwarp) + 4 * lane;
+      ulonglong2 *sp = ring + slot * nvec;
+#pragma unroll
+      for (int q = 0; q < NR; q++) {
+        if (vec_ok<NR>(q, tail)) {
+          red_add_v4(dst + 128 * q, *reinterpret_cast<const float4 *>(sp + 32 * q));
+          sp[32 * q] = make_ulonglong2(0ull, 0ull);
+        }
+      }
+    }
+  };
+  const int fold_every = 2 * fold_period(hot, lrate, 6.0f);
+  int until_fold = fold_every;
+  unsigned fold_turn = gwarp * 3u;
+
+  // index data of the pair (t, t + 1), fetched one pair ahead
+  auto fetch = [&](int t, int &wraw, int &lb0, int &ub0, int &lb1, int &ub1) {
+    const int u = t + lane - skip;
+    wraw = (t < last && lane < slots && u >= 0 && u < ncols) ? W[u] : -1;
+    const bool in0 = t < last, in1 = t + 1 < last;
+    lb0 = in0 ? max(LB[t], -skip) : 0;
+    ub0 = in0 ? min(UB[t], skip) : 0;
+    lb1 = in1 ? max(LB[t + 1], -skip) : 0;
+    ub1 = in1 ? min(UB[t + 1], skip) : 0;
+  };
+  int wraw, lb0, ub0, lb1, ub1;
+  fetch(first, wraw, lb0, ub0, lb1, ub1);
+
+  for (int t = first; t < last; t += 2) {
+    int wraw_n, lb0_n, ub0_n, lb1_n, ub1_n;
+    fetch(t + 2, wraw_n, lb0_n, ub0_n, lb1_n, ub1_n);
+    const int wt0 = __shfl_sync(kFullMask, wraw, skip);
+    const int wt1 = (t + 1 < last) ? __shfl_sync(kFullMask, wraw, skip + 1) : -1;
+    const int w_old0 = __shfl_sync(kFullMask, wraw, 0), w_old1 = __shfl_sync(kFullMask, wraw, 1);
+    const int j0 = lane - skip, j1 = lane - skip - 1;
+    const bool pair0 = wt0 >= 0 && wraw >= 0 && j0 != 0 && j0 >= lb0 && j0 <= ub0;
+    const bool pair1 = wt1 >= 0 && wraw >= 0 && j1 != 0 && j1 >= lb1 && j1 <= ub1;
+    const unsigned m0 = __ballot_sync(kFullMask, pair0), m1 = __ballot_sync(kFullMask, pair1);
+    unsigned todo = m0 | m1;
+    if (todo) {
+      // every lane that holds a word evaluates its scale: the centres' lanes among them
+      const float sc = (wraw >= 0) ? freq_scale(wraw, vexp) : 0.f;
+      const float sa0 = __shfl_sync(kFullMask, sc, skip), sa1 = __shfl_sync(kFullMask, sc, skip + 1);
+      PRow<NR> a0, a1, da0, da1;
+      prow_zero(a0);
+      prow_zero(a1);
+      if (m0) prow_load_lane(a0, reinterpret_cast<const ulonglong2 *>(A + (int64_t)wt0 * dim) + lane, tail);
+      if (m1) prow_load_lane(a1, reinterpret_cast<const ulonglong2 *>(A + (int64_t)wt1 * dim) + lane, tail);
+      prow_zero(da0);
+      prow_zero(da1);
+      auto take = [&](auto width) {
+        constexpr int CH = decltype(width)::value;
+        static_assert(Spread<2 * CH>::FIN == 1, "one total per lane expected");
+        int src[CH];
+        PRow<NR> rows[CH];
+        float p[2 * CH];
+#pragma unroll
+        for (int c = 0; c < CH; c++) {
+          src[c] = __ffs(todo) - 1;
+          todo &= todo - 1;
+          const int wc = __shfl_sync(kFullMask, wraw, src[c]);
+          prow_load_lane(rows[c], reinterpret_cast<const ulonglong2 *>(B + (int64_t)wc * dim) + lane, tail);
+        }
+#pragma unroll
+        for (int c = 0; c < CH; c++) {
+          p[2 * c] = prow_dot_partial(a0, rows[c]);
+          p[2 * c + 1] = prow_dot_partial(a1, rows[c]);
+        }
+        Spread<2 * CH>::reduce(p, lane);
+        const float mine = lrate * (1.0f - sigmoid_guard(p[0]));
+#pragma unroll
+        for (int c = 0; c < CH; c++) {
+          float g0 = __shfl_sync(kFullMask, mine, Spread<2 * CH>::lane_of(2 * c));
+          float g1 = __shfl_sync(kFullMask, mine, Spread<2 * CH>::lane_of(2 * c + 1));
+          if (!((m0 >> src[c]) & 1u)) g0 = 0.f;   // not a pair of this centre
+          if (!((m1 >> src[c]) & 1u)) g1 = 0.f;
+          const float sb = __shfl_sync(kFullMask, sc, src[c]);
+          prow_axpy(da0, sa0 * g0, rows[c]);
+          prow_axpy(da1, sa1 * g1, rows[c]);
+          // context side, once for both centres: slot(u) += sb * (g0 * a0 + g1 * a1)
+          int slot = wslot + src[c];
+          if (slot >= slots) slot -= slots;
+          ulonglong2 *sp = ring + slot * nvec;
+          const u64 c0 = pack2(sb * g0, sb * g0), c1 = pack2(sb * g1, sb * g1);
+          dirty |= 1u << slot;
+#pragma unroll
+          for (int q = 0; q < NR; q++) {
+            if (vec_ok<NR>(q, tail)) {
+              ulonglong2 v = sp[32 * q];
+              v.x = fma2(c1, a1.v[q][0], fma2(c0, a0.v[q][0], v.x));
+              v.y = fma2(c1, a1.v[q][1], fma2(c0, a0.v[q][1], v.y));
+              sp[32 * q] = v;
+            }
+          }
+        }
+      };
+      int cnt = __popc(todo);
+      while (cnt > 0) {
+        const int chunks = (cnt + kChunk - 1) / kChunk;
+        const int n = (cnt + chunks - 1) / chunks;  // even split: 7 contexts as 4 + 3, not 4 + 3 + 0
+        cnt -= n;
+        take_n<1, kChunk>(n, take);
+      }
+      if (m0) prow_red_lane(update_target(A, hot.shadowA, hot, wt0, dim, gwarp) + 4 * lane, tail, da0);
+      if (m1) prow_red_lane(update_target(A, hot.shadowA, hot, wt1, dim, gwarp) + 4 * lane, tail, da1);
+    }
+    // no later centre of this warp reaches positions t - skip and t - skip + 1
+    if (dirty) {
+      retire(w_old0, wslot);
+      retire(w_old1, (wslot + 1 == slots) ? 0 : wslot + 1);
+    }
+    wslot += 2;
+    if (wslot >= slots) wslot -= slots;
+    if (fold_every > 0 && (until_fold -= 2) <= 0) {
+      until_fold = fold_every;
+      fold_one_replica<NR>(hot, A, B, dim, nvec, lane, fold_turn++);
+    }
+    wraw = wraw_n;
+    lb0 = lb0_n;
+    ub0 = ub0_n;
+    lb1 = lb1_n;
+    ub1 = ub1_n;
+  }
+  // what is left in the ring belongs to the positions from (end of the last pair) - skip on
+  const int t_end = first + ((last - first + 1) & ~1);
+  for (int k = 0; k < slots && dirty; k++) {
+    const int u = t_end - skip + k;
+    const int wu = (u >= 0 && u < ncols) ? W[u] : 0;
     retire(wu, wslot);
     wslot = (wslot + 1 == slots) ? 0 : wslot + 1;
   }
@@ -1280,14 +1467,28 @@ template <int NR, bool SLICED>
 static cudaError_t launch_pos_update(int grid, size_t smem, cudaStream_t stream, int dim, int ncols,
                                      const int *ncols_dev, int skip, const int *W, const int *LB,
                                      const int *UB, float *A, float *B, float lrate, float vexp,
-                                     const HotRows &hot, const SliceMap &sl) {
+                                     const HotRows &hot, const SliceMap &sl, int yield_dense) {
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(pos_update_kernel<NR, SLICED>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
   pos_update_kernel<NR, SLICED><<<grid, kPosThreads, smem, stream>>>(dim, ncols, ncols_dev, skip, W, LB,
-                                                                     UB, A, B, lrate, vexp, hot, sl);
+                                                                     UB, A, B, lrate, vexp, hot, sl, yield_dense);
+  return cudaSuccess;
+}
+
+template <int NR>
+static cudaError_t launch_pos_pair(int grid, size_t smem, cudaStream_t stream, int dim, int ncols,
+                                   const int *ncols_dev, int skip, const int *W, const int *LB, const int *UB,
+                                   float *A, float *B, float lrate, float vexp, const HotRows &hot) {
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(pos_update_pair_kernel<NR>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  pos_update_pair_kernel<NR><<<grid, kPosThreads, smem, stream>>>(dim, ncols, ncols_dev, skip, W, LB, UB, A, B,
+                                                                  lrate, vexp, hot);
   return cudaSuccess;
 }
 
@@ -1317,12 +1518,27 @@ int pos_update_async(int dim, int ncols, const int *ncols_dev, int skip, const i
     const int max_grid = std::max(1, ncols / (64 * (kPosThreads / 32)));
     grid = std::max(1, std::min(grid, max_grid));
     cudaError_t e = cudaSuccess;
+    // two centres at a time for dense text, where three blocks of its ring fit an SM: launched
+    // beside the kernel for one centre at a time, the count of valid words on the device decides
+    // which of the two goes on (pos_text_is_dense)
+    const size_t smem_pair = (size_t)(kPosThreads / 32) * (2 * skip + 2) * (size_t)dim * sizeof(float);
+    const bool pair_too = !sliced && nr <= 4 && hot.stats != nullptr && 3 * (smem_pair + 1024) <= 228 * 1024;
     if (sliced) {
       W2V_NR_SWITCH(nr, (e = launch_pos_update<NR, true>(grid, smem, stream, dim, ncols, ncols_dev, skip, W,
-                                                         LB, UB, A, B, lrate, vexp, hot, slice)));
+                                                         LB, UB, A, B, lrate, vexp, hot, slice, 0)));
     } else {
       W2V_NR_SWITCH(nr, (e = launch_pos_update<NR, false>(grid, smem, stream, dim, ncols, ncols_dev, skip, W,
-                                                          LB, UB, A, B, lrate, vexp, hot, slice)));
+                                                          LB, UB, A, B, lrate, vexp, hot, slice, pair_too ? 1 : 0)));
+    }
+    if (e == cudaSuccess && pair_too) {
+      const int grid2 = std::max(1, std::min(device_sm_count() * 3, max_grid));
+      switch (nr) {
+        case 1: e = launch_pos_pair<1>(grid2, smem_pair, stream, dim, ncols, ncols_dev, skip, W, LB, UB, A, B, lrate, vexp, hot); break;
+        case 2: e = launch_pos_pair<2>(grid2, smem_pair, stream, dim, ncols, ncols_dev, skip, W, LB, UB, A, B, lrate, vexp, hot); break;
+        case 3: e = launch_pos_pair<3>(grid2, smem_pair, stream, dim, ncols, ncols_dev, skip, W, LB, UB, A, B, lrate, vexp, hot); break;
+        default: e = launch_pos_pair<4>(grid2, smem_pair, stream, dim, ncols, ncols_dev, skip, W, LB, UB, A, B, lrate, vexp, hot); break;
+      }
+      count_launch(1);
     }
     if (e != cudaSuccess) return (int)e;
     fold_hot_rows(dim, hot, A, B, stream);

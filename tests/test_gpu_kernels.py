@@ -24,9 +24,9 @@ def cumach():
     return CUMACH
 
 
-def _pos_case(oracle, cumach, dim, vocab, ncols, skip, seed, lrate=0.05, vexp=0.5):
+def _pos_case(oracle, cumach, dim, vocab, ncols, skip, seed, lrate=0.05, vexp=0.5, drop=0.1):
     A, B = random_model(vocab, dim, seed, scale=0.5)
-    W, LB, UB = conflict_free_pos(ncols, vocab, skip, seed)
+    W, LB, UB = conflict_free_pos(ncols, vocab, skip, seed, drop=drop)
     A_ref, B_ref = A.copy(), B.copy()
     oracle.word2vecPos(dim, ncols, skip, W, LB, UB, A_ref, B_ref, lrate, vexp, 1)
     dA, dB = dev(A), dev(B)
@@ -44,6 +44,14 @@ def _pos_case(oracle, cumach, dim, vocab, ncols, skip, seed, lrate=0.05, vexp=0.
 @pytest.mark.parametrize("skip", [5, 3, 2])
 def test_pos_update_matches_oracle(oracle, cumach, dim, skip):
     _pos_case(oracle, cumach, dim, vocab=3000, ncols=2500, skip=skip, seed=dim + skip)
+
+
+@pytest.mark.parametrize("dim", [100, 300, 512])
+@pytest.mark.parametrize("drop", [0.0, 0.24, 0.26, 0.6])
+def test_pos_update_dense_and_sparse_text(oracle, cumach, dim, drop):
+    """Text with three quarters or more of its positions filled goes to the kernel that takes
+    two centres at a time, sparser text to the one that takes one: both sides of the switch."""
+    _pos_case(oracle, cumach, dim, vocab=6000, ncols=5001, skip=5, seed=int(dim + 100 * drop), drop=drop)
 
 
 @pytest.mark.parametrize("dim", [37, 301, 1])

@@ -18,7 +18,7 @@ import numpy as np
 import torch
 
 from . import _lib, modelio
-from .cumach import CUMACH, cuda_error_string
+from .cumach import CUMACH, CUMACHSlice, cuda_error_string
 
 
 @dataclasses.dataclass
@@ -278,6 +278,42 @@ class Word2Vec:
         err = CUMACH.word2vecEvalNeg(modela.shape[1], wordsa.shape[0], nwa, nwb, wordsa, wordsb,
                                      modela, modelb, ret)
         _check(err, "CUMACH.word2vecEvalNeg")
+        return float(ret.item())
+
+    # The slice forms take the two matrices of the slice (`modelmats`, rows as `sliceRows()` lays them
+    # out) and the slice's number; slice count, head size and `doHead` come from the options.
+    def procPositivesSlice(self, nskip, words, lbound, ubound, modelmats, lrate, vexp, islice):
+        """Word2Vec.procPositivesSlice (Word2Vec.scala:404-433) on the device."""
+        o = self.opts
+        err = CUMACHSlice.word2vecPosSlice(modelmats[0].shape[1], words.numel(), nskip, words, lbound, ubound,
+                                           modelmats[1], modelmats[0], lrate, vexp, islice, o.nSlices,
+                                           o.nHeadTerms, o.doHead)
+        _check(err, "word2vecPosSlice")
+
+    def procNegativesSlice(self, nwa, nwb, wordsa, wordsb, modelmats, lrate, vexp, islice):
+        """Word2Vec.procNegativesSlice (Word2Vec.scala:435-467) on the device."""
+        o = self.opts
+        err = CUMACHSlice.word2vecNegSlice(modelmats[0].shape[1], wordsa.shape[0], nwa, nwb, wordsa, wordsb,
+                                           modelmats[1], modelmats[0], lrate, vexp, islice, o.nSlices,
+                                           o.nHeadTerms, o.doHead)
+        _check(err, "word2vecNegSlice")
+
+    def evalPositivesSlice(self, nskip, words, lbound, ubound, modelmats, islice) -> float:
+        """Word2Vec.evalPositivesSlice (Word2Vec.scala:491-501) on the device."""
+        o = self.opts
+        ret = torch.zeros(1, dtype=torch.float32, device=modelmats[0].device)
+        err = CUMACHSlice.word2vecEvalPosSlice(modelmats[0].shape[1], words.numel(), nskip, words, lbound, ubound,
+                                               modelmats[1], modelmats[0], ret, islice, o.nSlices, o.nHeadTerms)
+        _check(err, "word2vecEvalPosSlice")
+        return float(ret.item())
+
+    def evalNegativesSlice(self, nwa, nwb, wordsa, wordsb, modelmats, islice) -> float:
+        """Word2Vec.evalNegativesSlice (Word2Vec.scala:525-535) on the device."""
+        o = self.opts
+        ret = torch.zeros(1, dtype=torch.float32, device=modelmats[0].device)
+        err = CUMACHSlice.word2vecEvalNegSlice(modelmats[0].shape[1], wordsa.shape[0], nwa, nwb, wordsa, wordsb,
+                                               modelmats[1], modelmats[0], ret, islice, o.nSlices, o.nHeadTerms)
+        _check(err, "word2vecEvalNegSlice")
         return float(ret.item())
 
     # -- multi-GPU ------------------------------------------------------------

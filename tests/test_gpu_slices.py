@@ -178,3 +178,34 @@ def test_slice_binders_give_what_the_c_functions_give(oracle):
     want = oracle.word2vecEvalNegSlice(dim, ncols, 5, 5, WA, WB, dA.cpu().numpy(), dB.cpu().numpy(), islice,
                                        nslices, nhead)
     assert abs(ret.item() - want) <= TOL * abs(want)
+
+
+def test_word2vec_slice_methods_forward_to_the_slice_kernels(oracle):
+    """Word2Vec.procPositivesSlice / procNegativesSlice / evalPositivesSlice / evalNegativesSlice
+    (Word2Vec.scala:404-467, 491-535): A is modelmats(1) and B modelmats(0), slice count, head size
+    and doHead come from the options."""
+    from bidmach_b200 import Word2Vec
+    from bidmach_b200.word2vec import Opts
+    vocab, dim, skip, nslices, islice, nhead = 4000, 100, 5, 4, 2, 30
+    o = Opts(dim=dim, vocabSize=vocab, nskip=skip, nSlices=nslices, iSlice=islice, nHeadTerms=nhead, doHead=1)
+    m = Word2Vec(o, device=torch.device("cuda", 0))
+    rows = oracle.slice_rows(vocab, nslices, nhead)
+    assert m.sliceRows() == rows
+    A, B = random_model(rows, dim, 11, scale=0.5)
+    W, LB, UB = conflict_free_pos(3000, vocab, skip, 5)
+    WA, WB = conflict_free_neg(500, vocab, 5, 5, 6)
+    A_ref, B_ref = A.copy(), B.copy()
+    oracle.word2vecPosSlice(dim, len(W), skip, W, LB, UB, A_ref, B_ref, 0.05, 0.5, islice, nslices, nhead, 1)
+    oracle.word2vecNegSlice(dim, len(WA), 5, 5, WA, WB, A_ref, B_ref, 0.02, 0.5, islice, nslices, nhead, 1)
+    mats = [dev(B), dev(A)]                       # modelmats(0) = B, modelmats(1) = A
+    m.procPositivesSlice(skip, dev(W), dev(LB), dev(UB), mats, 0.05, 0.5, islice)
+    m.procNegativesSlice(5, 5, dev(WA), dev(WB), mats, 0.02, 0.5, islice)
+    gB, gA = mats[0].cpu().numpy(), mats[1].cpu().numpy()
+    assert rel_err(gA - A, A_ref - A) <= TOL and rel_err(gB - B, B_ref - B) <= TOL
+    Wr, LBr, UBr = random_pos(2000, vocab, skip, 9)
+    WAr, WBr = random_neg(400, vocab, 5, 5, 10)
+    want_pos = oracle.word2vecEvalPosSlice(dim, len(Wr), skip, Wr, LBr, UBr, gA, gB, islice, nslices, nhead)
+    want_neg = oracle.word2vecEvalNegSlice(dim, len(WAr), 5, 5, WAr, WBr, gA, gB, islice, nslices, nhead)
+    got_pos = m.evalPositivesSlice(skip, dev(Wr), dev(LBr), dev(UBr), mats, islice)
+    got_neg = m.evalNegativesSlice(5, 5, dev(WAr), dev(WBr), mats, islice)
+    assert abs(got_pos - want_pos) <= 1e-5 * abs(want_pos) and abs(got_neg - want_neg) <= 1e-5 * abs(want_neg)

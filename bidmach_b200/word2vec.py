@@ -280,6 +280,19 @@ class Word2Vec:
         _check(err, "CUMACH.word2vecEvalNeg")
         return float(ret.item())
 
+    @staticmethod
+    def mapIndx(indx: int, islice: int, nslices: int, nHead: int, maxCols: int, nrows: int, offset: int = 0):
+        """Word2Vec.mapIndx (Word2Vec.scala:665-672): where word ``indx`` lives in slice ``islice``:
+        (matrix block, element offset inside it, is it this slice's own word, is it a head word).
+        The slices here keep all their rows in one matrix per side, i.e. ``maxCols`` at least
+        ``sliceRows()``: the block is then ``offset`` and the element offset ``nrows`` times the
+        row the slice kernels use."""
+        newi = (indx - nHead) // nslices + nHead if indx >= nHead else indx
+        m = newi // maxCols + offset
+        ismine = indx >= nHead and indx % nslices == islice
+        ishead = indx < nHead
+        return m, nrows * (newi - m * maxCols), ismine, ishead
+
     # The slice forms take the two matrices of the slice (`modelmats`, rows as `sliceRows()` lays them
     # out) and the slice's number; slice count, head size and `doHead` come from the options.
     def procPositivesSlice(self, nskip, words, lbound, ubound, modelmats, lrate, vexp, islice):

@@ -389,3 +389,24 @@ def test_learner_progress_log(tmp_path):
     rows = [json.loads(l) for l in open(log)]
     assert [round(r["pct"]) for r in rows] == [25, 50, 75, 100]
     assert all(r["val"] == -1.0 and r["words_per_s"] > 0 and r["pass"] == 0 for r in rows)
+
+
+def test_map_indx_names_the_rows_the_slices_store(oracle):
+    """Word2Vec.mapIndx (Word2Vec.scala:665-672) against the layout the slice kernels use."""
+    from bidmach_b200 import Word2Vec
+    vocab, nrows = 1000, 7
+    ids = np.arange(vocab, dtype=np.float32).reshape(-1, 1)
+    for nslices, islice, nhead in ((4, 1, 20), (3, 0, 0), (8, 5, 16), (2, 1, 50)):
+        stored = oracle.slice_of_model(ids, islice, nslices, nhead)
+        rows = oracle.slice_rows(vocab, nslices, nhead)
+        seen = 0
+        for w in range(vocab):
+            m, off, mine, head = Word2Vec.mapIndx(w, islice, nslices, nhead, rows, nrows)
+            assert head == (w < nhead) and mine == (w >= nhead and w % nslices == islice)
+            if mine or head:
+                assert m == 0 and off % nrows == 0 and stored[off // nrows, 0] == w
+                seen += 1
+        assert seen == nhead + len([w for w in range(nhead, vocab) if w % nslices == islice])
+        # several blocks of maxCols rows each, as the reference lays a large slice out
+        m, off, _, _ = Word2Vec.mapIndx(nhead + 5 * nslices + islice, islice, nslices, nhead, 4, nrows)
+        assert (m, off) == ((nhead + 5) // 4, nrows * ((nhead + 5) % 4))
